@@ -1,0 +1,327 @@
+#!/usr/bin/env python3
+"""Benchmark of the optimizer-step engine: fused AdamW + global-norm clip + bf16 shadow.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl engine|reference]
+
+One "step" is one pass of the hot path over one parameter set: the gradient-norm
+reduction and the fused update (clip coefficient folded in, bf16 shadow written in the
+same pass) — two kernel launches. At one GPU the workload is the Llama-style 1.3B
+parameter set; at N > 1 it is the Llama-3-8B-shaped set sharded ZeRO-1 style
+(reduce-scatter of gradients, clip, shard update, all-gather of bf16 shadows).
+
+Prints ONE JSON line. `value` is parameters updated per second with everything resident
+in HBM; `e2e` is the same step driven through the C ABI's host-buffer entry point, with
+the gradients copied from page-locked host memory and the norm read back inside the
+timed region; `roofline` rates the update kernel against the measured HBM copy
+bandwidth; `cpu_baseline` is the CPU restatement of the reference's host optimizer timed
+on this machine's cores on a bounded sample of the same workload.
+
+`--impl reference` times that CPU path alone (the reference is Go and cannot be built
+in this image, so its arithmetic is run from the C restatement under oracle/).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "fused AdamW+clip+bf16-shadow step throughput"
+UNIT = "Gparams/s"
+BYTES_UPDATE = 30   # R p,g,m,v (16) + W p,m,v (12) + W bf16 (2)
+BYTES_NORM = 4      # R g
+FALLBACK_HBM_GBS = 6650.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (MEASURED_PEAKS.json absent)"
+
+
+def ncu_traffic_per_param():
+    """DRAM bytes per parameter of the update kernel from the committed ncu summary, if any."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except Exception:
+        return {}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.lines = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+                power.append(float(parts[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower() == "active":
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU path (the reference's host optimizer, restated in C under oracle/)
+# ---------------------------------------------------------------------------------------
+def cpu_reference_run(ps, sample_params: int, steps: int, warmup: int, cores: int):
+    """Times clip (serial float64 sum + in-place scale) and AdamW (per-tensor worker split)
+    on a bounded sample: the leading tensors of the workload up to sample_params elements."""
+    import numpy as np
+
+    from gograd_b200 import paramsets
+    from oracle import oracle
+    sample = paramsets.scaled(ps, sample_params)
+    rng = np.random.default_rng(ps.grad_seed)
+    params = [(rng.standard_normal(s.numel, dtype=np.float32) * np.float32(0.02)) for s in sample.params]
+    grads0 = [(rng.standard_normal(s.numel, dtype=np.float32) * np.float32(ps.grad_std)) for s in sample.params]
+    wd = sample.groups[0].weight_decay
+    opt = oracle.OracleAdamW(params, lr=ps.hparams["lr"], weight_decay=wd, beta1=ps.hparams["beta1"],
+                             beta2=ps.hparams["beta2"], eps=ps.hparams["eps"], max_procs=cores)
+    n = sum(s.numel for s in sample.params)
+    times = []
+    for it in range(warmup + steps):
+        grads = [g.copy() for g in grads0]  # fresh gradients; the copy is outside the timed region
+        t0 = time.perf_counter()
+        if ps.max_norm > 0:
+            oracle.clip_grad_norm(grads, ps.max_norm)
+        opt.step(grads)
+        dt = time.perf_counter() - t0
+        if it >= warmup:
+            times.append(dt)
+    sec = sum(times) / len(times)
+    return {"value": n / sec / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{len(sample.params)} leading tensors of {ps.key} = {n} params, {steps} steps after {warmup} warm-up; "
+                      "C restatement of the Go host optimizer (AdamW split over min(cores, n/65536) workers per tensor, "
+                      "clip single-threaded, as the reference)",
+            "ms_per_step_sample": sec * 1e3}, n, sec
+
+
+def run_reference_arm(args):
+    from gograd_b200 import paramsets
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    key = args.workload if args.workload != "auto" else ("llama1b" if args.gpus == 1 else "llama8b")
+    ps = paramsets.get(key)
+    cores = os.cpu_count() or 1
+    steps = max(1, min(args.steps, 10))
+    warmup = max(1, min(args.warmup, 2))
+    base, n, sec = cpu_reference_run(ps, args.cpu_sample_params, steps, warmup, cores)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": key, "params_total": ps.numel, "params_in_sample": n,
+                   "note": "the reference is Go (no toolchain in this image): CPU host path restated in C, all host "
+                           "threads, bounded sample per step"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------
+# engine arm, one GPU
+# ---------------------------------------------------------------------------------------
+def run_single(args):
+    import torch
+
+    import gograd_b200 as eng
+    from gograd_b200 import paramsets, workload
+    from gograd_b200.engine import OE_WRITE_SHADOW
+
+    key = args.workload if args.workload != "auto" else "llama1b"
+    ps = paramsets.get(key)
+    torch.cuda.set_device(0)
+    eng.init(0)
+    state = workload.materialize(ps, "cuda:0")
+    plan = eng.Plan(state.descs(), 0, args.chunk)
+    if args.variant:
+        plan.set_variant(args.variant)
+    n_params = state.numel
+    hp = ps.hparams
+    flags = OE_WRITE_SHADOW if ps.bf16_shadow else 0
+    stream = torch.cuda.current_stream()
+    step_no = [0]
+
+    def hparams():
+        step_no[0] += 1
+        b1, b2 = workload.bias_corrections(hp["beta1"], hp["beta2"], step_no[0])
+        return eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], b1, b2, ps.max_norm, flags)
+
+    def one_step(events=None):
+        if events is not None:
+            events[0].record(stream)
+        plan.grad_norm(0, stream)
+        if events is not None:
+            events[1].record(stream)
+        plan.adamw_step(hparams(), stream)
+        if events is not None:
+            events[2].record(stream)
+
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    eng.launch_count_reset()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record(stream)
+    for k in range(args.steps):
+        one_step(ev[k])
+    stop.record(stream)
+    torch.cuda.synchronize()
+    launches = eng.launch_count()
+    total_ms = start.elapsed_time(stop)
+    ms_per_step = total_ms / args.steps
+    norm_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    upd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    norm_value, _ = plan.read_norm(stream)
+
+    # ---- end to end through the host-buffer entry point -------------------------------
+    e2e = None
+    if not args.no_e2e:
+        try:
+            host_grads = [torch.empty(t.numel(), dtype=torch.float32).pin_memory() for t in state.g]
+            for hg, g in zip(host_grads, state.g):
+                hg.copy_(g)
+            torch.cuda.synchronize()
+            e2e_steps = max(3, min(args.steps, 10))
+            plan.adamw_step_from_host(hparams(), host_grads, stream)  # warm-up
+            t0 = time.perf_counter()
+            for _ in range(e2e_steps):
+                plan.adamw_step_from_host(hparams(), host_grads, stream)
+            dt = (time.perf_counter() - t0) / e2e_steps
+            e2e = {"value": n_params / dt / 1e9, "unit": UNIT, "h2d_bytes_per_step": 4 * n_params,
+                   "d2h_bytes_per_step": 32, "ms_per_step": dt * 1e3, "steps": e2e_steps,
+                   "api": "oe_adamw_step_from_host (gradients from page-locked host memory, norm read back, stream "
+                          "synchronised every step)"}
+            del host_grads
+        except Exception as exc:  # pinned allocation can fail on a small host
+            e2e = {"value": None, "unit": UNIT, "h2d_bytes_per_step": 4 * n_params, "d2h_bytes_per_step": 32,
+                   "error": str(exc)[:200]}
+    clocks = sampler.stop()
+
+    peak, peak_kind = measured_peak()
+    achieved = BYTES_UPDATE * n_params / (upd_ms * 1e-3) / 1e9
+    traffic = ncu_traffic_per_param().get("oe_adamw_fused_bytes_per_param")
+    roofline = {"bound": "hbm", "kernel": "oe_adamw_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "peak_kind": peak_kind,
+                "traffic": None if traffic is None else traffic * n_params,
+                "algorithmic_bytes_per_launch": BYTES_UPDATE * n_params, "kernel_ms": upd_ms,
+                "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
+                "norm_kernel": {"kernel": "oe_grad_sumsq", "kernel_ms": norm_ms,
+                                "achieved": BYTES_NORM * n_params / (norm_ms * 1e-3) / 1e9,
+                                "frac": BYTES_NORM * n_params / (norm_ms * 1e-3) / 1e9 / peak},
+                "whole_step": {"bytes_per_param": BYTES_UPDATE + BYTES_NORM,
+                               "achieved": (BYTES_UPDATE + BYTES_NORM) * n_params / (ms_per_step * 1e-3) / 1e9,
+                               "frac": (BYTES_UPDATE + BYTES_NORM) * n_params / (ms_per_step * 1e-3) / 1e9 / peak}}
+
+    cpu_baseline = None
+    if not args.no_cpu_baseline:
+        cpu_baseline, _, _ = cpu_reference_run(ps, args.cpu_sample_params, 5, 1, os.cpu_count() or 1)
+
+    line = {
+        "metric": METRIC, "value": n_params / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": 1,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": key, "title": ps.title, "params": n_params, "tensors": len(ps.params),
+                   "optimizer": "adamw", "max_norm": ps.max_norm, "bf16_shadow": ps.bf16_shadow,
+                   "chunk_elems": plan.info(5), "grid_update": plan.info(3), "grid_norm": plan.info(4),
+                   "variant": args.variant or "default",
+                   "l2": "inputs larger than L2: %.1f GB of p/g/m/v/shadow per step" % ((18 * n_params) / 1e9),
+                   "grad_norm": norm_value},
+        "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
+        "gpu_launches": launches,
+    }
+    print(json.dumps(line))
+    plan.close()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="engine", choices=["engine", "reference"])
+    ap.add_argument("--workload", default="auto")
+    ap.add_argument("--variant", default="")
+    ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-sample-params", type=int, default=120_000_000)
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 or world > 1:
+        from gograd_b200 import zero1_bench
+        return zero1_bench.run(args)
+    return run_single(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

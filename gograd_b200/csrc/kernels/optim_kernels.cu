@@ -1,0 +1,477 @@
+// Optimizer-step kernels for sm_100a (B200): multi-tensor AdamW / SGD update with the
+// clip coefficient folded in and the bf16 shadow written in the same pass, the
+// two-level gradient-norm reduction, the in-place gradient scale and the stand-alone
+// fp32 -> bf16 cast. Compiled to a cubin and loaded by the shim through the driver API;
+// this file holds device code only.
+//
+// Work layout. The host builds two device tables: one oe_dev_tensor per parameter
+// with a present gradient and one oe_dev_chunk per `chunk_elems` elements of such a
+// tensor. Every kernel is one launch over the whole parameter set: a persistent grid
+// (a multiple of the SM count) strides over the chunk table, so a 2048-element norm
+// weight and a 65M-element embedding cost the same per element.
+//
+// Arithmetic. The update follows the reference's host (CPU) optimizer operation for
+// operation with explicit round-to-nearest intrinsics, so that no multiply-add is
+// contracted: the results are meant to be bit-identical to that code, not merely
+// close (autograd/nn.go:519-528, autograd/sgd.go:205-220, autograd/nn.go:318-333).
+// The path is HBM-bound (about 0.3 flop per byte): no tensor cores, no shared-memory
+// staging; the design goal is bytes in flight — 128-bit streaming loads, several per
+// thread before the first use, streaming stores.
+#include <stdint.h>
+
+#include "../shim/oe_table.h"
+
+#define OE_THREADS 256
+#ifndef OE_UNROLL
+#define OE_UNROLL 2
+#endif
+#ifndef OE_NORM_UNROLL
+#define OE_NORM_UNROLL 4
+#endif
+
+// ---------------------------------------------------------------------------------
+// small helpers
+// ---------------------------------------------------------------------------------
+
+// fp32 -> bf16, round to nearest even: the reference's integer formula
+// (autograd/cuda_kernels.go:86-87) for every non-NaN input; NaN becomes a quiet NaN
+// with the input's sign instead of wrapping into an infinity or a zero.
+__device__ __forceinline__ uint32_t oe_bf16_rne(float x) {
+    uint32_t bits = __float_as_uint(x);
+    uint32_t r = (bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16;
+    if ((bits & 0x7fffffffu) > 0x7f800000u) r = ((bits >> 16) & 0x8000u) | 0x7fc0u;
+    return r & 0xffffu;
+}
+
+// Clip coefficient from the norm record of the reduction. Host rule
+// (autograd/nn.go:327-328): scale only when norm > max_norm > 0. Device-form rule
+// (autograd/cuda_kernels.go:676): fminf(1, max_norm/(norm+1e-6)) whenever max_norm > 0.
+__device__ __forceinline__ float oe_clip_coefficient(const oe_dev_norm* norm, float max_norm, uint32_t flags) {
+    if (norm == nullptr || !(max_norm > 0.0f)) return 1.0f;
+    float n = norm->norm;
+    float c = __fdiv_rn(max_norm, __fadd_rn(n, 1e-6f));
+    if (flags & OE_F_CLIP_DEVFORM) return fminf(1.0f, c);
+    return n > max_norm ? c : 1.0f;
+}
+
+struct oe_chunk_view {
+    const oe_dev_tensor* t;
+    uint64_t base;  // first element of the chunk inside the tensor
+    uint32_t n;     // elements in this chunk
+};
+
+__device__ __forceinline__ oe_chunk_view oe_view(const oe_dev_tensor* tensors, const oe_dev_chunk* chunks, uint32_t c,
+                                                 uint32_t chunk_elems) {
+    oe_dev_chunk ck = chunks[c];
+    oe_chunk_view v;
+    v.t = tensors + ck.tensor;
+    v.base = (uint64_t)ck.chunk * chunk_elems;
+    uint64_t left = v.t->numel - v.base;
+    v.n = left < chunk_elems ? (uint32_t)left : chunk_elems;
+    return v;
+}
+
+// ---------------------------------------------------------------------------------
+// AdamW
+// ---------------------------------------------------------------------------------
+struct oe_adamw_consts {
+    float b1, b2, omb1, omb2, eps, bc1, bc2, coef;
+};
+
+// One element of AdamW.Step's host loop (autograd/nn.go:522-527), g already the
+// stored gradient: g*coef rounds exactly like the in-place clip followed by a reload.
+__device__ __forceinline__ void oe_adamw_one(float& p, float g, float& m, float& v, const oe_adamw_consts& k,
+                                             float step, float one_minus_decay) {
+    g = __fmul_rn(g, k.coef);
+    float mi = __fadd_rn(__fmul_rn(k.b1, m), __fmul_rn(k.omb1, g));
+    float vi = __fadd_rn(__fmul_rn(k.b2, v), __fmul_rn(__fmul_rn(k.omb2, g), g));
+    m = mi;
+    v = vi;
+    float root = __fsqrt_rn(__fdiv_rn(vi, k.bc2));
+    float update = __fdiv_rn(__fmul_rn(step, __fdiv_rn(mi, k.bc1)), __fadd_rn(root, k.eps));
+    p = __fsub_rn(__fmul_rn(p, one_minus_decay), update);
+}
+
+template <int UNROLL>
+__device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ tensors,
+                                              const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+                                              uint32_t chunk_elems, const oe_adamw_args& a) {
+    oe_adamw_consts k;
+    k.b1 = a.beta1;
+    k.b2 = a.beta2;
+    k.omb1 = __fsub_rn(1.0f, a.beta1);
+    k.omb2 = __fsub_rn(1.0f, a.beta2);
+    k.eps = a.eps;
+    k.bc1 = a.bc1;
+    k.bc2 = a.bc2;
+    if (a.step_dev != 0) {
+        // Capture mode: the step counter lives on the device and was advanced by
+        // oe_step_increment; bias correction as on the host, in double
+        // (autograd/nn.go:493-494).
+        double t = (double)(*(const int32_t*)a.step_dev);
+        k.bc1 = (float)(1.0 - pow((double)a.beta1, t));
+        k.bc2 = (float)(1.0 - pow((double)a.beta2, t));
+    }
+    k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
+    const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
+    const bool zero_grad = (a.flags & OE_F_ZERO_GRAD) != 0;
+
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        const oe_dev_tensor* t = cv.t;
+        float* __restrict__ p = (float*)t->param + cv.base;
+        float* __restrict__ g = (float*)t->grad + cv.base;
+        float* __restrict__ m = (float*)t->state1 + cv.base;
+        float* __restrict__ v = (float*)t->state2 + cv.base;
+        uint16_t* __restrict__ sh = (want_shadow && t->shadow) ? (uint16_t*)t->shadow + cv.base : nullptr;
+        // Group scaling in fp32 exactly as AdamW.groupScale (autograd/nn.go:461-465).
+        const float step = __fmul_rn(a.lr, t->lr_scale);
+        const float omd = __fsub_rn(1.0f, __fmul_rn(step, t->weight_decay));
+        uint32_t done = 0;
+        if ((t->aligned & (OE_ALIGNED_BASE | OE_ALIGNED_STATE2)) == (OE_ALIGNED_BASE | OE_ALIGNED_STATE2)) {
+            const uint32_t nvec = cv.n >> 2;
+            float4* p4 = (float4*)p;
+            float4* g4 = (float4*)g;
+            float4* m4 = (float4*)m;
+            float4* v4 = (float4*)v;
+            for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += OE_THREADS * UNROLL) {
+                float4 P[UNROLL], G[UNROLL], M[UNROLL], V[UNROLL];
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) {
+                        G[u] = __ldcs(g4 + i);
+                        P[u] = __ldcs(p4 + i);
+                        M[u] = __ldcs(m4 + i);
+                        V[u] = __ldcs(v4 + i);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) {
+                        oe_adamw_one(P[u].x, G[u].x, M[u].x, V[u].x, k, step, omd);
+                        oe_adamw_one(P[u].y, G[u].y, M[u].y, V[u].y, k, step, omd);
+                        oe_adamw_one(P[u].z, G[u].z, M[u].z, V[u].z, k, step, omd);
+                        oe_adamw_one(P[u].w, G[u].w, M[u].w, V[u].w, k, step, omd);
+                        __stcs(p4 + i, P[u]);
+                        __stcs(m4 + i, M[u]);
+                        __stcs(v4 + i, V[u]);
+                        if (sh) {
+                            uint2 packed;
+                            packed.x = oe_bf16_rne(P[u].x) | (oe_bf16_rne(P[u].y) << 16);
+                            packed.y = oe_bf16_rne(P[u].z) | (oe_bf16_rne(P[u].w) << 16);
+                            __stcs((uint2*)sh + i, packed);
+                        }
+                        if (zero_grad) __stcs(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+                    }
+                }
+            }
+            done = nvec << 2;
+        }
+        // Scalar path: the tail of an aligned chunk (< 4 elements) or a whole chunk
+        // of a tensor whose pointers do not allow 128-bit accesses.
+        for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
+            float pi = p[i], mi = m[i], vi = v[i];
+            oe_adamw_one(pi, g[i], mi, vi, k, step, omd);
+            p[i] = pi;
+            m[i] = mi;
+            v[i] = vi;
+            if (sh) sh[i] = (uint16_t)oe_bf16_rne(pi);
+            if (zero_grad) g[i] = 0.0f;
+        }
+    }
+}
+
+// The update kernel is built in a few shapes (vectors in flight per thread x resident
+// CTAs per SM); the shim picks one per plan. All shapes compute identical results.
+#define OE_ADAMW_VARIANT(name, unroll, min_blocks)                                                         \
+    extern "C" __global__ void __launch_bounds__(OE_THREADS, min_blocks)                                   \
+    name(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks,               \
+         uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a) {                                       \
+        oe_adamw_body<unroll>(tensors, chunks, n_chunks, chunk_elems, a);                                  \
+    }
+OE_ADAMW_VARIANT(oe_adamw_fused, 2, 3)
+OE_ADAMW_VARIANT(oe_adamw_fused_u1, 1, 4)
+OE_ADAMW_VARIANT(oe_adamw_fused_u2b4, 2, 4)
+OE_ADAMW_VARIANT(oe_adamw_fused_u4, 4, 2)
+
+// Capture mode: one thread advances the device step counter before the update
+// (the reference's graph_adam_inc, autograd/cuda_kernels.go:595).
+extern "C" __global__ void oe_step_increment(int32_t* step) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) step[0] += 1;
+}
+
+// ---------------------------------------------------------------------------------
+// SGD (PyTorch semantics: coupled decay, momentum, dampening, Nesterov, maximize)
+// ---------------------------------------------------------------------------------
+struct oe_sgd_consts {
+    float momentum, one_minus_damp, coef;
+    bool nesterov, maximize;
+};
+
+// One element of SGD.Step's host loop (autograd/sgd.go:205-220).
+__device__ __forceinline__ void oe_sgd_one(float& p, float g, float& b, const oe_sgd_consts& k, float lr, float decay,
+                                           bool first) {
+    g = __fmul_rn(g, k.coef);
+    if (k.maximize) g = -g;
+    g = __fadd_rn(g, __fmul_rn(decay, p));
+    if (k.momentum > 0.0f) {
+        float nb = first ? g : __fadd_rn(__fmul_rn(k.momentum, b), __fmul_rn(k.one_minus_damp, g));
+        b = nb;
+        g = k.nesterov ? __fadd_rn(g, __fmul_rn(k.momentum, nb)) : nb;
+    }
+    p = __fsub_rn(p, __fmul_rn(lr, g));
+}
+
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+             uint32_t chunk_elems, oe_sgd_args a) {
+    oe_sgd_consts k;
+    k.momentum = a.momentum;
+    k.one_minus_damp = __fsub_rn(1.0f, a.dampening);
+    k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
+    k.nesterov = (a.flags & OE_F_NESTEROV) != 0;
+    k.maximize = (a.flags & OE_F_MAXIMIZE) != 0;
+    const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
+    const bool zero_grad = (a.flags & OE_F_ZERO_GRAD) != 0;
+
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        const oe_dev_tensor* t = cv.t;
+        float* __restrict__ p = (float*)t->param + cv.base;
+        float* __restrict__ g = (float*)t->grad + cv.base;
+        const bool has_buf = k.momentum > 0.0f && t->state1 != 0;
+        float* __restrict__ b = has_buf ? (float*)t->state1 + cv.base : nullptr;
+        // The per-tensor device flag says whether the momentum buffer holds a value
+        // yet (autograd/cuda_sgd.go:14); oe_sgd_mark sets it after this launch.
+        const bool first = has_buf && t->state2 != 0 ? (*(const float*)t->state2 == 0.0f) : true;
+        uint16_t* __restrict__ sh = (want_shadow && t->shadow) ? (uint16_t*)t->shadow + cv.base : nullptr;
+        // SGD.groupScale (autograd/sgd.go:127-130): the decay is not scaled by the rate.
+        const float lr = __fmul_rn(a.lr, t->lr_scale);
+        const float decay = t->weight_decay;
+        uint32_t done = 0;
+        if (t->aligned & OE_ALIGNED_BASE) {
+            const uint32_t nvec = cv.n >> 2;
+            float4* p4 = (float4*)p;
+            float4* g4 = (float4*)g;
+            float4* b4 = (float4*)b;
+            for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += OE_THREADS * OE_UNROLL) {
+                float4 P[OE_UNROLL], G[OE_UNROLL], B[OE_UNROLL];
+#pragma unroll
+                for (int u = 0; u < OE_UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) {
+                        G[u] = __ldcs(g4 + i);
+                        P[u] = __ldcs(p4 + i);
+                        B[u] = (has_buf && !first) ? __ldcs(b4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < OE_UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) {
+                        oe_sgd_one(P[u].x, G[u].x, B[u].x, k, lr, decay, first);
+                        oe_sgd_one(P[u].y, G[u].y, B[u].y, k, lr, decay, first);
+                        oe_sgd_one(P[u].z, G[u].z, B[u].z, k, lr, decay, first);
+                        oe_sgd_one(P[u].w, G[u].w, B[u].w, k, lr, decay, first);
+                        __stcs(p4 + i, P[u]);
+                        if (has_buf) __stcs(b4 + i, B[u]);
+                        if (sh) {
+                            uint2 packed;
+                            packed.x = oe_bf16_rne(P[u].x) | (oe_bf16_rne(P[u].y) << 16);
+                            packed.y = oe_bf16_rne(P[u].z) | (oe_bf16_rne(P[u].w) << 16);
+                            __stcs((uint2*)sh + i, packed);
+                        }
+                        if (zero_grad) __stcs(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+                    }
+                }
+            }
+            done = nvec << 2;
+        }
+        for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
+            float pi = p[i];
+            float bi = (has_buf && !first) ? b[i] : 0.0f;
+            oe_sgd_one(pi, g[i], bi, k, lr, decay, first);
+            p[i] = pi;
+            if (has_buf) b[i] = bi;
+            if (sh) sh[i] = (uint16_t)oe_bf16_rne(pi);
+            if (zero_grad) g[i] = 0.0f;
+        }
+    }
+}
+
+// After an SGD update: every tensor that took part now has an initialised momentum
+// buffer (the reference's sgd_mark, one launch per tensor; here one launch for all).
+extern "C" __global__ void oe_sgd_mark(const oe_dev_tensor* __restrict__ tensors, uint32_t n_tensors) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n_tensors && tensors[i].state1 != 0 && tensors[i].state2 != 0) *(float*)tensors[i].state2 = 1.0f;
+}
+
+// ---------------------------------------------------------------------------------
+// gradient norm: sum of squares in double, two levels, deterministic
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ double oe_block_sum(double x, double* warp_sums) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) x += __shfl_down_sync(0xffffffffu, x, off);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) warp_sums[warp] = x;
+    __syncthreads();
+    double total = 0.0;
+    if (threadIdx.x == 0) {
+#pragma unroll
+        for (int w = 0; w < OE_THREADS / 32; w++) total += warp_sums[w];
+    }
+    __syncthreads();
+    return total;  // valid in thread 0
+}
+
+// Level 1: every CTA accumulates its chunks in double (the host oracle sums in
+// float64 too, autograd/nn.go:319-324) and writes one partial. Level 2: the CTA that
+// arrives last adds the partials in index order, so the result depends only on the
+// grid size, never on timing; it stores sum, norm = (float)sqrt(sum) and re-arms the
+// ticket, so the launch needs no memset and can be captured in a graph.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+              uint32_t chunk_elems, oe_dev_norm* out, double* partials, uint32_t flags) {
+    __shared__ double warp_sums[OE_THREADS / 32];
+    __shared__ uint32_t is_last;
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        const float* __restrict__ g = (const float*)cv.t->grad + cv.base;
+        uint32_t done = 0;
+        if (cv.t->aligned & OE_ALIGNED_BASE) {
+            const uint32_t nvec = cv.n >> 2;
+            const float4* g4 = (const float4*)g;
+            for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += OE_THREADS * OE_NORM_UNROLL) {
+                float4 G[OE_NORM_UNROLL];
+#pragma unroll
+                for (int u = 0; u < OE_NORM_UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    G[u] = i < nvec ? __ldcs(g4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+#pragma unroll
+                for (int u = 0; u < OE_NORM_UNROLL; u++) {
+                    double x = (double)G[u].x, y = (double)G[u].y, z = (double)G[u].z, w = (double)G[u].w;
+                    a0 = fma(x, x, a0);
+                    a1 = fma(y, y, a1);
+                    a2 = fma(z, z, a2);
+                    a3 = fma(w, w, a3);
+                }
+            }
+            done = nvec << 2;
+        }
+        for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
+            double x = (double)g[i];
+            a0 = fma(x, x, a0);
+        }
+    }
+    double block = oe_block_sum((a0 + a1) + (a2 + a3), warp_sums);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = block;
+        __threadfence();
+        uint32_t ticket = atomicAdd(&out->ticket, 1u);
+        is_last = (ticket == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    double s = 0.0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += OE_THREADS) s += __ldcg(partials + i);
+    double total = oe_block_sum(s, warp_sums);
+    if (threadIdx.x == 0) {
+        out->sumsq = total;
+        if (!(flags & OE_F_PARTIAL_ONLY)) out->norm = (float)sqrt(total);
+        out->ticket = 0u;
+    }
+}
+
+// norm = (float)sqrt(sumsq) for a sum that was completed elsewhere (for instance by
+// an all-reduce over the ranks of a sharded step).
+extern "C" __global__ void oe_norm_finalize(oe_dev_norm* out) {
+    if (blockIdx.x == 0 && threadIdx.x == 0) out->norm = (float)sqrt(out->sumsq);
+}
+
+// In-place clip: g *= coefficient (autograd/nn.go:327-333, autograd/cuda_kernels.go:676).
+// A coefficient of exactly 1 writes nothing.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_scale_grads(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+               uint32_t chunk_elems, const oe_dev_norm* norm, float max_norm, uint32_t flags) {
+    const float coef = oe_clip_coefficient(norm, max_norm, flags);
+    if (coef == 1.0f) return;
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        float* __restrict__ g = (float*)cv.t->grad + cv.base;
+        uint32_t done = 0;
+        if (cv.t->aligned & OE_ALIGNED_BASE) {
+            const uint32_t nvec = cv.n >> 2;
+            float4* g4 = (float4*)g;
+            for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += OE_THREADS * OE_NORM_UNROLL) {
+                float4 G[OE_NORM_UNROLL];
+#pragma unroll
+                for (int u = 0; u < OE_NORM_UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) G[u] = __ldcs(g4 + i);
+                }
+#pragma unroll
+                for (int u = 0; u < OE_NORM_UNROLL; u++) {
+                    uint32_t i = i0 + u * OE_THREADS;
+                    if (i < nvec) {
+                        G[u].x = __fmul_rn(G[u].x, coef);
+                        G[u].y = __fmul_rn(G[u].y, coef);
+                        G[u].z = __fmul_rn(G[u].z, coef);
+                        G[u].w = __fmul_rn(G[u].w, coef);
+                        __stcs(g4 + i, G[u]);
+                    }
+                }
+            }
+            done = nvec << 2;
+        }
+        for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) g[i] = __fmul_rn(g[i], coef);
+    }
+}
+
+// Zero every present gradient in one launch (AdamW.ZeroGrad keeps the buffers and
+// memsets each of them, autograd/nn.go:533-537, autograd/tensor.go:407-420).
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_zero_grads(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+              uint32_t chunk_elems) {
+    for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        float* __restrict__ g = (float*)cv.t->grad + cv.base;
+        uint32_t done = 0;
+        if (cv.t->aligned & OE_ALIGNED_BASE) {
+            const uint32_t nvec = cv.n >> 2;
+            float4* g4 = (float4*)g;
+            for (uint32_t i = threadIdx.x; i < nvec; i += OE_THREADS) __stcs(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
+            done = nvec << 2;
+        }
+        for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) g[i] = 0.0f;
+    }
+}
+
+// ---------------------------------------------------------------------------------
+// stand-alone fp32 -> bf16 cast (the reference's f32_to_bf16, one tensor per call)
+// ---------------------------------------------------------------------------------
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t n) {
+    const uint64_t tid = (uint64_t)blockIdx.x * OE_THREADS + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * OE_THREADS;
+    const bool aligned = (((uint64_t)src & 15u) == 0) && (((uint64_t)dst & 7u) == 0);
+    uint64_t done = 0;
+    if (aligned) {
+        const uint64_t nvec = n >> 2;
+        const float4* s4 = (const float4*)src;
+        uint2* d2 = (uint2*)dst;
+        for (uint64_t i = tid; i < nvec; i += stride) {
+            float4 x = __ldcs(s4 + i);
+            uint2 packed;
+            packed.x = oe_bf16_rne(x.x) | (oe_bf16_rne(x.y) << 16);
+            packed.y = oe_bf16_rne(x.z) | (oe_bf16_rne(x.w) << 16);
+            __stcs(d2 + i, packed);
+        }
+        done = nvec << 2;
+    }
+    for (uint64_t i = done + tid; i < n; i += stride) dst[i] = (uint16_t)oe_bf16_rne(src[i]);
+}

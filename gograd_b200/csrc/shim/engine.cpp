@@ -1,0 +1,837 @@
+// Host side of liboptengine.so: plans (device tables), launches and the small set of
+// driver calls a host without a CUDA binding needs. Everything goes through the CUDA
+// driver API bound at run time (driver.h); the kernels come from an sm_100a cubin
+// embedded in the library (cubin_blob.S).
+#include <math.h>
+#include <string.h>
+
+#include <map>
+#include <mutex>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "../../../include/optengine.h"
+#include "driver.h"
+#include "oe_table.h"
+
+extern "C" const unsigned char oe_cubin_start[];
+extern "C" const unsigned char oe_cubin_end[];
+
+namespace {
+
+constexpr uint32_t kThreads = 256;             // must equal OE_THREADS of the kernels
+constexpr uint32_t kDefaultChunkElems = 8192;  // 32 KB of one fp32 stream per work unit
+constexpr int kMaxDevices = 64;
+
+thread_local std::string t_error;
+
+int fail(int code, const std::string& message) {
+    t_error = message;
+    return code;
+}
+
+int fail_cu(const oe_driver* d, CUresult r, const char* op) {
+    const char* name = nullptr;
+    const char* text = nullptr;
+    d->cuGetErrorName_(r, &name);
+    d->cuGetErrorString_(r, &text);
+    t_error = std::string(op) + ": " + (name ? name : "CUDA_ERROR") + " (" + (text ? text : "?") + ")";
+    return (int)r;
+}
+
+#define OE_CU(call, op)                                       \
+    do {                                                      \
+        CUresult oe_r_ = (call);                              \
+        if (oe_r_ != CUDA_SUCCESS) return fail_cu(d, oe_r_, op); \
+    } while (0)
+
+struct KernelSet {
+    CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2b4, u4
+    CUfunction step_increment = nullptr, sgd = nullptr, sgd_mark = nullptr, sumsq = nullptr, norm_finalize = nullptr,
+               scale = nullptr, zero = nullptr, cast = nullptr;
+};
+const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2b4", "oe_adamw_fused_u4"};
+const char* const kVariantKeys[4] = {"", "u1", "u2b4", "u4"};
+
+struct DeviceCtx {
+    bool ready = false;
+    int ordinal = -1;
+    CUdevice dev = 0;
+    CUcontext ctx = nullptr;
+    CUmodule module = nullptr;
+    int sm_count = 0;
+    KernelSet k;
+    int occ_adamw[4] = {0, 0, 0, 0};
+    int occ_sgd = 0, occ_sumsq = 0, occ_scale = 0, occ_zero = 0, occ_cast = 0;
+};
+
+std::mutex g_mu;
+DeviceCtx g_dev[kMaxDevices];
+std::map<std::string, int64_t> g_launches;
+
+// Pushes the device's primary context for the lifetime of the guard and pops it
+// again, so the caller's current context is never changed behind its back.
+struct CtxGuard {
+    const oe_driver* d;
+    bool pushed = false;
+    CtxGuard(const oe_driver* drv, CUcontext ctx) : d(drv) { pushed = d->cuCtxPushCurrent_(ctx) == CUDA_SUCCESS; }
+    ~CtxGuard() {
+        if (pushed) {
+            CUcontext old;
+            d->cuCtxPopCurrent_(&old);
+        }
+    }
+};
+
+const oe_driver* driver_or_fail(int* rc) {
+    const char* why = nullptr;
+    const oe_driver* d = oe_driver_get(&why);
+    if (!d) *rc = fail(OE_ERR_NO_DRIVER, why ? why : "CUDA driver unavailable");
+    return d;
+}
+
+DeviceCtx* device_or_fail(int device, int* rc) {
+    if (device < 0 || device >= kMaxDevices) {
+        *rc = fail(OE_ERR_INVALID, "device ordinal out of range");
+        return nullptr;
+    }
+    DeviceCtx* dc = &g_dev[device];
+    if (!dc->ready) {
+        *rc = fail(OE_ERR_NOT_INIT, "oe_init was not called for device " + std::to_string(device));
+        return nullptr;
+    }
+    return dc;
+}
+
+void count_launch(const char* name) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_launches[name] += 1;
+}
+
+int launch(const oe_driver* d, CUfunction f, const char* name, uint32_t grid, uint32_t block, CUstream stream,
+           void** args) {
+    OE_CU(d->cuLaunchKernel_(f, grid, 1, 1, block, 1, 1, 0, stream, args, nullptr), name);
+    count_launch(name);
+    return 0;
+}
+
+bool finite_nonneg(float x) { return isfinite(x) && x >= 0.0f; }
+
+}  // namespace
+
+// -------------------------------------------------------------------------------------
+// plan
+// -------------------------------------------------------------------------------------
+struct oe_plan {
+    DeviceCtx* dc = nullptr;
+    uint32_t chunk_elems = kDefaultChunkElems;
+    int variant = 0;
+    std::vector<oe_tensor_desc> descs;  // every parameter, with or without a gradient
+    uint32_t n_active = 0;              // parameters with a gradient = rows of the device tensor table
+    uint64_t n_chunks = 0;
+    uint64_t active_elems = 0;
+    bool all_adamw_state = true;        // every active tensor has state1 and state2
+    // device side
+    CUdeviceptr d_tensors = 0, d_chunks = 0, d_norm = 0, d_partials = 0;
+    size_t cap_tensors = 0, cap_chunks = 0;  // capacities in entries
+    uint32_t max_grid = 0;
+    // page-locked staging for the tables, and the event that guards its reuse
+    void* h_stage = nullptr;
+    size_t h_stage_bytes = 0;
+    CUevent staged = nullptr;
+    bool staged_pending = false;
+    int64_t uploads = 0;
+};
+
+namespace {
+
+int validate_descs(const oe_tensor_desc* t, uint32_t n, uint32_t chunk_elems) {
+    if (n > 0 && t == nullptr) return fail(OE_ERR_INVALID, "tensor descriptors are NULL");
+    for (uint32_t i = 0; i < n; i++) {
+        const oe_tensor_desc& x = t[i];
+        std::string at = "tensor " + std::to_string(i) + ": ";
+        if (x.numel == 0) return fail(OE_ERR_INVALID, at + "numel is 0");
+        if (x.param == 0) return fail(OE_ERR_INVALID, at + "param address is 0");
+        if ((x.param | x.grad | x.state1 | x.state2) & 3u) return fail(OE_ERR_INVALID, at + "fp32 address not 4-byte aligned");
+        if (x.shadow & 1u) return fail(OE_ERR_INVALID, at + "bf16 shadow address not 2-byte aligned");
+        if (!finite_nonneg(x.lr_scale)) return fail(OE_ERR_INVALID, at + "invalid parameter group learning-rate scale");
+        if (!finite_nonneg(x.weight_decay)) return fail(OE_ERR_INVALID, at + "invalid parameter group weight decay");
+        if ((x.numel + chunk_elems - 1) / chunk_elems > 0xffffffffull) return fail(OE_ERR_LIMIT, at + "too many chunks");
+    }
+    return 0;
+}
+
+// Fills the staging buffer with the tensor table followed by the chunk table.
+void build_tables(oe_plan* p, oe_dev_tensor* tt, oe_dev_chunk* ck) {
+    uint32_t row = 0;
+    uint64_t c = 0;
+    for (const oe_tensor_desc& x : p->descs) {
+        if (x.grad == 0) continue;
+        oe_dev_tensor& o = tt[row];
+        o.param = x.param;
+        o.grad = x.grad;
+        o.state1 = x.state1;
+        o.state2 = x.state2;
+        o.shadow = x.shadow;
+        o.numel = x.numel;
+        o.lr_scale = x.lr_scale == 0.0f ? 1.0f : x.lr_scale;
+        o.weight_decay = x.weight_decay;
+        // 128-bit path: fp32 streams 16-byte aligned, the bf16 stream 8-byte aligned.
+        // Bit 0 covers param, grad, state1 and the shadow; bit 1 adds state2, which is
+        // a full-size stream for AdamW (v) but a one-float flag for SGD.
+        bool aligned = ((x.param | x.grad | x.state1) & 15u) == 0 && (x.shadow & 7u) == 0;
+        o.aligned = (aligned ? OE_ALIGNED_BASE : 0u) | ((aligned && (x.state2 & 15u) == 0) ? OE_ALIGNED_STATE2 : 0u);
+        o.reserved = 0;
+        uint64_t nck = (x.numel + p->chunk_elems - 1) / p->chunk_elems;
+        for (uint64_t j = 0; j < nck; j++) {
+            ck[c].tensor = row;
+            ck[c].chunk = (uint32_t)j;
+            c++;
+        }
+        row++;
+    }
+}
+
+void count_active(oe_plan* p) {
+    p->n_active = 0;
+    p->n_chunks = 0;
+    p->active_elems = 0;
+    p->all_adamw_state = true;
+    for (const oe_tensor_desc& x : p->descs) {
+        if (x.grad == 0) continue;
+        p->n_active++;
+        p->n_chunks += (x.numel + p->chunk_elems - 1) / p->chunk_elems;
+        p->active_elems += x.numel;
+        if (x.state1 == 0 || x.state2 == 0) p->all_adamw_state = false;
+    }
+}
+
+// Makes room for the current tables on the device and in the staging buffer. Only
+// called outside stream capture paths that must not allocate: capacities never shrink.
+int ensure_capacity(const oe_driver* d, oe_plan* p) {
+    size_t need_t = p->n_active ? p->n_active : 1, need_c = p->n_chunks ? p->n_chunks : 1;
+    if (need_t > p->cap_tensors) {
+        if (p->d_tensors) OE_CU(d->cuMemFree_(p->d_tensors), "cuMemFree(tensor table)");
+        p->d_tensors = 0;
+        size_t cap = need_t + need_t / 4 + 8;
+        OE_CU(d->cuMemAlloc_(&p->d_tensors, cap * sizeof(oe_dev_tensor)), "cuMemAlloc(tensor table)");
+        p->cap_tensors = cap;
+    }
+    if (need_c > p->cap_chunks) {
+        if (p->d_chunks) OE_CU(d->cuMemFree_(p->d_chunks), "cuMemFree(chunk table)");
+        p->d_chunks = 0;
+        size_t cap = need_c + need_c / 4 + 64;
+        OE_CU(d->cuMemAlloc_(&p->d_chunks, cap * sizeof(oe_dev_chunk)), "cuMemAlloc(chunk table)");
+        p->cap_chunks = cap;
+    }
+    size_t bytes = p->cap_tensors * sizeof(oe_dev_tensor) + p->cap_chunks * sizeof(oe_dev_chunk);
+    if (bytes > p->h_stage_bytes) {
+        if (p->staged_pending) {
+            OE_CU(d->cuEventSynchronize_(p->staged), "cuEventSynchronize(table upload)");
+            p->staged_pending = false;
+        }
+        if (p->h_stage) OE_CU(d->cuMemFreeHost_(p->h_stage), "cuMemFreeHost(staging)");
+        p->h_stage = nullptr;
+        OE_CU(d->cuMemAllocHost_(&p->h_stage, bytes), "cuMemAllocHost(staging)");
+        p->h_stage_bytes = bytes;
+    }
+    return 0;
+}
+
+int upload_tables(const oe_driver* d, oe_plan* p, CUstream stream) {
+    int rc = ensure_capacity(d, p);
+    if (rc) return rc;
+    if (p->staged_pending) {
+        // The previous upload may still be reading the staging buffer.
+        OE_CU(d->cuEventSynchronize_(p->staged), "cuEventSynchronize(table upload)");
+        p->staged_pending = false;
+    }
+    oe_dev_tensor* tt = (oe_dev_tensor*)p->h_stage;
+    oe_dev_chunk* ck = (oe_dev_chunk*)((char*)p->h_stage + p->cap_tensors * sizeof(oe_dev_tensor));
+    build_tables(p, tt, ck);
+    if (p->n_active) {
+        OE_CU(d->cuMemcpyHtoDAsync_(p->d_tensors, tt, p->n_active * sizeof(oe_dev_tensor), stream),
+              "cuMemcpyHtoDAsync(tensor table)");
+        OE_CU(d->cuMemcpyHtoDAsync_(p->d_chunks, ck, p->n_chunks * sizeof(oe_dev_chunk), stream),
+              "cuMemcpyHtoDAsync(chunk table)");
+        OE_CU(d->cuEventRecord_(p->staged, stream), "cuEventRecord(table upload)");
+        p->staged_pending = true;
+    }
+    p->uploads++;
+    return 0;
+}
+
+uint32_t grid_for(const oe_plan* p, int occupancy) {
+    uint64_t persistent = (uint64_t)p->dc->sm_count * (uint64_t)(occupancy > 0 ? occupancy : 1);
+    uint64_t g = p->n_chunks < persistent ? p->n_chunks : persistent;
+    if (g == 0) g = 1;
+    if (g > p->max_grid) g = p->max_grid;
+    return (uint32_t)g;
+}
+
+void destroy_plan(const oe_driver* d, oe_plan* p) {
+    if (p->staged_pending) d->cuEventSynchronize_(p->staged);
+    if (p->staged) d->cuEventDestroy_(p->staged);
+    if (p->h_stage) d->cuMemFreeHost_(p->h_stage);
+    if (p->d_tensors) d->cuMemFree_(p->d_tensors);
+    if (p->d_chunks) d->cuMemFree_(p->d_chunks);
+    if (p->d_norm) d->cuMemFree_(p->d_norm);
+    if (p->d_partials) d->cuMemFree_(p->d_partials);
+    delete p;
+}
+
+bool same_descs(const std::vector<oe_tensor_desc>& a, const oe_tensor_desc* b, uint32_t n) {
+    if (a.size() != n) return false;
+    return n == 0 || memcmp(a.data(), b, (size_t)n * sizeof(oe_tensor_desc)) == 0;
+}
+
+}  // namespace
+
+// -------------------------------------------------------------------------------------
+// library
+// -------------------------------------------------------------------------------------
+extern "C" int oe_abi_version(void) { return OE_ABI_VERSION; }
+
+extern "C" const char* oe_last_error(void) { return t_error.c_str(); }
+
+extern "C" int oe_init(int device) {
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if (device < 0 || device >= kMaxDevices) return fail(OE_ERR_INVALID, "device ordinal out of range");
+    std::lock_guard<std::mutex> lock(g_mu);
+    DeviceCtx* dc = &g_dev[device];
+    if (dc->ready) return 0;
+    int count = 0;
+    OE_CU(d->cuDeviceGetCount_(&count), "cuDeviceGetCount");
+    if (device >= count) return fail(OE_ERR_INVALID, "no such CUDA device: " + std::to_string(device));
+    OE_CU(d->cuDeviceGet_(&dc->dev, device), "cuDeviceGet");
+    int major = 0, minor = 0;
+    OE_CU(d->cuDeviceGetAttribute_(&major, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MAJOR, dc->dev), "cuDeviceGetAttribute");
+    OE_CU(d->cuDeviceGetAttribute_(&minor, CU_DEVICE_ATTRIBUTE_COMPUTE_CAPABILITY_MINOR, dc->dev), "cuDeviceGetAttribute");
+    if (major != 10 || minor != 0)
+        return fail(OE_ERR_ARCH, "device " + std::to_string(device) + " is sm_" + std::to_string(major) +
+                                     std::to_string(minor) + "; this library carries sm_100a code only");
+    OE_CU(d->cuDeviceGetAttribute_(&dc->sm_count, CU_DEVICE_ATTRIBUTE_MULTIPROCESSOR_COUNT, dc->dev),
+          "cuDeviceGetAttribute");
+    OE_CU(d->cuDevicePrimaryCtxRetain_(&dc->ctx, dc->dev), "cuDevicePrimaryCtxRetain");
+    CtxGuard guard(d, dc->ctx);
+    CUresult r = d->cuModuleLoadData_(&dc->module, oe_cubin_start);
+    if (r != CUDA_SUCCESS) {
+        d->cuDevicePrimaryCtxRelease_(dc->dev);
+        return fail_cu(d, r, "cuModuleLoadData(embedded sm_100a cubin)");
+    }
+    struct {
+        CUfunction* f;
+        const char* name;
+        int* occ;
+    } table[] = {
+        {&dc->k.adamw[0], kAdamwNames[0], &dc->occ_adamw[0]}, {&dc->k.adamw[1], kAdamwNames[1], &dc->occ_adamw[1]},
+        {&dc->k.adamw[2], kAdamwNames[2], &dc->occ_adamw[2]}, {&dc->k.adamw[3], kAdamwNames[3], &dc->occ_adamw[3]},
+        {&dc->k.step_increment, "oe_step_increment", nullptr}, {&dc->k.sgd, "oe_sgd_fused", &dc->occ_sgd},
+        {&dc->k.sgd_mark, "oe_sgd_mark", nullptr},             {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
+        {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
+        {&dc->k.zero, "oe_zero_grads", &dc->occ_zero},         {&dc->k.cast, "oe_cast_bf16", &dc->occ_cast},
+    };
+    for (auto& e : table) {
+        r = d->cuModuleGetFunction_(e.f, dc->module, e.name);
+        if (r == CUDA_SUCCESS && e.occ)
+            r = d->cuOccupancyMaxActiveBlocksPerMultiprocessor_(e.occ, *e.f, (int)kThreads, 0);
+        if (r != CUDA_SUCCESS) {
+            d->cuModuleUnload_(dc->module);
+            d->cuDevicePrimaryCtxRelease_(dc->dev);
+            dc->module = nullptr;
+            return fail_cu(d, r, e.name);
+        }
+    }
+    dc->ordinal = device;
+    dc->ready = true;
+    return 0;
+}
+
+extern "C" int oe_shutdown(void) {
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    std::lock_guard<std::mutex> lock(g_mu);
+    for (DeviceCtx& dc : g_dev) {
+        if (!dc.ready) continue;
+        {
+            CtxGuard guard(d, dc.ctx);
+            d->cuModuleUnload_(dc.module);
+        }
+        d->cuDevicePrimaryCtxRelease_(dc.dev);
+        dc = DeviceCtx();
+    }
+    return 0;
+}
+
+extern "C" int oe_device_sm_count(int device) {
+    int rc = 0;
+    DeviceCtx* dc = device_or_fail(device, &rc);
+    return dc ? dc->sm_count : rc;
+}
+
+// -------------------------------------------------------------------------------------
+// plans
+// -------------------------------------------------------------------------------------
+extern "C" int oe_plan_create(int device, const oe_tensor_desc* tensors, uint32_t n_tensors, uint32_t chunk_elems,
+                              oe_plan** out) {
+    if (!out) return fail(OE_ERR_INVALID, "out is NULL");
+    *out = nullptr;
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    DeviceCtx* dc = device_or_fail(device, &rc);
+    if (!dc) return rc;
+    if (chunk_elems == 0) chunk_elems = kDefaultChunkElems;
+    if (chunk_elems % 1024 != 0 || chunk_elems > (1u << 24))
+        return fail(OE_ERR_INVALID, "chunk_elems must be a multiple of 1024, at most 2^24");
+    if ((rc = validate_descs(tensors, n_tensors, chunk_elems)) != 0) return rc;
+    oe_plan* p = new (std::nothrow) oe_plan();
+    if (!p) return fail(OE_ERR_INVALID, "out of host memory");
+    p->dc = dc;
+    p->chunk_elems = chunk_elems;
+    p->descs.assign(tensors, tensors + n_tensors);
+    count_active(p);
+    CtxGuard guard(d, dc->ctx);
+    int occ_max = dc->occ_sumsq;
+    for (int o : dc->occ_adamw) occ_max = o > occ_max ? o : occ_max;
+    for (int o : {dc->occ_sgd, dc->occ_scale, dc->occ_zero}) occ_max = o > occ_max ? o : occ_max;
+    p->max_grid = (uint32_t)dc->sm_count * (uint32_t)(occ_max > 0 ? occ_max : 1);
+    CUresult r = d->cuMemAlloc_(&p->d_norm, sizeof(oe_dev_norm));
+    if (r == CUDA_SUCCESS) r = d->cuMemAlloc_(&p->d_partials, (size_t)p->max_grid * sizeof(double));
+    if (r == CUDA_SUCCESS) r = d->cuEventCreate_(&p->staged, CU_EVENT_DISABLE_TIMING);
+    if (r == CUDA_SUCCESS) r = d->cuMemsetD8Async_(p->d_norm, 0, sizeof(oe_dev_norm), nullptr);
+    if (r != CUDA_SUCCESS) {
+        rc = fail_cu(d, r, "oe_plan_create(allocate)");
+        destroy_plan(d, p);
+        return rc;
+    }
+    rc = upload_tables(d, p, nullptr);
+    if (rc == 0) {
+        r = d->cuStreamSynchronize_(nullptr);
+        if (r != CUDA_SUCCESS) rc = fail_cu(d, r, "cuStreamSynchronize");
+        p->staged_pending = false;
+    }
+    if (rc) {
+        std::string keep = t_error;
+        destroy_plan(d, p);
+        t_error = keep;
+        return rc;
+    }
+    *out = p;
+    return 0;
+}
+
+extern "C" int oe_plan_update(oe_plan* plan, const oe_tensor_desc* tensors, uint32_t n_tensors, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if (same_descs(plan->descs, tensors, n_tensors)) return 0;
+    if ((rc = validate_descs(tensors, n_tensors, plan->chunk_elems)) != 0) return rc;
+    plan->descs.assign(tensors, tensors + n_tensors);
+    count_active(plan);
+    CtxGuard guard(d, plan->dc->ctx);
+    return upload_tables(d, plan, (CUstream)stream);
+}
+
+extern "C" int oe_plan_destroy(oe_plan* plan) {
+    if (!plan) return 0;
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    destroy_plan(d, plan);
+    return 0;
+}
+
+extern "C" int64_t oe_plan_info(const oe_plan* plan, int what) {
+    if (!plan) return -1;
+    switch (what) {
+        case 0: return plan->n_active;
+        case 1: return (int64_t)plan->n_chunks;
+        case 2: return (int64_t)plan->active_elems;
+        case 3: return grid_for(plan, plan->dc->occ_adamw[plan->variant]);
+        case 4: return grid_for(plan, plan->dc->occ_sumsq);
+        case 5: return plan->chunk_elems;
+        case 6: return plan->uploads;
+        default: return -1;
+    }
+}
+
+extern "C" uint64_t oe_plan_norm_address(const oe_plan* plan) { return plan ? (uint64_t)plan->d_norm : 0; }
+
+extern "C" int oe_plan_set_variant(oe_plan* plan, const char* variant) {
+    if (!plan || !variant) return fail(OE_ERR_INVALID, "plan or variant is NULL");
+    for (int i = 0; i < 4; i++) {
+        if (strcmp(variant, kVariantKeys[i]) == 0) {
+            plan->variant = i;
+            return 0;
+        }
+    }
+    return fail(OE_ERR_INVALID, std::string("unknown update-kernel variant: ") + variant);
+}
+
+// -------------------------------------------------------------------------------------
+// norm and clip
+// -------------------------------------------------------------------------------------
+namespace {
+int launch_sumsq(const oe_driver* d, oe_plan* p, uint32_t flags, CUstream stream) {
+    uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
+    void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &p->d_norm, &p->d_partials, &flags};
+    return launch(d, p->dc->k.sumsq, "oe_grad_sumsq", grid_for(p, p->dc->occ_sumsq), kThreads, stream, args);
+}
+
+int check_chunk_count(const oe_plan* p) {
+    if (p->n_chunks > 0xffffffffull) return fail(OE_ERR_LIMIT, "plan has more than 2^32-1 chunks; use a larger chunk_elems");
+    return 0;
+}
+}  // namespace
+
+extern "C" int oe_grad_norm(oe_plan* plan, uint32_t flags, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    if (flags & ~OE_PARTIAL_ONLY) return fail(OE_ERR_INVALID, "oe_grad_norm: unknown flag");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = check_chunk_count(plan)) != 0) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_sumsq(d, plan, flags, (CUstream)stream);
+}
+
+extern "C" int oe_norm_finalize(oe_plan* plan, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    void* args[] = {&plan->d_norm};
+    return launch(d, plan->dc->k.norm_finalize, "oe_norm_finalize", 1, 32, (CUstream)stream, args);
+}
+
+extern "C" int oe_clip_grad_norm(oe_plan* plan, const float* max_norm, uint32_t flags, uint64_t stream) {
+    if (!plan || !max_norm) return fail(OE_ERR_INVALID, "plan or max_norm is NULL");
+    if (flags & ~OE_CLIP_DEVFORM) return fail(OE_ERR_INVALID, "oe_clip_grad_norm: unknown flag");
+    if (isnan(*max_norm)) return fail(OE_ERR_INVALID, "max_norm is NaN");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = check_chunk_count(plan)) != 0) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    if ((rc = launch_sumsq(d, plan, 0, (CUstream)stream)) != 0) return rc;
+    if (!(*max_norm > 0.0f) || plan->n_chunks == 0) return 0;  // norm only (autograd/cuda_clip.go:130)
+    uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
+    float mx = *max_norm;
+    void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &plan->d_norm, &mx, &flags};
+    return launch(d, plan->dc->k.scale, "oe_scale_grads", grid_for(plan, plan->dc->occ_scale), kThreads,
+                  (CUstream)stream, args);
+}
+
+extern "C" int oe_read_norm(oe_plan* plan, float* norm_out, double* sumsq_out, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    oe_dev_norm rec;
+    OE_CU(d->cuMemcpyDtoHAsync_(&rec, plan->d_norm, sizeof(rec), (CUstream)stream), "cuMemcpyDtoHAsync(norm)");
+    OE_CU(d->cuStreamSynchronize_((CUstream)stream), "cuStreamSynchronize");
+    if (norm_out) *norm_out = rec.norm;
+    if (sumsq_out) *sumsq_out = rec.sumsq;
+    return 0;
+}
+
+// -------------------------------------------------------------------------------------
+// updates
+// -------------------------------------------------------------------------------------
+namespace {
+int validate_adamw(const oe_plan* p, const oe_adamw_hparams* hp) {
+    if (!hp) return fail(OE_ERR_INVALID, "hyper-parameters are NULL");
+    if (!finite_nonneg(hp->lr)) return fail(OE_ERR_INVALID, "invalid learning rate");
+    if (!(hp->beta1 >= 0.0f && hp->beta1 < 1.0f) || !(hp->beta2 >= 0.0f && hp->beta2 < 1.0f) || !(hp->eps > 0.0f) ||
+        !isfinite(hp->eps))
+        return fail(OE_ERR_INVALID, "invalid optimizer configuration");
+    if (hp->step_dev == 0 && (!(hp->bc1 > 0.0f) || !(hp->bc2 > 0.0f) || !isfinite(hp->bc1) || !isfinite(hp->bc2)))
+        return fail(OE_ERR_INVALID, "bias corrections must be positive and finite (step >= 1)");
+    if (hp->step_dev & 3u) return fail(OE_ERR_INVALID, "step_dev not 4-byte aligned");
+    if (isnan(hp->max_norm)) return fail(OE_ERR_INVALID, "max_norm is NaN");
+    if (hp->flags & ~(OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD))
+        return fail(OE_ERR_INVALID, "oe_adamw_step: unknown flag");
+    if (!p->all_adamw_state) return fail(OE_ERR_INVALID, "AdamW needs m (state1) and v (state2) for every parameter with a gradient");
+    return check_chunk_count(p);
+}
+
+int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUstream stream) {
+    if (hp->step_dev) {
+        uint64_t sd = hp->step_dev;
+        void* inc_args[] = {&sd};
+        int rc = launch(d, p->dc->k.step_increment, "oe_step_increment", 1, 32, stream, inc_args);
+        if (rc) return rc;
+    }
+    if (p->n_chunks == 0) return 0;
+    oe_adamw_args a;
+    memset(&a, 0, sizeof(a));
+    a.lr = hp->lr;
+    a.beta1 = hp->beta1;
+    a.beta2 = hp->beta2;
+    a.eps = hp->eps;
+    a.bc1 = hp->bc1;
+    a.bc2 = hp->bc2;
+    a.max_norm = hp->max_norm;
+    a.flags = hp->flags;
+    a.norm = hp->max_norm > 0.0f ? (uint64_t)p->d_norm : 0;
+    a.step_dev = hp->step_dev;
+    uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
+    void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &a};
+    return launch(d, p->dc->k.adamw[p->variant], kAdamwNames[p->variant], grid_for(p, p->dc->occ_adamw[p->variant]),
+                  kThreads, stream, args);
+}
+}  // namespace
+
+extern "C" int oe_adamw_step(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = validate_adamw(plan, hp)) != 0) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_adamw(d, plan, hp, (CUstream)stream);
+}
+
+extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream) {
+    if (!plan || !hp) return fail(OE_ERR_INVALID, "plan or hyper-parameters are NULL");
+    // SGDOptions.validate (autograd/sgd.go:21-31)
+    for (float v : {hp->lr, hp->momentum, hp->dampening})
+        if (!finite_nonneg(v)) return fail(OE_ERR_INVALID, "invalid SGD configuration");
+    if ((hp->flags & OE_NESTEROV) && (!(hp->momentum > 0.0f) || hp->dampening != 0.0f))
+        return fail(OE_ERR_INVALID, "Nesterov needs positive momentum and zero dampening");
+    if (isnan(hp->max_norm)) return fail(OE_ERR_INVALID, "max_norm is NaN");
+    if (hp->flags & ~(OE_NESTEROV | OE_MAXIMIZE | OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD))
+        return fail(OE_ERR_INVALID, "oe_sgd_step: unknown flag");
+    if (hp->momentum > 0.0f) {
+        for (const oe_tensor_desc& x : plan->descs)
+            if (x.grad != 0 && (x.state1 == 0 || x.state2 == 0))
+                return fail(OE_ERR_INVALID, "incomplete SGD device storage: momentum needs a buffer and a flag per parameter");
+    }
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = check_chunk_count(plan)) != 0) return rc;
+    if (plan->n_chunks == 0) return 0;
+    CtxGuard guard(d, plan->dc->ctx);
+    oe_sgd_args a;
+    memset(&a, 0, sizeof(a));
+    a.lr = hp->lr;
+    a.momentum = hp->momentum;
+    a.dampening = hp->dampening;
+    a.max_norm = hp->max_norm;
+    a.flags = hp->flags;
+    a.norm = hp->max_norm > 0.0f ? (uint64_t)plan->d_norm : 0;
+    uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
+    void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
+    rc = launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
+    if (rc || !(hp->momentum > 0.0f)) return rc;
+    uint32_t n = plan->n_active;
+    void* mark_args[] = {&plan->d_tensors, &n};
+    return launch(d, plan->dc->k.sgd_mark, "oe_sgd_mark", (n + kThreads - 1) / kThreads, kThreads, (CUstream)stream,
+                  mark_args);
+}
+
+extern "C" int oe_zero_grads(oe_plan* plan, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = check_chunk_count(plan)) != 0) return rc;
+    if (plan->n_chunks == 0) return 0;
+    CtxGuard guard(d, plan->dc->ctx);
+    uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
+    void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems};
+    return launch(d, plan->dc->k.zero, "oe_zero_grads", grid_for(plan, plan->dc->occ_zero), kThreads, (CUstream)stream,
+                  args);
+}
+
+extern "C" int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t numel, uint64_t stream) {
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    DeviceCtx* dc = device_or_fail(device, &rc);
+    if (!dc) return rc;
+    if (numel == 0) return 0;  // an empty launch is not an error (kernels/kernels_test.go:153-174)
+    if (src == 0 || dst == 0 || (src & 3u) || (dst & 1u)) return fail(OE_ERR_INVALID, "oe_cast_bf16: bad address");
+    CtxGuard guard(d, dc->ctx);
+    uint64_t vec_threads = (numel + 3) / 4;
+    uint64_t blocks = (vec_threads + kThreads - 1) / kThreads;
+    uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_cast > 0 ? dc->occ_cast : 1);
+    uint32_t grid = (uint32_t)(blocks < persistent ? blocks : persistent);
+    void* args[] = {&src, &dst, &numel};
+    return launch(d, dc->k.cast, "oe_cast_bf16", grid, kThreads, (CUstream)stream, args);
+}
+
+extern "C" int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, const float* const* host_grads,
+                                       uint32_t n_tensors, float* norm_out, uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    if (n_tensors != plan->descs.size()) return fail(OE_ERR_INVALID, "host gradient count differs from the plan's");
+    if (n_tensors > 0 && !host_grads) return fail(OE_ERR_INVALID, "host_grads is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = validate_adamw(plan, hp)) != 0) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    CUstream s = (CUstream)stream;
+    for (uint32_t i = 0; i < n_tensors; i++) {
+        const oe_tensor_desc& x = plan->descs[i];
+        if (x.grad == 0 || host_grads[i] == nullptr) continue;
+        OE_CU(d->cuMemcpyHtoDAsync_((CUdeviceptr)x.grad, host_grads[i], x.numel * sizeof(float), s),
+              "cuMemcpyHtoDAsync(gradient)");
+    }
+    if ((rc = launch_sumsq(d, plan, 0, s)) != 0) return rc;
+    if ((rc = launch_adamw(d, plan, hp, s)) != 0) return rc;
+    oe_dev_norm rec;
+    OE_CU(d->cuMemcpyDtoHAsync_(&rec, plan->d_norm, sizeof(rec), s), "cuMemcpyDtoHAsync(norm)");
+    OE_CU(d->cuStreamSynchronize_(s), "cuStreamSynchronize");
+    if (norm_out) *norm_out = rec.norm;
+    return 0;
+}
+
+// -------------------------------------------------------------------------------------
+// launch counters
+// -------------------------------------------------------------------------------------
+extern "C" int64_t oe_launch_count(const char* kernel_name) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    int64_t total = 0;
+    for (const auto& kv : g_launches)
+        if (!kernel_name || kv.first == kernel_name) total += kv.second;
+    return total;
+}
+
+extern "C" void oe_launch_count_reset(void) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_launches.clear();
+}
+
+// -------------------------------------------------------------------------------------
+// device plumbing
+// -------------------------------------------------------------------------------------
+#define OE_DEVICE_PROLOGUE                          \
+    int rc = 0;                                     \
+    const oe_driver* d = driver_or_fail(&rc);       \
+    if (!d) return rc;                              \
+    DeviceCtx* dc = device_or_fail(device, &rc);    \
+    if (!dc) return rc;                             \
+    CtxGuard guard(d, dc->ctx)
+
+extern "C" int oe_mem_alloc(int device, uint64_t bytes, uint64_t* address_out) {
+    if (!address_out || bytes == 0) return fail(OE_ERR_INVALID, "oe_mem_alloc: bad argument");
+    OE_DEVICE_PROLOGUE;
+    CUdeviceptr p = 0;
+    OE_CU(d->cuMemAlloc_(&p, bytes), "cuMemAlloc");
+    *address_out = (uint64_t)p;
+    return 0;
+}
+extern "C" int oe_mem_free(int device, uint64_t address) {
+    if (address == 0) return 0;
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemFree_((CUdeviceptr)address), "cuMemFree");
+    return 0;
+}
+extern "C" int oe_mem_info(int device, uint64_t* free_out, uint64_t* total_out) {
+    OE_DEVICE_PROLOGUE;
+    size_t f = 0, t = 0;
+    OE_CU(d->cuMemGetInfo_(&f, &t), "cuMemGetInfo");
+    if (free_out) *free_out = f;
+    if (total_out) *total_out = t;
+    return 0;
+}
+extern "C" int oe_memcpy_h2d(int device, uint64_t dst, const void* src, uint64_t bytes, uint64_t stream) {
+    if (bytes == 0) return 0;
+    if (!dst || !src) return fail(OE_ERR_INVALID, "oe_memcpy_h2d: NULL address");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemcpyHtoDAsync_((CUdeviceptr)dst, src, bytes, (CUstream)stream), "cuMemcpyHtoDAsync");
+    return 0;
+}
+extern "C" int oe_memcpy_d2h(int device, void* dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+    if (bytes == 0) return 0;
+    if (!dst || !src) return fail(OE_ERR_INVALID, "oe_memcpy_d2h: NULL address");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemcpyDtoHAsync_(dst, (CUdeviceptr)src, bytes, (CUstream)stream), "cuMemcpyDtoHAsync");
+    return 0;
+}
+extern "C" int oe_memcpy_d2d(int device, uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream) {
+    if (bytes == 0) return 0;
+    if (!dst || !src) return fail(OE_ERR_INVALID, "oe_memcpy_d2d: NULL address");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemcpyDtoDAsync_((CUdeviceptr)dst, (CUdeviceptr)src, bytes, (CUstream)stream), "cuMemcpyDtoDAsync");
+    return 0;
+}
+extern "C" int oe_memset_u32(int device, uint64_t dst, uint32_t value, uint64_t count, uint64_t stream) {
+    if (count == 0) return 0;
+    if (!dst || (dst & 3u)) return fail(OE_ERR_INVALID, "oe_memset_u32: bad address");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemsetD32Async_((CUdeviceptr)dst, value, count, (CUstream)stream), "cuMemsetD32Async");
+    return 0;
+}
+extern "C" int oe_host_alloc(int device, uint64_t bytes, void** out) {
+    if (!out || bytes == 0) return fail(OE_ERR_INVALID, "oe_host_alloc: bad argument");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemAllocHost_(out, bytes), "cuMemAllocHost");
+    return 0;
+}
+extern "C" int oe_host_free(int device, void* ptr) {
+    if (!ptr) return 0;
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuMemFreeHost_(ptr), "cuMemFreeHost");
+    return 0;
+}
+extern "C" int oe_stream_create(int device, uint64_t* stream_out) {
+    if (!stream_out) return fail(OE_ERR_INVALID, "stream_out is NULL");
+    OE_DEVICE_PROLOGUE;
+    CUstream s = nullptr;
+    OE_CU(d->cuStreamCreate_(&s, CU_STREAM_NON_BLOCKING), "cuStreamCreate");
+    *stream_out = (uint64_t)s;
+    return 0;
+}
+extern "C" int oe_stream_destroy(int device, uint64_t stream) {
+    if (!stream) return 0;
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuStreamDestroy_((CUstream)stream), "cuStreamDestroy");
+    return 0;
+}
+extern "C" int oe_stream_sync(int device, uint64_t stream) {
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuStreamSynchronize_((CUstream)stream), "cuStreamSynchronize");
+    return 0;
+}
+extern "C" int oe_event_create(int device, uint64_t* event_out) {
+    if (!event_out) return fail(OE_ERR_INVALID, "event_out is NULL");
+    OE_DEVICE_PROLOGUE;
+    CUevent e = nullptr;
+    OE_CU(d->cuEventCreate_(&e, CU_EVENT_DEFAULT), "cuEventCreate");
+    *event_out = (uint64_t)e;
+    return 0;
+}
+extern "C" int oe_event_destroy(int device, uint64_t event) {
+    if (!event) return 0;
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuEventDestroy_((CUevent)event), "cuEventDestroy");
+    return 0;
+}
+extern "C" int oe_event_record(int device, uint64_t event, uint64_t stream) {
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuEventRecord_((CUevent)event, (CUstream)stream), "cuEventRecord");
+    return 0;
+}
+extern "C" int oe_event_sync(int device, uint64_t event) {
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuEventSynchronize_((CUevent)event), "cuEventSynchronize");
+    return 0;
+}
+extern "C" int oe_event_elapsed_ms(int device, uint64_t start, uint64_t stop, float* ms_out) {
+    if (!ms_out) return fail(OE_ERR_INVALID, "ms_out is NULL");
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuEventElapsedTime_(ms_out, (CUevent)start, (CUevent)stop), "cuEventElapsedTime");
+    return 0;
+}

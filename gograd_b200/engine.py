@@ -1,0 +1,199 @@
+"""Python face of the C ABI: plans over torch tensors. No arithmetic happens here."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+from . import _lib
+from ._lib import (OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,
+                   EngineError, check, lib)
+
+_initialised = set()
+
+
+def init(device: int = 0) -> None:
+    """oe_init once per device; raises EngineError without a driver or a B200."""
+    if device not in _initialised:
+        check(lib().oe_init(device))
+        _initialised.add(device)
+
+
+def _addr(t) -> int:
+    return 0 if t is None else int(t.data_ptr())
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        import torch
+        return int(torch.cuda.current_stream().cuda_stream)
+    if isinstance(stream, int):
+        return stream
+    return int(stream.cuda_stream)
+
+
+@dataclass
+class TensorDesc:
+    """One parameter as the engine sees it (oe_tensor_desc). Tensors are torch CUDA
+    tensors (fp32; shadow bf16 or int16/uint16) or None."""
+    param: object
+    grad: object = None
+    state1: object = None
+    state2: object = None
+    shadow: object = None
+    lr_scale: float = 1.0
+    weight_decay: float = 0.0
+
+    def to_c(self) -> _lib.oe_tensor_desc:
+        return _lib.oe_tensor_desc(_addr(self.param), _addr(self.grad), _addr(self.state1), _addr(self.state2),
+                                   _addr(self.shadow), int(self.param.numel()), self.lr_scale, self.weight_decay)
+
+
+@dataclass
+class AdamWHParams:
+    lr: float
+    beta1: float = 0.9
+    beta2: float = 0.999
+    eps: float = 1e-8
+    bc1: float = 1.0
+    bc2: float = 1.0
+    max_norm: float = 0.0
+    flags: int = 0
+    step_dev: int = 0
+
+    def to_c(self) -> _lib.oe_adamw_hparams:
+        return _lib.oe_adamw_hparams(self.lr, self.beta1, self.beta2, self.eps, self.bc1, self.bc2, self.max_norm,
+                                     self.flags, self.step_dev)
+
+
+@dataclass
+class SGDHParams:
+    lr: float
+    momentum: float = 0.0
+    dampening: float = 0.0
+    max_norm: float = 0.0
+    flags: int = 0
+
+    def to_c(self) -> _lib.oe_sgd_hparams:
+        return _lib.oe_sgd_hparams(self.lr, self.momentum, self.dampening, self.max_norm, self.flags, 0)
+
+
+def _desc_array(descs: Sequence[TensorDesc]):
+    arr = (_lib.oe_tensor_desc * max(len(descs), 1))()
+    for i, d in enumerate(descs):
+        arr[i] = d.to_c()
+    return arr
+
+
+class Plan:
+    """oe_plan: device tables for one parameter list on one device."""
+
+    def __init__(self, descs: Sequence[TensorDesc], device: int = 0, chunk_elems: int = 0):
+        init(device)
+        self.device = device
+        self._descs = list(descs)  # keeps the tensors alive while the plan borrows them
+        self._h = C.c_void_p()
+        check(lib().oe_plan_create(device, _desc_array(descs), len(descs), chunk_elems, C.byref(self._h)))
+
+    def update(self, descs: Sequence[TensorDesc], stream=None) -> None:
+        self._descs = list(descs)
+        check(lib().oe_plan_update(self._h, _desc_array(descs), len(descs), _stream(stream)))
+
+    def info(self, what: int) -> int:
+        return int(lib().oe_plan_info(self._h, what))
+
+    @property
+    def n_active(self) -> int:
+        return self.info(0)
+
+    @property
+    def n_chunks(self) -> int:
+        return self.info(1)
+
+    @property
+    def active_elems(self) -> int:
+        return self.info(2)
+
+    @property
+    def uploads(self) -> int:
+        return self.info(6)
+
+    def norm_address(self) -> int:
+        return int(lib().oe_plan_norm_address(self._h))
+
+    def set_variant(self, name: str) -> None:
+        check(lib().oe_plan_set_variant(self._h, name.encode()))
+
+    def grad_norm(self, flags: int = 0, stream=None) -> None:
+        check(lib().oe_grad_norm(self._h, flags, _stream(stream)))
+
+    def norm_finalize(self, stream=None) -> None:
+        check(lib().oe_norm_finalize(self._h, _stream(stream)))
+
+    def clip_grad_norm(self, max_norm: float, flags: int = 0, stream=None) -> None:
+        mx = C.c_float(max_norm)
+        check(lib().oe_clip_grad_norm(self._h, C.byref(mx), flags, _stream(stream)))
+
+    def read_norm(self, stream=None):
+        n, s = C.c_float(), C.c_double()
+        check(lib().oe_read_norm(self._h, C.byref(n), C.byref(s), _stream(stream)))
+        return n.value, s.value
+
+    def adamw_step(self, hp: AdamWHParams, stream=None) -> None:
+        c = hp.to_c()
+        check(lib().oe_adamw_step(self._h, C.byref(c), _stream(stream)))
+
+    def sgd_step(self, hp: SGDHParams, stream=None) -> None:
+        c = hp.to_c()
+        check(lib().oe_sgd_step(self._h, C.byref(c), _stream(stream)))
+
+    def zero_grads(self, stream=None) -> None:
+        check(lib().oe_zero_grads(self._h, _stream(stream)))
+
+    def adamw_step_from_host(self, hp: AdamWHParams, host_grads: Sequence[Optional[object]], stream=None) -> float:
+        """host_grads: per parameter a CPU torch tensor / numpy array (ideally page-locked) or None."""
+        n = len(host_grads)
+        ptrs = (C.c_void_p * max(n, 1))()
+        for i, g in enumerate(host_grads):
+            if g is None:
+                ptrs[i] = None
+            elif hasattr(g, "data_ptr"):
+                ptrs[i] = g.data_ptr()
+            else:
+                ptrs[i] = g.ctypes.data
+        c = hp.to_c()
+        norm = C.c_float()
+        check(lib().oe_adamw_step_from_host(self._h, C.byref(c), ptrs, n, C.byref(norm), _stream(stream)))
+        return norm.value
+
+    def close(self) -> None:
+        if self._h:
+            check(lib().oe_plan_destroy(self._h))
+            self._h = C.c_void_p()
+            self._descs = []
+
+    def __del__(self):  # best effort; explicit close() is the supported way
+        try:
+            if getattr(self, "_h", None):
+                lib().oe_plan_destroy(self._h)
+        except Exception:
+            pass
+
+
+def cast_bf16(src, dst, stream=None, device: int = 0) -> None:
+    """Stand-alone fp32 -> bf16 cast of one tensor (oe_cast_bf16)."""
+    init(device)
+    check(lib().oe_cast_bf16(device, _addr(src), _addr(dst), int(src.numel()), _stream(stream)))
+
+
+def launch_count(name: Optional[str] = None) -> int:
+    return int(lib().oe_launch_count(None if name is None else name.encode()))
+
+
+def launch_count_reset() -> None:
+    lib().oe_launch_count_reset()
+
+
+__all__ = ["AdamWHParams", "SGDHParams", "TensorDesc", "Plan", "cast_bf16", "init", "launch_count",
+           "launch_count_reset", "EngineError", "OE_CLIP_DEVFORM", "OE_WRITE_SHADOW", "OE_ZERO_GRAD", "OE_NESTEROV",
+           "OE_MAXIMIZE", "OE_PARTIAL_ONLY"]

@@ -1,0 +1,250 @@
+/*
+ * optengine — C ABI of the B200 optimizer-step engine (liboptengine.so).
+ *
+ * The library replaces, for NVIDIA B200 (sm_100a), the device side of gograd's
+ * training hot path: the AdamW / SGD parameter update, the global gradient-norm
+ * clip and the fp32-master -> bf16-shadow cast. It is what gograd's Go host code
+ * binds instead of compiling CUDA C with NVRTC at run time: prebuilt sm_100a
+ * cubins are embedded in the library and loaded through the CUDA driver API.
+ *
+ * Calling convention. Every argument is an integer, a pointer, or a pointer to a
+ * plain struct; floating-point values travel inside structs, never as direct
+ * arguments, so that a cgo-free Go binding (purego.SyscallN, the mechanism of
+ * vulkan/loader_linux.go:16-47) can call every entry point. Device addresses and
+ * streams are passed as uint64_t (CUdeviceptr / CUstream values; 0 = the default
+ * stream). Every function returns 0 on success, a positive CUresult when a driver
+ * call failed, or a negative OE_ERR_* code; oe_last_error() returns the message of
+ * the calling thread's last failure. Nothing here aborts, exits or throws.
+ *
+ * Ownership. The caller owns parameters, gradients, optimizer state and shadows;
+ * the library borrows their addresses for the duration of a call and owns only its
+ * plans (device tables, the norm record, reduction scratch). There is no CPU
+ * fallback: without a CUDA driver and a B200 every device call fails.
+ *
+ * Threading. A plan may be used from any thread, by one thread and one stream at a
+ * time. The library never changes the caller's current context: it pushes the
+ * device's primary context for the duration of a call and pops it again.
+ */
+#ifndef OPTENGINE_H
+#define OPTENGINE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OE_ABI_VERSION 1
+
+#if defined(__GNUC__)
+#define OE_API __attribute__((visibility("default")))
+#else
+#define OE_API
+#endif
+
+/* negative engine error codes (positive return values are CUresult codes) */
+#define OE_ERR_INVALID   (-1) /* bad argument; nothing was launched or changed           */
+#define OE_ERR_NO_DRIVER (-2) /* libcuda.so.1 missing or cuInit failed                   */
+#define OE_ERR_NOT_INIT  (-3) /* oe_init was not called for the device                   */
+#define OE_ERR_ARCH      (-4) /* the device is not sm_100 (the cubins are sm_100a only)  */
+#define OE_ERR_LIMIT     (-5) /* a size exceeds what the entry point supports            */
+#define OE_ERR_DEVICE    (-6) /* a kernel reported an error in its status word           */
+
+/* flag bits (oe_adamw_hparams.flags, oe_sgd_hparams.flags, oe_grad_norm flags) */
+#define OE_CLIP_DEVFORM  0x1u  /* clip coefficient fminf(1, max/(norm+1e-6)) as the reference's CUDA
+                                  kernels do (autograd/cuda_kernels.go:676); default is the host rule
+                                  "scale only if norm > max_norm" (autograd/nn.go:327-328)           */
+#define OE_WRITE_SHADOW  0x2u  /* write the bf16 shadow of every tensor that has one                 */
+#define OE_ZERO_GRAD     0x4u  /* store zeros over each gradient after it was consumed               */
+#define OE_NESTEROV      0x8u  /* SGDOptions.Nesterov (autograd/sgd.go:16-19)                        */
+#define OE_MAXIMIZE      0x10u /* SGDOptions.Maximize                                                */
+#define OE_PARTIAL_ONLY  0x20u /* oe_grad_norm: leave the sum of squares, do not take the root       */
+
+/* One optimizer parameter. Mirrors what the reference keeps per parameter:
+ * Tensor.buf / Tensor.gradBuf (autograd/tensor.go:19-52), AdamW.mGPU/vGPU
+ * (autograd/nn.go:336-346) or SGD.bufferGPU/initializedGPU (autograd/sgd.go:33-45), the
+ * bf16 shadow (autograd/cuda_autocast.go:15-60) and the resolved group of the
+ * parameter (autograd/param_groups.go:30-35). */
+typedef struct oe_tensor_desc {
+    uint64_t param;     /* float[numel]  master weights, device address                              */
+    uint64_t grad;      /* float[numel]  gradient, or 0 when the parameter has none: it is then
+                           skipped by every entry point, as a nil gradBuf is in the reference        */
+    uint64_t state1;    /* AdamW: m.   SGD: momentum buffer, or 0 when momentum == 0                 */
+    uint64_t state2;    /* AdamW: v.   SGD: device float holding 0/1 "buffer initialised", or 0      */
+    uint64_t shadow;    /* uint16[numel] bf16 shadow, or 0                                           */
+    uint64_t numel;     /* elements, > 0                                                             */
+    float lr_scale;     /* ParameterGroup.LRScale after normalisation (0 is taken as 1)              */
+    float weight_decay; /* ParameterGroup.WeightDecay                                                */
+} oe_tensor_desc;
+
+/* AdamW hyper-parameters of one step. The caller advances its step counter and
+ * computes the bias corrections exactly as AdamW.Step does (autograd/nn.go:492-494):
+ * bc = float32(1 - pow(float64(beta), float64(step))). */
+typedef struct oe_adamw_hparams {
+    float lr;          /* AdamW.LR (base rate; the group scale is applied on the device)             */
+    float beta1, beta2, eps;
+    float bc1, bc2;    /* bias corrections; ignored when step_dev != 0                               */
+    float max_norm;    /* > 0: fold the clip coefficient of the plan's last oe_grad_norm into the
+                          update (g*coef in registers); <= 0: no clipping                            */
+    uint32_t flags;    /* OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD                           */
+    uint64_t step_dev; /* device int32 step counter for captured steps (AdamW.PrepareGraph,
+                          autograd/nn.go:350-361): incremented on the device, bias corrections
+                          computed there; 0 = eager mode                                             */
+} oe_adamw_hparams;
+
+/* SGD hyper-parameters of one step (SGDOptions, autograd/sgd.go:16-19). */
+typedef struct oe_sgd_hparams {
+    float lr;          /* SGD.LR (base rate)                                                         */
+    float momentum, dampening;
+    float max_norm;    /* as in oe_adamw_hparams                                                     */
+    uint32_t flags;    /* OE_NESTEROV | OE_MAXIMIZE | OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD */
+    uint32_t reserved;
+} oe_sgd_hparams;
+
+typedef struct oe_plan oe_plan;
+
+/* ---- library ------------------------------------------------------------------------------------ */
+
+/* ABI version of the loaded library (OE_ABI_VERSION it was built with). */
+OE_API int oe_abi_version(void);
+
+/* Message of the calling thread's last failed call ("" when none). Replaces the
+ * *cuda.Error{Op,Code,Message} values of cuda/cuda_windows.go:24-36. */
+OE_API const char* oe_last_error(void);
+
+/* Binds the CUDA driver, retains the device's primary context and loads the embedded
+ * sm_100a cubin into it. Idempotent per device. Replaces the lazy NVRTC compile +
+ * cuModuleLoadData of cuda.Compile (cuda/kernel_windows.go:131-228) and the per-device
+ * kernel cache (cuda/device_cache.go:23-68). */
+OE_API int oe_init(int device);
+
+/* Unloads the modules and releases the primary contexts retained by oe_init. Plans
+ * must be destroyed first. */
+OE_API int oe_shutdown(void);
+
+/* Number of SMs of an initialised device (148 on B200); < 0 on error. */
+OE_API int oe_device_sm_count(int device);
+
+/* ---- plans -------------------------------------------------------------------------------------- */
+
+/* Builds the device-side tensor table and chunk table for a parameter list: the
+ * multi-tensor replacement of the reference's one-launch-per-tensor loops
+ * (autograd/nn.go:495-505, autograd/cuda_sgd.go:71-97) and of its clip pointer table
+ * (getClipPlan, autograd/cuda_clip.go:66-113, one write_clip_entry launch per tensor).
+ * Parameters with grad == 0 stay in the plan but are left out of the tables.
+ * chunk_elems = 0 selects the default work-unit size. Validates every descriptor
+ * before allocating anything. */
+OE_API int oe_plan_create(int device, const oe_tensor_desc* tensors, uint32_t n_tensors, uint32_t chunk_elems,
+                   oe_plan** out);
+
+/* Replaces the descriptors (gradients appear or disappear, the pool hands out other
+ * addresses, a group's decay changes). Like getClipPlan's cache check
+ * (autograd/cuda_clip.go:80-93) it compares addresses and sizes and re-uploads the
+ * tables on `stream` only when something changed. */
+OE_API int oe_plan_update(oe_plan* plan, const oe_tensor_desc* tensors, uint32_t n_tensors, uint64_t stream);
+
+OE_API int oe_plan_destroy(oe_plan* plan);
+
+/* Plan facts: what = 0 tensors with a gradient, 1 chunks, 2 elements with a gradient,
+ * 3 grid size of the update launch, 4 grid size of the norm launch, 5 chunk_elems,
+ * 6 number of table uploads so far. Returns -1 for an unknown query. */
+OE_API int64_t oe_plan_info(const oe_plan* plan, int what);
+
+/* Device address of the plan's norm record: a float32 norm at byte offset 8 and the
+ * float64 sum of squares at offset 0. Replaces clipState.norm (autograd/cuda_clip.go:22). */
+OE_API uint64_t oe_plan_norm_address(const oe_plan* plan);
+
+/* Selects one of the built shapes of the update kernel by name suffix ("" default,
+ * "u1", "u2b4", "u4"); a tuning knob, results are identical. */
+OE_API int oe_plan_set_variant(oe_plan* plan, const char* variant);
+
+/* ---- gradient norm and clip --------------------------------------------------------------------- */
+
+/* Global L2 norm over every present gradient of the plan: per-CTA float64 partial
+ * sums, finalised by the last CTA to arrive (deterministic, no memset, no host
+ * sync). Replaces norm.Memset + global_norm_parts + kernels.SqrtScalar
+ * (autograd/cuda_clip.go:120-129, autograd/cuda_kernels.go:675, kernels/optim.go:56-64).
+ * flags: OE_PARTIAL_ONLY leaves only the sum of squares (for a cross-rank reduction). */
+OE_API int oe_grad_norm(oe_plan* plan, uint32_t flags, uint64_t stream);
+
+/* norm = (float)sqrt(sum of squares) for a sum completed outside (after an all-reduce
+ * of the record's float64 field). */
+OE_API int oe_norm_finalize(oe_plan* plan, uint64_t stream);
+
+/* ClipGradNorm on the device (autograd/nn.go:310-317, autograd/cuda_clip.go:114-134): the
+ * norm as oe_grad_norm, then, when max_norm > 0, every present gradient scaled in
+ * place (scale_all_grads, autograd/cuda_kernels.go:676). max_norm travels by pointer. */
+OE_API int oe_clip_grad_norm(oe_plan* plan, const float* max_norm, uint32_t flags, uint64_t stream);
+
+/* Blocking read of the last norm (GradientNormToHost, autograd/nn.go:17-27). */
+OE_API int oe_read_norm(oe_plan* plan, float* norm_out, double* sumsq_out, uint64_t stream);
+
+/* ---- updates ------------------------------------------------------------------------------------ */
+
+/* One fused AdamW step over the whole plan in one launch: reads p, g, m, v with
+ * 128-bit loads, updates in fp32 registers in the operation order of the reference's
+ * host loop (autograd/nn.go:519-528), writes p, m, v and — with OE_WRITE_SHADOW — the
+ * round-to-nearest-even bf16 shadow. Replaces the per-tensor kernels.AdamWUpdate
+ * launches (autograd/nn.go:495-505, kernels/optim.go:69-82), graph_adamw
+ * (autograd/cuda_kernels.go:597) and the later f32_to_bf16 pass per weight
+ * (autograd/cuda_autocast.go:15-20). */
+OE_API int oe_adamw_step(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t stream);
+
+/* One fused SGD step (autograd/sgd.go:192-225 semantics; replaces sgd_update + sgd_mark
+ * per tensor, autograd/cuda_sgd.go:66-98): one update launch plus one launch that sets
+ * the per-tensor "initialised" flags. */
+OE_API int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream);
+
+/* Zero every present gradient in one launch (AdamW.ZeroGrad, autograd/nn.go:533-537). */
+OE_API int oe_zero_grads(oe_plan* plan, uint64_t stream);
+
+/* Stand-alone fp32 -> bf16 cast of one buffer (castBF16 / f32_to_bf16,
+ * autograd/cuda_autocast.go:15-20, autograd/cuda_kernels.go:86). */
+OE_API int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t numel, uint64_t stream);
+
+/* ---- host-buffer step --------------------------------------------------------------------------- */
+
+/* The whole step for a caller whose gradients live in host memory (Tensor.Grad):
+ * copies host_grads[i] (float[numel], page-locked for full speed; NULL = keep what is
+ * on the device) into each present gradient buffer, computes the norm, runs the fused
+ * AdamW step with the clip folded in, reads the pre-clip norm back into *norm_out and
+ * waits for the stream. n_tensors must equal the plan's. */
+OE_API int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, const float* const* host_grads,
+                            uint32_t n_tensors, float* norm_out, uint64_t stream);
+
+/* ---- launch counters ---------------------------------------------------------------------------- */
+
+/* Launches of the named kernel since the last reset (all devices). The reference's
+ * tests assert "kernel X ran" through its profile counts (autograd/cuda_kernels.go:11-82,
+ * autograd/sgd_test.go:119-121). name NULL = all kernels. */
+OE_API int64_t oe_launch_count(const char* kernel_name);
+OE_API void oe_launch_count_reset(void);
+
+/* ---- device plumbing for a host without a CUDA binding ------------------------------------------ */
+/* The reference's cuda package only exists for Windows (cuda/cuda_stub.go:1-25); these
+ * are the few calls its optimizer path needs on Linux (cuda.Alloc / Buffer.Free /
+ * CopyFromHost / CopyToHost / Memset, cuda/cuda_windows.go:324-700; Stream and Event,
+ * cuda/cuda_windows.go:700-900). */
+OE_API int oe_mem_alloc(int device, uint64_t bytes, uint64_t* address_out);
+OE_API int oe_mem_free(int device, uint64_t address);
+OE_API int oe_mem_info(int device, uint64_t* free_out, uint64_t* total_out);
+OE_API int oe_memcpy_h2d(int device, uint64_t dst, const void* src, uint64_t bytes, uint64_t stream);
+OE_API int oe_memcpy_d2h(int device, void* dst, uint64_t src, uint64_t bytes, uint64_t stream);
+OE_API int oe_memcpy_d2d(int device, uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream);
+OE_API int oe_memset_u32(int device, uint64_t dst, uint32_t value, uint64_t count, uint64_t stream);
+OE_API int oe_host_alloc(int device, uint64_t bytes, void** out); /* page-locked host memory */
+OE_API int oe_host_free(int device, void* ptr);
+OE_API int oe_stream_create(int device, uint64_t* stream_out);
+OE_API int oe_stream_destroy(int device, uint64_t stream);
+OE_API int oe_stream_sync(int device, uint64_t stream);
+OE_API int oe_event_create(int device, uint64_t* event_out);
+OE_API int oe_event_destroy(int device, uint64_t event);
+OE_API int oe_event_record(int device, uint64_t event, uint64_t stream);
+OE_API int oe_event_sync(int device, uint64_t event);
+OE_API int oe_event_elapsed_ms(int device, uint64_t start, uint64_t stop, float* ms_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPTENGINE_H */
