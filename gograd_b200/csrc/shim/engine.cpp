@@ -47,12 +47,12 @@ int fail_cu(const oe_driver* d, CUresult r, const char* op) {
     } while (0)
 
 struct KernelSet {
-    CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2b4, u4
+    CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
     CUfunction step_increment = nullptr, sgd = nullptr, sgd_mark = nullptr, sumsq = nullptr, norm_finalize = nullptr,
                scale = nullptr, zero = nullptr, cast = nullptr;
 };
-const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2b4", "oe_adamw_fused_u4"};
-const char* const kVariantKeys[4] = {"", "u1", "u2b4", "u4"};
+const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2", "oe_adamw_fused_u8"};
+const char* const kVariantKeys[4] = {"", "u1", "u2", "u8"};
 
 struct DeviceCtx {
     bool ready = false;

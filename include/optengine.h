@@ -156,7 +156,7 @@ OE_API int64_t oe_plan_info(const oe_plan* plan, int what);
 OE_API uint64_t oe_plan_norm_address(const oe_plan* plan);
 
 /* Selects one of the built shapes of the update kernel by name suffix ("" default,
- * "u1", "u2b4", "u4"); a tuning knob, results are identical. */
+ * "u1", "u2", "u8"); a tuning knob, results are identical. */
 OE_API int oe_plan_set_variant(oe_plan* plan, const char* variant);
 
 /* ---- gradient norm and clip --------------------------------------------------------------------- */
