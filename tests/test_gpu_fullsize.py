@@ -1,0 +1,120 @@
+"""Full-size checks: the GPT-style set against the oracle over several steps, and the 1.3B
+set through size-independent properties plus oracle checks on sampled tensors."""
+import os
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+def host(t):
+    return t.detach().cpu().numpy()
+
+
+def test_gpt_set_clip_shadow_groups_against_oracle():
+    """109.6M parameters, two groups (decay .1 on matrices, 0 on norms/biases), 2 % of the tensors
+    with x100 gradients so that clipping triggers, bf16 shadow: 5 steps, every element of p, m, v
+    against the oracle (bit-identical, and within the stated 1e-6 after the first step), the norm
+    within 1e-6 relative, the shadow bit-exact to RNE of the GPU master."""
+    import gograd_b200 as eng
+    from gograd_b200 import paramsets, workload
+    from gograd_b200.engine import OE_WRITE_SHADOW
+    from oracle import oracle
+
+    ps = paramsets.get("gpt")
+    assert ps.numel == paramsets.EXPECTED_NUMEL["gpt"]
+    st = workload.materialize(ps, "cuda:0")
+    plan = eng.Plan(st.descs())
+    names = [s.name for s in ps.params]
+    groups = [oracle.Group(g.name, [i for i, s in enumerate(ps.params) if s.group == g.name], g.lr_scale,
+                           g.weight_decay) for g in ps.groups]
+    hp = ps.hparams
+    ref = oracle.OracleAdamW([host(x).copy() for x in st.p], lr=hp["lr"], groups=groups, beta1=hp["beta1"],
+                             beta2=hp["beta2"], eps=hp["eps"], max_procs=os.cpu_count() or 1)
+    assert len(workload.boosted_indices(ps)) == 3
+    for t in range(1, 6):
+        workload.fill_grads(st, t)
+        grads = [host(g).copy() for g in st.g]
+        want_norm, scale = oracle.clip_grad_norm(grads, ps.max_norm)
+        assert scale < 1, "the boosted tensors must make the clip trigger"
+        ref.step(grads)
+        b1, b2 = workload.bias_corrections(hp["beta1"], hp["beta2"], t)
+        plan.grad_norm()
+        plan.adamw_step(eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], b1, b2, ps.max_norm,
+                                         OE_WRITE_SHADOW))
+        norm, _ = plan.read_norm()
+        assert abs(norm - float(want_norm)) <= 1e-6 * float(want_norm)
+        if t in (1, 5):
+            worst = 0.0
+            for i, name in enumerate(names):
+                for kind, got, want in (("p", st.p[i], ref.params[i]), ("m", st.s1[i], ref.m[i]),
+                                        ("v", st.s2[i], ref.v[i])):
+                    got = host(got)
+                    scale_ = float(np.max(np.abs(want))) or 1.0
+                    err = np.max(np.abs(got.astype(np.float64) - want) / (np.abs(want) + scale_))
+                    worst = max(worst, float(err))
+                    assert np.array_equal(got, want), f"step {t} {kind} {name} differs from the host loop"
+            assert worst <= (1e-6 if t == 1 else 1e-5)
+    for i in range(len(names)):
+        want = st.p[i].to(torch.bfloat16).view(torch.int16)
+        assert torch.equal(st.shadow[i].view(torch.int16), want), f"shadow {names[i]}"
+    plan.close()
+
+
+def test_llama1b_full_size_properties():
+    """1,345,423,360 parameters, one fused step (clip 1.0 + shadow) at full size:
+    - the norm equals an independent float64 reduction (torch) within 1e-6 relative;
+    - every shadow element is round-to-nearest-even of the GPU's own master (torch's
+      conversion, independent of this library) — bit-exact over all 1.3B elements;
+    - five sampled tensors (embedding, a projection, an FFN matrix, a norm weight, the head)
+      match the oracle element for element, with the clip coefficient derived from the norm;
+    - gradients are left untouched by the folded clip; two launches were issued."""
+    import gograd_b200 as eng
+    from gograd_b200 import paramsets, workload
+    from gograd_b200.engine import OE_WRITE_SHADOW
+    from oracle import oracle
+
+    ps = paramsets.get("llama1b")
+    assert ps.numel == paramsets.EXPECTED_NUMEL["llama1b"] and len(ps.params) == 219
+    st = workload.materialize(ps, "cuda:0")
+    # make the clip trigger: the natural norm is ~36.7 > 1
+    plan = eng.Plan(st.descs())
+    assert plan.active_elems == ps.numel
+    sample = [0, 1, 5, 8, 218]
+    before = {i: (host(st.p[i]).copy(), host(st.g[i]).copy()) for i in sample}
+    ref_sq = sum(float((g.double() ** 2).sum().item()) for g in st.g)
+    hp = ps.hparams
+    b1, b2 = workload.bias_corrections(hp["beta1"], hp["beta2"], 1)
+    eng.launch_count_reset()
+    plan.grad_norm()
+    plan.adamw_step(eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], b1, b2, ps.max_norm,
+                                     OE_WRITE_SHADOW))
+    norm, sumsq = plan.read_norm()
+    assert eng.launch_count() == 2
+    assert abs(sumsq - ref_sq) <= 1e-9 * ref_sq
+    assert abs(norm - ref_sq ** 0.5) <= 1e-6 * ref_sq ** 0.5
+    for i in range(len(st.p)):
+        assert torch.equal(st.shadow[i].view(torch.int16), st.p[i].to(torch.bfloat16).view(torch.int16)), i
+    coef = float(oracle.clip_coefficient(norm, ps.max_norm))
+    assert coef < 1
+    wd = ps.groups[0].weight_decay
+    for i in sample:
+        p0, g0 = before[i]
+        assert np.array_equal(host(st.g[i]), g0), "folded clip modified a gradient"
+        g = g0.copy()
+        oracle.scale_(g, coef)
+        o = oracle.OracleAdamW([p0], lr=hp["lr"], weight_decay=wd, beta1=hp["beta1"], beta2=hp["beta2"],
+                               eps=hp["eps"], max_procs=os.cpu_count() or 1)
+        o.step([g])
+        assert np.array_equal(host(st.p[i]), o.params[0]), ps.params[i].name
+        assert np.array_equal(host(st.s1[i]), o.m[0]) and np.array_equal(host(st.s2[i]), o.v[0])
+    # linearity of the norm: doubling every gradient doubles it exactly (power of two)
+    for g in st.g:
+        g.mul_(2.0)
+    plan.grad_norm()
+    norm2, sumsq2 = plan.read_norm()
+    assert sumsq2 == 4.0 * sumsq and norm2 == np.float32(2.0) * np.float32(norm)
+    plan.close()
