@@ -21,7 +21,7 @@ extern "C" const unsigned char oe_cubin_end[];
 namespace {
 
 constexpr uint32_t kThreads = 256;             // must equal OE_THREADS of the kernels
-constexpr uint32_t kDefaultChunkElems = 8192;  // 32 KB of one fp32 stream per work unit
+constexpr uint32_t kDefaultChunkElems = 4096;  // one pass of the update CTA: 256 threads x 4 vectors x 4 floats
 constexpr int kMaxDevices = 64;
 
 thread_local std::string t_error;
