@@ -835,3 +835,6 @@ extern "C" int oe_event_elapsed_ms(int device, uint64_t start, uint64_t stop, fl
     OE_CU(d->cuEventElapsedTime_(ms_out, (CUevent)start, (CUevent)stop), "cuEventElapsedTime");
     return 0;
 }
+
+// Lets other translation units of the library report through oe_last_error().
+extern "C" void oe_internal_set_error(const char* message) { t_error = message ? message : ""; }

@@ -213,6 +213,28 @@ OE_API int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t numel, 
 OE_API int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, const float* const* host_grads,
                             uint32_t n_tensors, float* norm_out, uint64_t stream);
 
+/* ---- allocation-free norm ------------------------------------------------------------------------ */
+
+/* Largest input of oe_grad_norm_static: 2^31 elements (8 GiB of fp32). */
+#define OE_STATIC_NORM_MAX_ELEMS 2147483648ull
+
+/* L2 norm of ONE contiguous fp32 gradient buffer, written as a float to the device address
+ * norm_out, without allocating anything: no plan, no cuMemAlloc/cudaMalloc, no free. It exists
+ * for hosts that cannot allocate once training runs — a process that gave the whole GPU to its
+ * own arena, so that a later driver allocation fails, or a step loop that must not take the
+ * device-wide synchronisation an allocation implies. The reduction's scratch (one float64
+ * partial sum per 65536 elements plus an arrival counter, 257 KB) is a fixed __device__ array
+ * inside the library image: every GPU that loads the library holds it until the process ends,
+ * and numel above OE_STATIC_NORM_MAX_ELEMS is refused with OE_ERR_LIMIT.
+ * All calls on a device share that array and it keeps the previous call's contents (the entry
+ * point re-zeroes the counter on `stream` before each launch): calls whose kernels could overlap
+ * on the GPU — other streams, other threads — race and must be serialised by the caller. The
+ * first call on a device also resolves the array's device address, which loads the module: make
+ * it at start-up, before any stream capture begins.
+ * No counterpart in the reference; same result as oe_grad_norm on a one-tensor plan up to the
+ * summation order of the float64 partial sums. */
+OE_API int oe_grad_norm_static(int device, uint64_t grad, uint64_t numel, uint64_t norm_out, uint64_t stream);
+
 /* ---- launch counters ---------------------------------------------------------------------------- */
 
 /* Launches of the named kernel since the last reset (all devices). The reference's

@@ -46,6 +46,7 @@ def test_no_cpu_fallback_without_a_driver():
     desc = (_lib.oe_tensor_desc * 1)()
     assert lib.oe_plan_create(0, desc, 1, 0, C.byref(out)) != 0 and not out.value
     assert lib.oe_cast_bf16(0, 16, 16, 4, 0) != 0
+    assert lib.oe_grad_norm_static(0, 16, 4, 16, 0) != 0
     with pytest.raises(_lib.EngineError):
         import gograd_b200
         gograd_b200.init(0)
