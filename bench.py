@@ -309,6 +309,8 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--variant", default="")
     ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: fused peer-memory kernels, or NCCL reduce-scatter / all-gather around the kernels")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-params", type=int, default=120_000_000)

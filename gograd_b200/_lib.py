@@ -62,6 +62,11 @@ PROTOTYPES = {
     "oe_cast_bf16": (_i, [_i, _u64, _u64, _u64, _u64]),
     "oe_adamw_step_from_host": (_i, [_plan, C.POINTER(oe_adamw_hparams), C.POINTER(_vp), _u32,
                                      C.POINTER(C.c_float), _u64]),
+    "oe_peer_reduce_grads": (_i, [_plan, C.POINTER(_u64), _u32, _u64, _u64, _u64, C.POINTER(C.c_float), _u32, _u64]),
+    "oe_adamw_step_peers": (_i, [_plan, C.POINTER(oe_adamw_hparams), C.POINTER(C.c_int64), _u32, _u64]),
+    "oe_ipc_export": (_i, [_i, _u64, _vp, C.POINTER(_u64)]),
+    "oe_ipc_import": (_i, [_i, _vp, C.POINTER(_u64)]),
+    "oe_ipc_close": (_i, [_i, _u64]),
     "oe_grad_norm_static": (_i, [_i, _u64, _u64, _u64, _u64]),
     "oe_launch_count": (C.c_int64, [C.c_char_p]),
     "oe_launch_count_reset": (None, []),

@@ -92,10 +92,34 @@ __device__ __forceinline__ void oe_adamw_one(float& p, float g, float& m, float&
     p = __fsub_rn(__fmul_rn(p, one_minus_decay), update);
 }
 
-template <int UNROLL>
+// Where the bf16 shadow of a chunk goes. Single GPU: the tensor's own shadow buffer.
+// Sharded step: every rank keeps a full shadow with the same layout, and the rank that
+// owns a shard stores its bf16 values into all of them (its own included) — the
+// all-gather of the shadows is these stores, overlapped with the update's HBM traffic.
+// Peer buffers are plain peer-mapped device memory reached with ordinary stores.
+template <bool PEERS>
+__device__ __forceinline__ void oe_store_shadow4(uint16_t* sh, uint32_t vec_index, uint2 packed, const oe_peer_set& peers) {
+    if (PEERS) {
+        for (uint32_t k = 0; k < peers.n; k++)
+            __stcs((uint2*)((char*)sh + peers.delta[k]) + vec_index, packed);
+    } else {
+        __stcs((uint2*)sh + vec_index, packed);
+    }
+}
+
+template <bool PEERS>
+__device__ __forceinline__ void oe_store_shadow1(uint16_t* sh, uint32_t index, uint16_t value, const oe_peer_set& peers) {
+    if (PEERS) {
+        for (uint32_t k = 0; k < peers.n; k++) ((uint16_t*)((char*)sh + peers.delta[k]))[index] = value;
+    } else {
+        sh[index] = value;
+    }
+}
+
+template <int UNROLL, bool PEERS>
 __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ tensors,
                                               const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
-                                              uint32_t chunk_elems, const oe_adamw_args& a) {
+                                              uint32_t chunk_elems, const oe_adamw_args& a, const oe_peer_set& peers) {
     oe_adamw_consts k;
     k.b1 = a.beta1;
     k.b2 = a.beta2;
@@ -161,7 +185,7 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
                             uint2 packed;
                             packed.x = oe_bf16_rne(P[u].x) | (oe_bf16_rne(P[u].y) << 16);
                             packed.y = oe_bf16_rne(P[u].z) | (oe_bf16_rne(P[u].w) << 16);
-                            __stcs((uint2*)sh + i, packed);
+                            oe_store_shadow4<PEERS>(sh, i, packed, peers);
                         }
                         if (zero_grad) __stcs(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
                     }
@@ -177,10 +201,12 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
             p[i] = pi;
             m[i] = mi;
             v[i] = vi;
-            if (sh) sh[i] = (uint16_t)oe_bf16_rne(pi);
+            if (sh) oe_store_shadow1<PEERS>(sh, i, (uint16_t)oe_bf16_rne(pi), peers);
             if (zero_grad) g[i] = 0.0f;
         }
     }
+    // Peer stores must be performed before the kernel is reported complete to other devices.
+    if (PEERS) __threadfence_system();
 }
 
 // The update kernel is built in a few shapes (vectors in flight per thread x resident
@@ -189,7 +215,9 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
     extern "C" __global__ void __launch_bounds__(OE_THREADS, min_blocks)                                   \
     name(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks,               \
          uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a) {                                       \
-        oe_adamw_body<unroll>(tensors, chunks, n_chunks, chunk_elems, a);                                  \
+        oe_peer_set none;                                                                                  \
+        none.n = 0;                                                                                        \
+        oe_adamw_body<unroll, false>(tensors, chunks, n_chunks, chunk_elems, a, none);                     \
     }
 // Default: four 128-bit vectors per stream in flight per thread, two CTAs per SM (measured
 // fastest on B200: fewer, fatter threads keep more bytes in flight than more CTAs do).
@@ -197,6 +225,13 @@ OE_ADAMW_VARIANT(oe_adamw_fused, 4, 2)
 OE_ADAMW_VARIANT(oe_adamw_fused_u1, 1, 4)
 OE_ADAMW_VARIANT(oe_adamw_fused_u2, 2, 3)
 OE_ADAMW_VARIANT(oe_adamw_fused_u8, 8, 1)
+
+// Sharded step: same update, shadow stored into every rank's shadow buffer.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
+oe_adamw_fused_peers(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks,
+                     uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a, const __grid_constant__ oe_peer_set peers) {
+    oe_adamw_body<4, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
+}
 
 // Capture mode: one thread advances the device step counter before the update
 // (the reference's graph_adam_inc, autograd/cuda_kernels.go:595).
@@ -477,3 +512,110 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
     }
     for (uint64_t i = done + tid; i < n; i += stride) dst[i] = (uint16_t)oe_bf16_rne(src[i]);
 }
+
+// ---------------------------------------------------------------------------------
+// sharded step: pull reduce-scatter of the gradients fused with the norm pass
+// ---------------------------------------------------------------------------------
+// Every rank holds a full flat gradient buffer of the same layout. The rank that owns
+// the shard [first, first+numel) reads that range from every rank's buffer with plain
+// 128-bit loads (its own from HBM, the others over NVLink through peer-mapped
+// addresses), adds them in ascending rank order — so the sum is the same on every run
+// and can be reproduced on the host —, scales the sum (1/n for a mean), writes the
+// reduced shard to `out` and accumulates its sum of squares in double in the same pass:
+// the reduce-scatter and the 4 B/param norm read of the single-GPU step become one
+// kernel. `out` may be this rank's own range (in place): a thread reads every element it
+// writes before it writes it, and no other rank reads that range of this buffer.
+// No flag or barrier is waited on here; ordering against the other ranks is the host's
+// job (stream-ordered collectives before and after).
+template <int NP>
+__device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
+                                                    float* __restrict__ out, oe_dev_norm* rec, double* partials) {
+    __shared__ double warp_sums[OE_THREADS / 32];
+    __shared__ uint32_t is_last;
+    const uint32_t n = pg.n;
+    const float scale = pg.scale;
+    double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
+    bool aligned = (((uint64_t)out | (first * 4u)) & 15u) == 0;
+#pragma unroll
+    for (int k = 0; k < NP; k++)
+        if (k < (int)n) aligned = aligned && ((pg.base[k] & 15u) == 0);
+    const uint64_t tid = (uint64_t)blockIdx.x * OE_THREADS + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * OE_THREADS;
+    uint64_t done = 0;
+    if (aligned) {
+        const uint64_t nvec = numel >> 2;
+        float4* o4 = (float4*)out;
+        for (uint64_t i0 = tid; i0 < nvec; i0 += 2 * stride) {
+            float4 v[2][NP];
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint64_t i = i0 + u * stride;
+#pragma unroll
+                for (int k = 0; k < NP; k++)
+                    if (k < (int)n && i < nvec) v[u][k] = __ldcs((const float4*)((const float*)pg.base[k] + first) + i);
+            }
+#pragma unroll
+            for (int u = 0; u < 2; u++) {
+                const uint64_t i = i0 + u * stride;
+                if (i < nvec) {
+                    float4 s = v[u][0];
+#pragma unroll
+                    for (int k = 1; k < NP; k++) {
+                        if (k < (int)n) {
+                            s.x = __fadd_rn(s.x, v[u][k].x);
+                            s.y = __fadd_rn(s.y, v[u][k].y);
+                            s.z = __fadd_rn(s.z, v[u][k].z);
+                            s.w = __fadd_rn(s.w, v[u][k].w);
+                        }
+                    }
+                    s.x = __fmul_rn(s.x, scale);
+                    s.y = __fmul_rn(s.y, scale);
+                    s.z = __fmul_rn(s.z, scale);
+                    s.w = __fmul_rn(s.w, scale);
+                    __stcs(o4 + i, s);
+                    double x = (double)s.x, y = (double)s.y, z = (double)s.z, w = (double)s.w;
+                    a0 = fma(x, x, a0);
+                    a1 = fma(y, y, a1);
+                    a2 = fma(z, z, a2);
+                    a3 = fma(w, w, a3);
+                }
+            }
+        }
+        done = nvec << 2;
+    }
+    for (uint64_t i = done + tid; i < numel; i += stride) {
+        float s = ((const float*)pg.base[0])[first + i];
+        for (uint32_t k = 1; k < n; k++) s = __fadd_rn(s, ((const float*)pg.base[k])[first + i]);
+        s = __fmul_rn(s, scale);
+        out[i] = s;
+        double x = (double)s;
+        a0 = fma(x, x, a0);
+    }
+    double block = oe_block_sum((a0 + a1) + (a2 + a3), warp_sums);
+    if (threadIdx.x == 0) {
+        partials[blockIdx.x] = block;
+        __threadfence();
+        uint32_t ticket = atomicAdd(&rec->ticket, 1u);
+        is_last = (ticket == gridDim.x - 1) ? 1u : 0u;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    double s = 0.0;
+    for (uint32_t i = threadIdx.x; i < gridDim.x; i += OE_THREADS) s += __ldcg(partials + i);
+    double total = oe_block_sum(s, warp_sums);
+    if (threadIdx.x == 0) {
+        rec->sumsq = total;
+        if (!(pg.flags & OE_F_PARTIAL_ONLY)) rec->norm = (float)sqrt(total);
+        rec->ticket = 0u;
+    }
+}
+
+#define OE_PEER_REDUCE_VARIANT(name, np)                                                               \
+    extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)                                       \
+    name(const __grid_constant__ oe_peer_grads pg, uint64_t first, uint64_t numel, float* out, oe_dev_norm* rec, double* partials) { \
+        oe_peer_reduce_body<np>(pg, first, numel, out, rec, partials);                                \
+    }
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2)
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4)
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n8, 8)

@@ -37,6 +37,7 @@
     X(cuMemsetD32Async)                      \
     X(cuMemsetD8Async)                       \
     X(cuMemGetInfo)                          \
+    X(cuMemGetAddressRange)                  \
     X(cuStreamCreate)                        \
     X(cuStreamDestroy)                       \
     X(cuStreamSynchronize)                   \

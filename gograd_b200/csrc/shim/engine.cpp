@@ -48,6 +48,7 @@ int fail_cu(const oe_driver* d, CUresult r, const char* op) {
 
 struct KernelSet {
     CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
+    CUfunction adamw_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
     CUfunction step_increment = nullptr, sgd = nullptr, sgd_mark = nullptr, sumsq = nullptr, norm_finalize = nullptr,
                scale = nullptr, zero = nullptr, cast = nullptr;
 };
@@ -63,6 +64,7 @@ struct DeviceCtx {
     int sm_count = 0;
     KernelSet k;
     int occ_adamw[4] = {0, 0, 0, 0};
+    int occ_adamw_peers = 0, occ_peer_reduce[3] = {0, 0, 0};
     int occ_sgd = 0, occ_sumsq = 0, occ_scale = 0, occ_zero = 0, occ_cast = 0;
 };
 
@@ -329,6 +331,10 @@ extern "C" int oe_init(int device) {
     } table[] = {
         {&dc->k.adamw[0], kAdamwNames[0], &dc->occ_adamw[0]}, {&dc->k.adamw[1], kAdamwNames[1], &dc->occ_adamw[1]},
         {&dc->k.adamw[2], kAdamwNames[2], &dc->occ_adamw[2]}, {&dc->k.adamw[3], kAdamwNames[3], &dc->occ_adamw[3]},
+        {&dc->k.adamw_peers, "oe_adamw_fused_peers", &dc->occ_adamw_peers},
+        {&dc->k.peer_reduce[0], "oe_peer_reduce_sumsq_n2", &dc->occ_peer_reduce[0]},
+        {&dc->k.peer_reduce[1], "oe_peer_reduce_sumsq_n4", &dc->occ_peer_reduce[1]},
+        {&dc->k.peer_reduce[2], "oe_peer_reduce_sumsq_n8", &dc->occ_peer_reduce[2]},
         {&dc->k.step_increment, "oe_step_increment", nullptr}, {&dc->k.sgd, "oe_sgd_fused", &dc->occ_sgd},
         {&dc->k.sgd_mark, "oe_sgd_mark", nullptr},             {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
         {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
@@ -564,7 +570,8 @@ int validate_adamw(const oe_plan* p, const oe_adamw_hparams* hp) {
     return check_chunk_count(p);
 }
 
-int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUstream stream) {
+int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUstream stream,
+                 const oe_peer_set* peers = nullptr) {
     if (hp->step_dev) {
         uint64_t sd = hp->step_dev;
         void* inc_args[] = {&sd};
@@ -585,6 +592,12 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     a.norm = hp->max_norm > 0.0f ? (uint64_t)p->d_norm : 0;
     a.step_dev = hp->step_dev;
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
+    if (peers) {
+        oe_peer_set ps = *peers;
+        void* peer_args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &a, &ps};
+        return launch(d, p->dc->k.adamw_peers, "oe_adamw_fused_peers", grid_for(p, p->dc->occ_adamw_peers), kThreads,
+                      stream, peer_args);
+    }
     void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &a};
     return launch(d, p->dc->k.adamw[p->variant], kAdamwNames[p->variant], grid_for(p, p->dc->occ_adamw[p->variant]),
                   kThreads, stream, args);
@@ -835,6 +848,97 @@ extern "C" int oe_event_elapsed_ms(int device, uint64_t start, uint64_t stop, fl
     OE_CU(d->cuEventElapsedTime_(ms_out, (CUevent)start, (CUevent)stop), "cuEventElapsedTime");
     return 0;
 }
+
+// -------------------------------------------------------------------------------------
+// sharded step (ZeRO-1 style): peer-memory kernels and the IPC plumbing they need
+// -------------------------------------------------------------------------------------
+extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
+                                    uint64_t numel, uint64_t out, const float* scale, uint32_t flags, uint64_t stream) {
+    if (!plan || !rank_bases || !scale) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: NULL argument");
+    if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_peer_reduce_grads: 1 to 8 ranks are supported");
+    if (flags & ~OE_PARTIAL_ONLY) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
+    if (!isfinite(*scale)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: scale is not finite");
+    if (numel > 0 && (out == 0 || (out & 3u))) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad output address");
+    oe_peer_grads pg;
+    memset(&pg, 0, sizeof(pg));
+    pg.n = n_ranks;
+    pg.flags = flags;
+    pg.scale = *scale;
+    for (uint32_t k = 0; k < n_ranks; k++) {
+        if (rank_bases[k] == 0 || (rank_bases[k] & 3u)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad gradient base of rank " + std::to_string(k));
+        pg.base[k] = rank_bases[k];
+    }
+    for (uint32_t k = n_ranks; k < OE_MAX_PEERS; k++) pg.base[k] = rank_bases[0];
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    DeviceCtx* dc = plan->dc;
+    CtxGuard guard(d, dc->ctx);
+    int which = n_ranks <= 2 ? 0 : n_ranks <= 4 ? 1 : 2;
+    static const char* const names[3] = {"oe_peer_reduce_sumsq_n2", "oe_peer_reduce_sumsq_n4", "oe_peer_reduce_sumsq_n8"};
+    uint64_t vec_threads = (numel / 4 + 1) / 2 + 1;
+    uint64_t blocks = (vec_threads + kThreads - 1) / kThreads;
+    uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_peer_reduce[which] > 0 ? dc->occ_peer_reduce[which] : 1);
+    uint64_t grid = blocks < persistent ? blocks : persistent;
+    if (grid > plan->max_grid) grid = plan->max_grid;
+    if (grid == 0) grid = 1;
+    void* args[] = {&pg, &first_elem, &numel, &out, &plan->d_norm, &plan->d_partials};
+    return launch(d, dc->k.peer_reduce[which], names[which], (uint32_t)grid, kThreads, (CUstream)stream, args);
+}
+
+extern "C" int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
+                                   uint32_t n_ranks, uint64_t stream) {
+    if (!plan || !shadow_deltas) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: NULL argument");
+    if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_adamw_step_peers: 1 to 8 ranks are supported");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = validate_adamw(plan, hp)) != 0) return rc;
+    oe_peer_set ps;
+    memset(&ps, 0, sizeof(ps));
+    ps.n = n_ranks;
+    for (uint32_t k = 0; k < n_ranks; k++) {
+        if (shadow_deltas[k] & 1) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: odd byte distance to a bf16 buffer");
+        // an 8-byte store needs every target as aligned as the local one
+        if (shadow_deltas[k] & 7) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: shadow buffers must be mutually 8-byte aligned");
+        ps.delta[k] = shadow_deltas[k];
+    }
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_adamw(d, plan, hp, (CUstream)stream, &ps);
+}
+
+extern "C" int oe_ipc_export(int device, uint64_t address, void* handle_out, uint64_t* offset_out) {
+    if (!address || !handle_out || !offset_out) return fail(OE_ERR_INVALID, "oe_ipc_export: NULL argument");
+    static_assert(sizeof(CUipcMemHandle) == 64, "IPC handle is 64 bytes");
+    OE_DEVICE_PROLOGUE;
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    OE_CU(d->cuMemGetAddressRange_(&base, &size, (CUdeviceptr)address), "cuMemGetAddressRange");
+    CUipcMemHandle h;
+    OE_CU(d->cuIpcGetMemHandle_(&h, base), "cuIpcGetMemHandle");
+    memcpy(handle_out, &h, sizeof(h));
+    *offset_out = (uint64_t)address - (uint64_t)base;
+    return 0;
+}
+
+extern "C" int oe_ipc_import(int device, const void* handle, uint64_t* base_out) {
+    if (!handle || !base_out) return fail(OE_ERR_INVALID, "oe_ipc_import: NULL argument");
+    OE_DEVICE_PROLOGUE;
+    CUipcMemHandle h;
+    memcpy(&h, handle, sizeof(h));
+    CUdeviceptr p = 0;
+    OE_CU(d->cuIpcOpenMemHandle_(&p, h, CU_IPC_MEM_LAZY_ENABLE_PEER_ACCESS), "cuIpcOpenMemHandle");
+    *base_out = (uint64_t)p;
+    return 0;
+}
+
+extern "C" int oe_ipc_close(int device, uint64_t base) {
+    if (!base) return 0;
+    OE_DEVICE_PROLOGUE;
+    OE_CU(d->cuIpcCloseMemHandle_((CUdeviceptr)base), "cuIpcCloseMemHandle");
+    return 0;
+}
+
 
 // Lets other translation units of the library report through oe_last_error().
 extern "C" void oe_internal_set_error(const char* message) { t_error = message ? message : ""; }

@@ -57,6 +57,24 @@ typedef struct oe_sgd_args {
     uint64_t norm;
 } oe_sgd_args;
 
+/* Ranks of a sharded step: byte distance from this rank's buffer to rank k's buffer of the
+ * same layout (0 for the rank itself). */
+#define OE_MAX_PEERS 8
+typedef struct oe_peer_set {
+    uint32_t n;
+    uint32_t pad;
+    int64_t delta[OE_MAX_PEERS];
+} oe_peer_set;
+
+/* Arguments of the pull-reduce kernel: rank k's gradient buffer base, as seen from this GPU. */
+typedef struct oe_peer_grads {
+    uint32_t n;
+    uint32_t flags;
+    float scale;      /* multiplies the fixed-order sum (1/n for a mean, 1 for a sum) */
+    uint32_t pad;
+    uint64_t base[OE_MAX_PEERS];
+} oe_peer_grads;
+
 /* flag bits shared with include/optengine.h */
 #define OE_F_CLIP_DEVFORM 0x1u  /* coefficient = fminf(1, max/(norm+1e-6)) instead of the host rule */
 #define OE_F_WRITE_SHADOW 0x2u  /* write the bf16 shadow where a tensor has one  */

@@ -147,6 +147,20 @@ class Plan:
         c = hp.to_c()
         check(lib().oe_sgd_step(self._h, C.byref(c), _stream(stream)))
 
+    def peer_reduce_grads(self, rank_bases: Sequence[int], first_elem: int, numel: int, out_address: int,
+                          scale: float, flags: int = 0, stream=None) -> None:
+        """Pull reduce-scatter + sum of squares over peer-mapped gradient buffers (oe_peer_reduce_grads)."""
+        bases = (C.c_uint64 * len(rank_bases))(*rank_bases)
+        sc = C.c_float(scale)
+        check(lib().oe_peer_reduce_grads(self._h, bases, len(rank_bases), first_elem, numel, out_address,
+                                         C.byref(sc), flags, _stream(stream)))
+
+    def adamw_step_peers(self, hp: AdamWHParams, shadow_deltas: Sequence[int], stream=None) -> None:
+        """AdamW step whose shadow stores go to every rank's shadow buffer (oe_adamw_step_peers)."""
+        c = hp.to_c()
+        deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
+        check(lib().oe_adamw_step_peers(self._h, C.byref(c), deltas, len(shadow_deltas), _stream(stream)))
+
     def zero_grads(self, stream=None) -> None:
         check(lib().oe_zero_grads(self._h, _stream(stream)))
 
@@ -184,6 +198,28 @@ def cast_bf16(src, dst, stream=None, device: int = 0) -> None:
     """Stand-alone fp32 -> bf16 cast of one tensor (oe_cast_bf16)."""
     init(device)
     check(lib().oe_cast_bf16(device, _addr(src), _addr(dst), int(src.numel()), _stream(stream)))
+
+
+def ipc_export(address: int, device: int = 0):
+    """(64-byte handle, offset) of the allocation containing a device address (oe_ipc_export)."""
+    init(device)
+    handle = (C.c_ubyte * 64)()
+    offset = C.c_uint64()
+    check(lib().oe_ipc_export(device, address, handle, C.byref(offset)))
+    return bytes(handle), int(offset.value)
+
+
+def ipc_import(handle: bytes, device: int = 0) -> int:
+    """Maps a peer's allocation on this device and returns its base address (oe_ipc_import)."""
+    init(device)
+    buf = (C.c_ubyte * 64).from_buffer_copy(handle)
+    base = C.c_uint64()
+    check(lib().oe_ipc_import(device, buf, C.byref(base)))
+    return int(base.value)
+
+
+def ipc_close(base: int, device: int = 0) -> None:
+    check(lib().oe_ipc_close(device, base))
 
 
 def launch_count(name: Optional[str] = None) -> int:

@@ -1,0 +1,288 @@
+"""Sharded (ZeRO-1 style) AdamW step: one process per GPU, state partitioned over ranks.
+
+The reference has no distributed code; this is the data-parallel form of its optimizer
+step. Every rank holds a full flat fp32 gradient buffer (its own gradients, input) and a
+full flat bf16 shadow buffer (output, what the next forward reads); master weights, m and
+v exist only on the rank that owns their shard. One step:
+
+    1. reduce-scatter the gradients (mean over ranks) into the owner's shard
+    2. sum of squares of the shard -> all-reduce of one float64 -> global norm
+    3. fused AdamW on the shard with the clip coefficient folded in
+    4. all-gather of the bf16 shadows
+
+Two data paths do this:
+
+  "peer"  hand-written kernels over peer-mapped memory (CUDA IPC, plain loads/stores):
+          step 1+2 are ONE kernel (each rank pulls its shard from every rank, adds in
+          ascending rank order, writes the mean and accumulates its squares), step 3+4 are
+          ONE kernel (the update stores each bf16 value into every rank's shadow buffer).
+          The only library collective is the 8-byte all-reduce, which also orders the
+          ranks: nothing in the kernels waits on another GPU.
+  "nccl"  ncclReduceScatter(avg) + the single-GPU kernels + ncclAllGather: the baseline
+          the fused path is measured against.
+
+The flat layout and the partition live in `ShardLayout` (pure Python, tested on CPU with
+gloo ranks); `Zero1AdamW` drives either path through torch.distributed.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+
+@dataclass(frozen=True)
+class Piece:
+    """The part of one tensor that falls into one rank's shard."""
+    tensor: int        # index in the parameter list
+    tensor_offset: int  # first element inside the tensor
+    flat_offset: int    # first element inside the flat buffer
+    length: int
+
+
+class ShardLayout:
+    """Flat layout of a parameter list and its contiguous partition over `world` ranks.
+
+    Tensor i starts at `offsets[i]`, a multiple of `align` elements (8 elements = 32 bytes of
+    fp32 and 16 bytes of bf16, so both streams keep their 128-bit alignment); rank r owns
+    [r*shard_len, (r+1)*shard_len) with shard_len a multiple of `shard_align`; the gaps and
+    the tail are padding that must hold zeros in the gradient buffer. 64-bit offsets: the
+    8B-parameter set's flat length exceeds 2^31."""
+
+    def __init__(self, numels: Sequence[int], world: int, align: int = 8, shard_align: int = 4096):
+        if world < 1:
+            raise ValueError("world size must be positive")
+        if align < 1 or shard_align % align != 0:
+            raise ValueError("shard_align must be a multiple of align")
+        if any(n <= 0 for n in numels):
+            raise ValueError("tensors must not be empty")
+        self.numels = [int(n) for n in numels]
+        self.world = world
+        self.align = align
+        self.offsets: List[int] = []
+        pos = 0
+        for n in self.numels:
+            pos = -(-pos // align) * align
+            self.offsets.append(pos)
+            pos += n
+        self.used = pos
+        per_rank = -(-pos // world)
+        self.shard_len = max(shard_align, -(-per_rank // shard_align) * shard_align)
+        self.total = self.shard_len * world
+
+    def shard_range(self, rank: int) -> Tuple[int, int]:
+        if not 0 <= rank < self.world:
+            raise ValueError("rank out of range")
+        return rank * self.shard_len, (rank + 1) * self.shard_len
+
+    def pieces(self, rank: int) -> List[Piece]:
+        lo, hi = self.shard_range(rank)
+        out = []
+        for i, (off, n) in enumerate(zip(self.offsets, self.numels)):
+            a, b = max(off, lo), min(off + n, hi)
+            if a < b:
+                out.append(Piece(i, a - off, a, b - a))
+        return out
+
+    def padding_ranges(self) -> List[Tuple[int, int]]:
+        """[start, end) ranges of the flat buffer that belong to no tensor."""
+        gaps, pos = [], 0
+        for off, n in zip(self.offsets, self.numels):
+            if off > pos:
+                gaps.append((pos, off))
+            pos = off + n
+        if pos < self.total:
+            gaps.append((pos, self.total))
+        return gaps
+
+    def owner_of(self, flat_index: int) -> int:
+        return flat_index // self.shard_len
+
+
+class _RawCuda:
+    """Lets torch view a device address it does not own (the plan's norm record)."""
+
+    def __init__(self, address: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (address, False),
+                                         "version": 2}
+
+
+class Zero1Schedule:
+    """What every rank does in one sharded step, independent of where the arithmetic runs.
+
+    Subclasses provide the four phases. `Zero1AdamW` runs them on the GPU through the C ABI;
+    the CPU test-suite runs them over gloo ranks to check the layout, the partition and the
+    sequencing against an unsharded run."""
+
+    def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
+                 beta2: float, eps: float, max_norm: float, rank: int, world: int):
+        if len(group_of) != len(numels):
+            raise ValueError("one (lr_scale, weight_decay) pair per parameter")
+        self.rank, self.world = rank, world
+        self.group_of = list(group_of)
+        self.lr, self.beta1, self.beta2, self.eps, self.max_norm = lr, beta1, beta2, eps, max_norm
+        self.step_count = 0
+        self.layout = ShardLayout(numels, world)
+        self.lo, self.hi = self.layout.shard_range(rank)
+        self.my_pieces = self.layout.pieces(rank)
+
+    def bias_corrections(self) -> Tuple[float, float]:
+        from .workload import bias_corrections
+        return bias_corrections(self.beta1, self.beta2, self.step_count)
+
+    def step(self) -> None:
+        self.step_count += 1          # one shared counter, as AdamW.Step keeps (autograd/nn.go:492)
+        self.reduce_grads()           # mean over ranks of this rank's shard + its sum of squares
+        self.combine_sumsq()          # sum over ranks -> global norm
+        self.update()                 # clip folded in, shard of p/m/v, bf16 of the shard
+        self.gather_shadows()         # every rank ends with the full bf16 model
+
+    def reduce_grads(self) -> None:
+        raise NotImplementedError
+
+    def combine_sumsq(self) -> None:
+        raise NotImplementedError
+
+    def update(self) -> None:
+        raise NotImplementedError
+
+    def gather_shadows(self) -> None:
+        raise NotImplementedError
+
+
+class Zero1AdamW(Zero1Schedule):
+    """Sharded AdamW + clip + bf16 shadow over torch.distributed (NCCL), one rank per GPU.
+
+    group_of[i] = (lr_scale, weight_decay) of parameter i. `comm` selects the data path
+    ("peer" or "nccl"). Gradients are written by the caller into `self.grad_flat`
+    (or the per-tensor views `self.grads`); after `step()` every rank's `self.shadow_flat`
+    holds the bf16 weights of the whole model."""
+
+    def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
+                 beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
+                 chunk_elems: int = 0):
+        import torch
+        import torch.distributed as dist
+
+        from . import engine
+        if comm not in ("peer", "nccl"):
+            raise ValueError("comm must be 'peer' or 'nccl'")
+        self.torch, self.dist, self.engine = torch, dist, engine
+        self.pg = process_group
+        super().__init__(numels, group_of, lr, beta1, beta2, eps, max_norm, dist.get_rank(process_group),
+                         dist.get_world_size(process_group))
+        self.device = device
+        self.comm = comm
+        # The peer path reads other ranks' gradient buffers directly: by default a tiny
+        # stream-ordered all-reduce at the start of a step makes sure they are complete. A
+        # caller that already synchronised its ranks after backward can switch it off.
+        self.sync_before_pull = True
+        L = self.layout
+        dev = torch.device("cuda", device)
+        self.grad_flat = torch.zeros(L.total, dtype=torch.float32, device=dev)
+        self.shadow_flat = torch.zeros(L.total, dtype=torch.bfloat16, device=dev)
+        self.master = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
+        self.m = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
+        self.grads = [self.grad_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
+        self.shadows = [self.shadow_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
+        lo = self.lo
+        descs = []
+        for pc in self.my_pieces:
+            a, b = pc.flat_offset, pc.flat_offset + pc.length
+            scale, decay = group_of[pc.tensor]
+            descs.append(engine.TensorDesc(self.master[a - lo:b - lo], self.grad_flat[a:b], self.m[a - lo:b - lo],
+                                           self.v[a - lo:b - lo], self.shadow_flat[a:b], scale, decay))
+        self.plan = engine.Plan(descs, device, chunk_elems)
+        self.sumsq = torch.as_tensor(_RawCuda(self.plan.norm_address(), (1,), "<f8"), device=dev)
+        self._token = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._imported: List[int] = []
+        self.grad_bases: Optional[List[int]] = None
+        self.shadow_deltas: Optional[List[int]] = None
+        if comm == "peer":
+            self._map_peers()
+
+    # ---- peer mapping (CUDA IPC through the C ABI) -------------------------------------
+    def _map_peers(self) -> None:
+        eng, dist = self.engine, self.dist
+        mine = {"grad": eng.ipc_export(self.grad_flat.data_ptr(), self.device),
+                "shadow": eng.ipc_export(self.shadow_flat.data_ptr(), self.device)}
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, mine, group=self.pg)
+        opened = {}
+        self.grad_bases, self.shadow_deltas = [], []
+        for r, info in enumerate(everyone):
+            if r == self.rank:
+                self.grad_bases.append(self.grad_flat.data_ptr())
+                self.shadow_deltas.append(0)
+                continue
+            addr = {}
+            for key in ("grad", "shadow"):
+                handle, offset = info[key]
+                if handle not in opened:  # both buffers may live in one allocation
+                    opened[handle] = eng.ipc_import(handle, self.device)
+                    self._imported.append(opened[handle])
+                addr[key] = opened[handle] + offset
+            self.grad_bases.append(addr["grad"])
+            self.shadow_deltas.append(addr["shadow"] - self.shadow_flat.data_ptr())
+        dist.barrier(group=self.pg)
+
+    # ---- helpers --------------------------------------------------------------------------
+    def zero_padding(self) -> None:
+        for a, b in self.layout.padding_ranges():
+            self.grad_flat[a:b].zero_()
+
+    def load_master(self, flat_weights) -> None:
+        """Every rank takes its shard out of a full flat fp32 weight tensor (same on all ranks)."""
+        self.master.copy_(flat_weights[self.lo:self.hi])
+
+    def _hparams(self, flags: int):
+        b1, b2 = self.bias_corrections()
+        return self.engine.AdamWHParams(self.lr, self.beta1, self.beta2, self.eps, b1, b2, self.max_norm, flags)
+
+    # ---- the four phases; all work is enqueued on the current torch stream, no host sync ----
+    def reduce_grads(self) -> None:
+        from .engine import OE_PARTIAL_ONLY
+        dist = self.dist
+        own = self.grad_flat[self.lo:self.hi]
+        if self.comm == "peer":
+            if self.sync_before_pull:
+                # every rank's gradients must be complete before anyone pulls them
+                dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
+            self.plan.peer_reduce_grads(self.grad_bases, self.lo, self.layout.shard_len, own.data_ptr(),
+                                        1.0 / self.world, OE_PARTIAL_ONLY)
+        else:
+            dist.reduce_scatter_tensor(own, self.grad_flat, op=dist.ReduceOp.AVG, group=self.pg)
+            self.plan.grad_norm(OE_PARTIAL_ONLY)
+
+    def combine_sumsq(self) -> None:
+        # 8 bytes; on the peer path this is also the point after which every rank's pull is over
+        self.dist.all_reduce(self.sumsq, op=self.dist.ReduceOp.SUM, group=self.pg)
+        self.plan.norm_finalize()
+
+    def update(self) -> None:
+        from .engine import OE_WRITE_SHADOW
+        hp = self._hparams(OE_WRITE_SHADOW)
+        if self.comm == "peer":
+            self.plan.adamw_step_peers(hp, self.shadow_deltas)
+        else:
+            self.plan.adamw_step(hp)
+
+    def gather_shadows(self) -> None:
+        dist = self.dist
+        if self.comm == "peer":
+            # the update kernel already stored into every rank's buffer; once this tiny reduction
+            # returns, every rank's stores are complete on every GPU
+            dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
+        else:
+            dist.all_gather_into_tensor(self.shadow_flat, self.shadow_flat[self.lo:self.hi], group=self.pg)
+
+    def grad_norm(self) -> float:
+        return self.plan.read_norm()[0]
+
+    def close(self) -> None:
+        self.torch.cuda.synchronize()
+        self.dist.barrier(group=self.pg)
+        self.plan.close()
+        for base in self._imported:
+            self.engine.ipc_close(base, self.device)
+        self._imported = []

@@ -213,6 +213,34 @@ OE_API int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t numel, 
 OE_API int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, const float* const* host_grads,
                             uint32_t n_tensors, float* norm_out, uint64_t stream);
 
+/* ---- sharded step (ZeRO-1 style) over peer memory ------------------------------------------------ */
+/* The reference has no distributed code at all (no collective, no sharding); these entry points
+ * have no counterpart there. Every rank (one process per GPU) keeps a full flat fp32 gradient
+ * buffer and a full flat bf16 shadow buffer of one common layout, and owns one contiguous shard of
+ * master weights, m and v. Buffers of other ranks are reached through CUDA IPC mappings (plain peer
+ * loads and stores only). None of these kernels waits on another rank: the caller
+ * orders them with stream-ordered collectives (see gograd_b200/zero1.py). */
+
+/* Pull reduce-scatter fused with the norm pass. rank_bases[k] is the address, valid on this GPU, of
+ * rank k's gradient buffer; the kernel reads elements [first_elem, first_elem+numel) of each, adds
+ * them in ascending rank order (deterministic), multiplies by *scale (1/n for a mean), writes the
+ * reduced shard to `out` (may be this rank's own range, in place) and leaves the float64 sum of
+ * squares of the reduced shard in the plan's norm record (and the norm, unless OE_PARTIAL_ONLY). */
+OE_API int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
+                                uint64_t numel, uint64_t out, const float* scale, uint32_t flags, uint64_t stream);
+
+/* oe_adamw_step whose bf16 shadow stores go to every rank's shadow buffer: shadow_deltas[k] is the
+ * byte distance from this rank's shadow buffer to rank k's mapping (0 for the rank itself). The
+ * all-gather of the shadows is these stores, overlapped with the update's own HBM traffic. */
+OE_API int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
+                               uint32_t n_ranks, uint64_t stream);
+
+/* CUDA IPC plumbing: export the allocation that contains `address` (64-byte handle + offset of
+ * the address inside it), map a peer's allocation on this device, unmap it. */
+OE_API int oe_ipc_export(int device, uint64_t address, void* handle_out, uint64_t* offset_out);
+OE_API int oe_ipc_import(int device, const void* handle, uint64_t* base_out);
+OE_API int oe_ipc_close(int device, uint64_t base);
+
 /* ---- allocation-free norm ------------------------------------------------------------------------ */
 
 /* Largest input of oe_grad_norm_static: 2^31 elements (8 GiB of fp32). */

@@ -1,0 +1,180 @@
+"""The sharded step's kernels on the GPU.
+
+One GPU: the ranks are emulated as separate buffers on the same device (the peer kernels
+never wait on one another, so running the ranks one after the other is exact). Two or more
+GPUs: real ranks over NCCL with CUDA-IPC peer mappings, both data paths, against the oracle.
+"""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+NUMELS = [5000, 3, 4097, 12, 70001, 8192]
+GROUPS = [(1.0, 0.1), (1.0, 0.0), (0.5, 0.1), (1.0, 0.0), (1.0, 0.1), (2.0, 0.05)]
+HP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, max_norm=0.01)
+
+
+def _grads(rank, step):
+    rng = np.random.default_rng(1000 * step + rank)
+    return [rng.normal(0, 1e-3, n).astype(np.float32) for n in NUMELS]
+
+
+def _weights():
+    rng = np.random.default_rng(77)
+    return [rng.normal(0, 0.02, n).astype(np.float32) for n in NUMELS]
+
+
+def _oracle_run(world, steps):
+    """Unsharded oracle on the fixed-order mean: (((g0+g1)+g2)+...) * float32(1/world)."""
+    from oracle import oracle
+    groups = [oracle.Group(f"g{i}", [i], s, d) for i, (s, d) in enumerate(GROUPS)]
+    ref = oracle.OracleAdamW([w.copy() for w in _weights()], lr=HP["lr"], groups=groups, beta1=HP["beta1"],
+                             beta2=HP["beta2"], eps=HP["eps"])
+    norms = []
+    for step in range(1, steps + 1):
+        per_rank = [_grads(r, step) for r in range(world)]
+        mean = []
+        for i in range(len(NUMELS)):
+            acc = per_rank[0][i].copy()
+            for r in range(1, world):
+                acc = (acc + per_rank[r][i]).astype(np.float32)
+            mean.append((acc * np.float32(1.0 / world)).astype(np.float32))
+        norm, _ = oracle.clip_grad_norm(mean, HP["max_norm"])
+        norms.append(float(norm))
+        ref.step(mean)
+    return ref, norms
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_peer_kernels_with_emulated_ranks(world):
+    import gograd_b200 as eng
+    from gograd_b200.engine import OE_PARTIAL_ONLY, OE_WRITE_SHADOW
+    from gograd_b200.workload import bias_corrections
+    from gograd_b200.zero1 import ShardLayout, _RawCuda
+    from oracle import oracle
+
+    eng.init(0)
+    L = ShardLayout(NUMELS, world)
+    G = [torch.zeros(L.total, device="cuda") for _ in range(world)]
+    S = [torch.full((L.total,), -1, dtype=torch.int16, device="cuda") for _ in range(world)]
+    weights = np.zeros(L.total, np.float32)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = w
+    P, M, V, plans, records = [], [], [], [], []
+    for r in range(world):
+        lo, hi = L.shard_range(r)
+        P.append(torch.from_numpy(weights[lo:hi].copy()).cuda())
+        M.append(torch.zeros(L.shard_len, device="cuda"))
+        V.append(torch.zeros(L.shard_len, device="cuda"))
+        descs = []
+        for pc in L.pieces(r):
+            a, b = pc.flat_offset, pc.flat_offset + pc.length
+            descs.append(eng.TensorDesc(P[r][a - lo:b - lo], G[r][a:b], M[r][a - lo:b - lo], V[r][a - lo:b - lo],
+                                        S[r][a:b], *GROUPS[pc.tensor]))
+        plans.append(eng.Plan(descs))
+        records.append(torch.as_tensor(_RawCuda(plans[r].norm_address(), (1,), "<f8"), device="cuda"))
+    steps = 2
+    ref, want_norms = _oracle_run(world, steps)
+    for step in range(1, steps + 1):
+        for r in range(world):
+            G[r].zero_()
+            for o, g in zip(L.offsets, _grads(r, step)):
+                G[r][o:o + g.size] = torch.from_numpy(g).cuda()
+        bases = [g.data_ptr() for g in G]
+        for r in range(world):
+            lo, hi = L.shard_range(r)
+            plans[r].peer_reduce_grads(bases, lo, L.shard_len, G[r][lo:hi].data_ptr(), 1.0 / world, OE_PARTIAL_ONLY)
+        total = sum(float(rec.item()) for rec in records)     # what the 8-byte all-reduce does
+        for r in range(world):
+            records[r].fill_(total)
+            plans[r].norm_finalize()
+            norm, _ = plans[r].read_norm()
+            assert abs(norm - want_norms[step - 1]) <= 1e-6 * want_norms[step - 1]
+            b1, b2 = bias_corrections(HP["beta1"], HP["beta2"], step)
+            hp = eng.AdamWHParams(HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], b1, b2, HP["max_norm"], OE_WRITE_SHADOW)
+            deltas = [S[k].data_ptr() - S[r].data_ptr() for k in range(world)]
+            plans[r].adamw_step_peers(hp, deltas)
+    torch.cuda.synchronize()
+    flat = {k: np.zeros(L.total, np.float32) for k in "pmv"}
+    for r in range(world):
+        lo, hi = L.shard_range(r)
+        flat["p"][lo:hi], flat["m"][lo:hi], flat["v"][lo:hi] = P[r].cpu().numpy(), M[r].cpu().numpy(), V[r].cpu().numpy()
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat["p"][o:o + n], ref.params[i]), f"p[{i}] world {world}"
+        assert np.array_equal(flat["m"][o:o + n], ref.m[i]) and np.array_equal(flat["v"][o:o + n], ref.v[i])
+        want = oracle.f32_to_bf16(ref.params[i]).view(np.int16)
+        for r in range(world):
+            assert np.array_equal(S[r][o:o + n].cpu().numpy(), want), f"shadow[{i}] on rank {r}"
+    # padding of every shadow buffer was never written
+    for r in range(world):
+        got = S[r].cpu().numpy()
+        for a, b in L.padding_ranges():
+            assert np.all(got[a:b] == -1)
+    for p in plans:
+        p.close()
+
+
+def _rank_main(rank, world, port, comm, queue):
+    import torch.distributed as dist
+    from gograd_b200.zero1 import Zero1AdamW
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank, comm=comm)
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+    norms = []
+    for step in (1, 2):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+        opt.step()
+        norms.append(opt.grad_norm())
+    torch.cuda.synchronize()
+    queue.put((rank, opt.lo, opt.master.cpu().numpy(), opt.m.cpu().numpy(), opt.v.cpu().numpy(),
+               opt.shadow_flat.view(torch.int16).cpu().numpy(), norms))
+    opt.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("comm", ["peer", "nccl"])
+def test_two_real_ranks(comm):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from gograd_b200.zero1 import ShardLayout
+    from oracle import oracle
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, comm, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    ref, want_norms = _oracle_run(world, 2)
+    L = ShardLayout(NUMELS, world)
+    flat = {k: np.zeros(L.total, np.float32) for k in "pmv"}
+    for rank, lo, master, m, v, shadow, norms in results:
+        flat["p"][lo:lo + master.size], flat["m"][lo:lo + m.size], flat["v"][lo:lo + v.size] = master, m, v
+        for a, b in zip(norms, want_norms):
+            assert abs(a - b) <= 1e-6 * b
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat["p"][o:o + n], ref.params[i]), f"p[{i}] ({comm})"
+        assert np.array_equal(flat["m"][o:o + n], ref.m[i]) and np.array_equal(flat["v"][o:o + n], ref.v[i])
+        want = oracle.f32_to_bf16(ref.params[i]).view(np.int16)
+        for rank, lo, master, m, v, shadow, norms in results:
+            assert np.array_equal(shadow[o:o + n], want), f"rank {rank} shadow[{i}] ({comm})"

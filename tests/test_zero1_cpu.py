@@ -1,0 +1,178 @@
+"""Host-side checks of the sharded step: layout and partition arithmetic, and a world-size-2
+run over gloo ranks on the CPU whose arithmetic is the oracle's. The sharded run must end
+bit-identical to an unsharded oracle run on the mean gradient."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+from gograd_b200.zero1 import ShardLayout, Zero1Schedule
+
+
+def test_layout_partition_properties():
+    rng = np.random.default_rng(0)
+    for world in (1, 2, 3, 4, 8):
+        for _ in range(20):
+            numels = [int(x) for x in rng.integers(1, 20000, size=int(rng.integers(1, 12)))]
+            L = ShardLayout(numels, world)
+            assert L.total == L.shard_len * world and L.shard_len % 4096 == 0 and L.total >= L.used
+            assert all(o % 8 == 0 for o in L.offsets)
+            covered = np.zeros(L.total, np.int32)
+            for r in range(world):
+                lo, hi = L.shard_range(r)
+                for pc in L.pieces(r):
+                    assert lo <= pc.flat_offset and pc.flat_offset + pc.length <= hi
+                    assert pc.flat_offset == L.offsets[pc.tensor] + pc.tensor_offset
+                    assert pc.flat_offset % 8 == 0, "every piece keeps 128-bit alignment of fp32 and bf16"
+                    covered[pc.flat_offset:pc.flat_offset + pc.length] += 1
+            for a, b in L.padding_ranges():
+                assert np.all(covered[a:b] == 0)
+                covered[a:b] -= 1
+            assert np.all(np.abs(covered) == 1), "every element is owned exactly once or is padding"
+            per_tensor = [0] * len(numels)
+            for r in range(world):
+                for pc in L.pieces(r):
+                    per_tensor[pc.tensor] += pc.length
+            assert per_tensor == numels
+
+
+def test_layout_8b_set_uses_64_bit_offsets():
+    from gograd_b200 import paramsets
+    ps = paramsets.get("llama8b")
+    L = ShardLayout([s.numel for s in ps.params], 8)
+    assert L.used >= ps.numel and L.total > 2 ** 32 and L.shard_len == 1_003_786_240
+    assert sum(pc.length for r in range(8) for pc in L.pieces(r)) == ps.numel
+    with pytest.raises(ValueError):
+        ShardLayout([4, 0], 2)
+    with pytest.raises(ValueError):
+        ShardLayout([4], 0)
+
+
+class OracleRank(Zero1Schedule):
+    """A gloo rank whose arithmetic is the CPU oracle (test infrastructure)."""
+
+    def __init__(self, numels, group_of, hp, rank, world, dist, weights):
+        super().__init__(numels, group_of, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], hp["max_norm"], rank, world)
+        import torch
+        self.dist, self.torch = dist, torch
+        L = self.layout
+        self.grad_flat = np.zeros(L.total, np.float32)
+        self.shadow_flat = np.zeros(L.total, np.uint16)
+        flat = np.zeros(L.total, np.float32)
+        for o, w in zip(L.offsets, weights):
+            flat[o:o + w.size] = w
+        self.master = flat[self.lo:self.hi].copy()
+        self.m = np.zeros(L.shard_len, np.float32)
+        self.v = np.zeros(L.shard_len, np.float32)
+        self.norm = 0.0
+
+    def reduce_grads(self):
+        t = self.torch.from_numpy(self.grad_flat.copy())
+        self.dist.all_reduce(t)                     # two ranks: g0 + g1, commutative, one rounding
+        mean = (t.numpy() * np.float32(1.0 / self.world)).astype(np.float32)
+        self.grad_flat[self.lo:self.hi] = mean[self.lo:self.hi]
+        from oracle import oracle
+        self.sumsq = oracle.sum_squares([self.grad_flat[self.lo:self.hi]])
+
+    def combine_sumsq(self):
+        t = self.torch.tensor([self.sumsq], dtype=self.torch.float64)
+        self.dist.all_reduce(t)
+        self.norm = np.float32(np.sqrt(float(t.item())))
+
+    def update(self):
+        from oracle import oracle
+        coef = oracle.clip_coefficient(float(self.norm), self.max_norm)
+        bc1, bc2 = self.bias_corrections()
+        for pc in self.my_pieces:
+            a, b = pc.flat_offset - self.lo, pc.flat_offset - self.lo + pc.length
+            g = self.grad_flat[pc.flat_offset:pc.flat_offset + pc.length].copy()
+            oracle.scale_(g, float(coef))
+            scale, decay = self.group_of[pc.tensor]
+            step, dec = oracle.C.c_float(), oracle.C.c_float()
+            oracle.lib().oracle_adamw_group_scale(self.lr, scale, decay, step, dec)
+            p, m, v = self.master[a:b], self.m[a:b], self.v[a:b]
+            oracle.lib().oracle_adamw_update(oracle._ptr(p), oracle._ptr(g), oracle._ptr(m), oracle._ptr(v), p.size,
+                                             self.beta1, self.beta2, self.eps, step.value, dec.value, bc1, bc2)
+            self.shadow_flat[pc.flat_offset:pc.flat_offset + pc.length] = oracle.f32_to_bf16(p)
+
+    def gather_shadows(self):
+        mine = self.torch.from_numpy(self.shadow_flat[self.lo:self.hi].astype(np.int32))
+        out = [self.torch.zeros_like(mine) for _ in range(self.world)]
+        self.dist.all_gather(out, mine)
+        self.shadow_flat[:] = np.concatenate([x.numpy() for x in out]).astype(np.uint16)
+
+
+NUMELS = [5000, 3, 4097, 12, 7001]
+GROUPS = [(1.0, 0.1), (1.0, 0.0), (0.5, 0.1), (1.0, 0.0), (1.0, 0.1)]
+HP = dict(lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8, max_norm=0.01)
+
+
+def _inputs(rank, step):
+    rng = np.random.default_rng(1000 * step + rank)
+    return [rng.normal(0, 1e-3, n).astype(np.float32) for n in NUMELS]
+
+
+def _weights():
+    rng = np.random.default_rng(77)
+    return [rng.normal(0, 0.02, n).astype(np.float32) for n in NUMELS]
+
+
+def _worker(rank, world, port, queue):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    opt = OracleRank(NUMELS, GROUPS, HP, rank, world, dist, _weights())
+    norms = []
+    for step in range(1, 4):
+        opt.grad_flat[:] = 0
+        for o, g in zip(opt.layout.offsets, _inputs(rank, step)):
+            opt.grad_flat[o:o + g.size] = g
+        opt.step()
+        norms.append(float(opt.norm))
+    queue.put((rank, opt.lo, opt.master.copy(), opt.m.copy(), opt.v.copy(), opt.shadow_flat.copy(), norms))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_match_unsharded_oracle():
+    import torch.multiprocessing as mp
+    from oracle import oracle
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=120) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    # unsharded oracle on the mean gradient
+    weights = _weights()
+    groups = [oracle.Group(f"g{i}", [i], s, d) for i, (s, d) in enumerate(GROUPS)]
+    ref = oracle.OracleAdamW([w.copy() for w in weights], lr=HP["lr"], groups=groups, beta1=HP["beta1"],
+                             beta2=HP["beta2"], eps=HP["eps"])
+    want_norms = []
+    for step in range(1, 4):
+        g0, g1 = _inputs(0, step), _inputs(1, step)
+        mean = [((a + b) * np.float32(0.5)).astype(np.float32) for a, b in zip(g0, g1)]
+        norm, _ = oracle.clip_grad_norm(mean, HP["max_norm"])
+        want_norms.append(float(norm))
+        ref.step(mean)
+    L = ShardLayout(NUMELS, world)
+    flat_p = np.zeros(L.total, np.float32)
+    flat_m = np.zeros(L.total, np.float32)
+    flat_v = np.zeros(L.total, np.float32)
+    for rank, lo, master, m, v, shadow, norms in results:
+        flat_p[lo:lo + master.size], flat_m[lo:lo + m.size], flat_v[lo:lo + v.size] = master, m, v
+        for a, b in zip(norms, want_norms):
+            assert abs(a - b) <= 1e-6 * b
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat_p[o:o + n], ref.params[i]), f"p[{i}]"
+        assert np.array_equal(flat_m[o:o + n], ref.m[i]) and np.array_equal(flat_v[o:o + n], ref.v[i])
+        for rank, lo, master, m, v, shadow, norms in results:
+            assert np.array_equal(shadow[o:o + n], oracle.f32_to_bf16(ref.params[i])), f"rank {rank} shadow[{i}]"
