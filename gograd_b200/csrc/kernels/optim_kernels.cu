@@ -527,7 +527,7 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
 // writes before it writes it, and no other rank reads that range of this buffer.
 // No flag or barrier is waited on here; ordering against the other ranks is the host's
 // job (stream-ordered collectives before and after).
-template <int NP>
+template <int NP, int U>
 __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
                                                     float* __restrict__ out, oe_dev_norm* rec, double* partials) {
     __shared__ double warp_sums[OE_THREADS / 32];
@@ -545,17 +545,19 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
     if (aligned) {
         const uint64_t nvec = numel >> 2;
         float4* o4 = (float4*)out;
-        for (uint64_t i0 = tid; i0 < nvec; i0 += 2 * stride) {
-            float4 v[2][NP];
+        // U x n 128-bit loads are issued before the first add: a remote load takes a few
+        // microseconds, so bytes in flight per SM decide the NVLink throughput.
+        for (uint64_t i0 = tid; i0 < nvec; i0 += U * stride) {
+            float4 v[U][NP];
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
+            for (int u = 0; u < U; u++) {
                 const uint64_t i = i0 + u * stride;
 #pragma unroll
                 for (int k = 0; k < NP; k++)
                     if (k < (int)n && i < nvec) v[u][k] = __ldcs((const float4*)((const float*)pg.base[k] + first) + i);
             }
 #pragma unroll
-            for (int u = 0; u < 2; u++) {
+            for (int u = 0; u < U; u++) {
                 const uint64_t i = i0 + u * stride;
                 if (i < nvec) {
                     float4 s = v[u][0];
@@ -611,11 +613,11 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
     }
 }
 
-#define OE_PEER_REDUCE_VARIANT(name, np)                                                               \
+#define OE_PEER_REDUCE_VARIANT(name, np, unroll)                                                               \
     extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)                                       \
     name(const __grid_constant__ oe_peer_grads pg, uint64_t first, uint64_t numel, float* out, oe_dev_norm* rec, double* partials) { \
-        oe_peer_reduce_body<np>(pg, first, numel, out, rec, partials);                                \
+        oe_peer_reduce_body<np, unroll>(pg, first, numel, out, rec, partials);                             \
     }
-OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2)
-OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4)
-OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n8, 8)
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2, 8)
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4, 4)
+OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n8, 8, 2)

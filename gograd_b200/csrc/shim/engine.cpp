@@ -876,7 +876,7 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     CtxGuard guard(d, dc->ctx);
     int which = n_ranks <= 2 ? 0 : n_ranks <= 4 ? 1 : 2;
     static const char* const names[3] = {"oe_peer_reduce_sumsq_n2", "oe_peer_reduce_sumsq_n4", "oe_peer_reduce_sumsq_n8"};
-    uint64_t vec_threads = (numel / 4 + 1) / 2 + 1;
+    uint64_t vec_threads = numel / 4 / 2 + 1;
     uint64_t blocks = (vec_threads + kThreads - 1) / kThreads;
     uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_peer_reduce[which] > 0 ? dc->occ_peer_reduce[which] : 1);
     uint64_t grid = blocks < persistent ? blocks : persistent;
