@@ -1,0 +1,400 @@
+"""ctypes binding of libgograd_host.so: the C++ host mirror of gograd's optimizer surface.
+
+Names follow the reference (``NewAdamW``, ``NewSGDGroups``, ``ClipGradNorm``, ...). All logic
+lives in C++ (gograd_b200/csrc/host); this file only marshals arguments. Errors — the
+mirror's counterpart of a Go error value or panic — raise ``HostError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import os
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libgograd_host.so")
+_lib = None
+_f32p = C.POINTER(C.c_float)
+
+
+class HostError(RuntimeError):
+    pass
+
+
+class _SGDOptions(C.Structure):
+    _fields_ = [("lr", C.c_float), ("momentum", C.c_float), ("dampening", C.c_float), ("weight_decay", C.c_float),
+                ("nesterov", C.c_int32), ("maximize", C.c_int32)]
+
+
+class _OneCycle(C.Structure):
+    _fields_ = [("max_lr", C.c_double), ("pct_start", C.c_double), ("div_factor", C.c_double),
+                ("final_div_factor", C.c_double), ("total", C.c_int32), ("step_count", C.c_int32)]
+
+
+class _Groups(C.Structure):
+    _fields_ = [("n_groups", C.c_int32), ("group_names", C.POINTER(C.c_char_p)), ("offsets", C.POINTER(C.c_int32)),
+                ("members", C.POINTER(C.c_int32)), ("lr_scales", _f32p), ("decays", _f32p)]
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(f"{LIB_PATH} is missing: build it with `make -C gograd_b200/csrc`")
+        from . import _lib as engine_lib
+        engine_lib.lib()  # liboptengine.so first (the host library links against it)
+        h = C.CDLL(LIB_PATH)
+        h.gg_last_error.restype = C.c_char_p
+        h.gg_tensor_numel.restype = C.c_int64
+        h.gg_opt_step_count.restype = C.c_int64
+        h.gg_tensor_address.restype = C.c_uint64
+        h.gg_tensor_free.restype = None
+        h.gg_opt_free.restype = None
+        h.gg_release_clip_state.restype = None
+        _lib = h
+    return _lib
+
+
+def _check(rc: int) -> None:
+    if rc != 0:
+        raise HostError(lib().gg_last_error().decode("utf-8", "replace"))
+
+
+def _f(x: float):
+    return C.byref(C.c_float(x))
+
+
+class Tensor:
+    """A contiguous float32 CUDA leaf (autograd.Tensor as the optimizer path sees it)."""
+
+    def __init__(self, values, shape: Optional[Sequence[int]] = None, device: int = 0, requires_grad: bool = True):
+        v = np.ascontiguousarray(values, np.float32).reshape(-1)
+        shape = list(shape) if shape is not None else [v.size]
+        self.shape = shape
+        self._h = C.c_void_p()
+        arr = (C.c_int32 * max(len(shape), 1))(*shape)
+        _check(lib().gg_tensor_new(v.ctypes.data_as(_f32p), arr, len(shape), device, int(requires_grad), C.byref(self._h)))
+
+    @property
+    def numel(self) -> int:
+        return int(lib().gg_tensor_numel(self._h))
+
+    def to_host(self) -> np.ndarray:
+        out = np.empty(self.numel, np.float32)
+        _check(lib().gg_tensor_to_host(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def copy_from_host(self, values) -> None:
+        v = np.ascontiguousarray(values, np.float32).reshape(-1)
+        assert v.size == self.numel
+        _check(lib().gg_tensor_copy_from_host(self._h, v.ctypes.data_as(C.c_void_p)))
+
+    @property
+    def has_grad(self) -> bool:
+        return bool(lib().gg_tensor_has_grad(self._h))
+
+    def set_grad(self, values) -> None:
+        """None makes the gradient absent (a nil gradBuf)."""
+        if values is None:
+            _check(lib().gg_tensor_set_grad(self._h, None))
+            return
+        v = np.ascontiguousarray(values, np.float32).reshape(-1)
+        assert v.size == self.numel
+        _check(lib().gg_tensor_set_grad(self._h, v.ctypes.data_as(C.c_void_p)))
+
+    def ensure_grad(self) -> None:
+        _check(lib().gg_tensor_ensure_grad(self._h))
+
+    def grad_to_host(self) -> np.ndarray:
+        out = np.empty(self.numel, np.float32)
+        _check(lib().gg_tensor_grad_to_host(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def shadow_to_host(self) -> np.ndarray:
+        out = np.empty(self.numel, np.uint16)
+        _check(lib().gg_tensor_shadow_to_host(self._h, out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    @property
+    def shadow_current(self) -> bool:
+        return bool(lib().gg_tensor_shadow_current(self._h))
+
+    def address(self, which: int = 0) -> int:
+        return int(lib().gg_tensor_address(self._h, which))
+
+    def close(self) -> None:
+        if self._h:
+            lib().gg_tensor_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+@dataclass
+class Parameter:
+    Name: str
+    Value: Optional[Tensor]
+
+
+@dataclass
+class ParameterGroupSpec:
+    Name: str
+    Params: List[Parameter]
+    LRScale: float = 0.0
+    WeightDecay: float = 0.0
+
+
+@dataclass
+class SGDOptions:
+    LR: float = 0.0
+    Momentum: float = 0.0
+    Dampening: float = 0.0
+    WeightDecay: float = 0.0
+    Nesterov: bool = False
+    Maximize: bool = False
+
+    def to_c(self) -> _SGDOptions:
+        return _SGDOptions(self.LR, self.Momentum, self.Dampening, self.WeightDecay, int(self.Nesterov), int(self.Maximize))
+
+
+def _param_arrays(params: Sequence[Parameter]):
+    n = len(params)
+    names = (C.c_char_p * max(n, 1))(*[p.Name.encode() for p in params])
+    handles = (C.c_void_p * max(n, 1))(*[(p.Value._h if p.Value is not None else None) for p in params])
+    return names, handles, n
+
+
+def _groups_struct(params: Sequence[Parameter], specs: Sequence[ParameterGroupSpec]):
+    index_of = {id(p.Value): i for i, p in enumerate(params) if p.Value is not None}
+    names = (C.c_char_p * max(len(specs), 1))(*[s.Name.encode() for s in specs])
+    offsets, members = [0], []
+    for s in specs:
+        for p in s.Params:
+            members.append(index_of.get(id(p.Value), -1))  # -1: a tensor the optimizer does not own
+        offsets.append(len(members))
+    off = (C.c_int32 * len(offsets))(*offsets)
+    mem = (C.c_int32 * max(len(members), 1))(*members)
+    scales = (C.c_float * max(len(specs), 1))(*[s.LRScale for s in specs])
+    decays = (C.c_float * max(len(specs), 1))(*[s.WeightDecay for s in specs])
+    g = _Groups(len(specs), names, off, mem, scales, decays)
+    g._keep = (names, off, mem, scales, decays)
+    return g
+
+
+class _Optimizer:
+    def __init__(self, handle, params):
+        self._h = handle
+        self.Params = list(params)
+
+    def Step(self) -> None:
+        _check(lib().gg_opt_step(self._h))
+
+    def StepClipped(self, max_norm: float) -> None:
+        _check(lib().gg_opt_step_clipped(self._h, _f(max_norm)))
+
+    def LastGradNorm(self) -> float:
+        out = C.c_float()
+        _check(lib().gg_opt_last_norm(self._h, C.byref(out)))
+        return out.value
+
+    def ZeroGrad(self) -> None:
+        _check(lib().gg_opt_zero_grad(self._h))
+
+    def LearningRate(self) -> float:
+        out = C.c_float()
+        _check(lib().gg_opt_get_lr(self._h, C.byref(out)))
+        return out.value
+
+    def SetLearningRate(self, lr: float) -> None:
+        _check(lib().gg_opt_set_lr(self._h, _f(lr)))
+
+    @property
+    def StepCount(self) -> int:
+        return int(lib().gg_opt_step_count(self._h))
+
+    def SetEngine(self, write_shadow: bool = False, clip_devform: bool = False) -> None:
+        _check(lib().gg_opt_set_engine(self._h, int(write_shadow), int(clip_devform)))
+
+    def groupScale(self, index: int):
+        a, b = C.c_float(), C.c_float()
+        _check(lib().gg_opt_group_scale(self._h, index, C.byref(a), C.byref(b)))
+        return np.float32(a.value), np.float32(b.value)
+
+    def _state(self, index: int, which: int):
+        n = self.Params[index].Value.numel
+        out = np.zeros(n, np.float32)
+        flag = C.c_int32()
+        _check(lib().gg_opt_state(self._h, index, which, out.ctypes.data_as(_f32p), C.byref(flag)))
+        return out, bool(flag.value)
+
+    def SaveSafeTensors(self, path: str) -> None:
+        _check(lib().gg_opt_save(self._h, path.encode()))
+
+    def LoadSafeTensors(self, path: str) -> None:
+        _check(lib().gg_opt_load(self._h, path.encode()))
+
+    def Close(self) -> None:
+        _check(lib().gg_opt_close(self._h))
+
+    def __del__(self):
+        try:
+            if self._h:
+                lib().gg_opt_free(self._h)
+                self._h = None
+        except Exception:
+            pass
+
+
+class AdamW(_Optimizer):
+    def M(self, index: int) -> np.ndarray:
+        return self._state(index, 0)[0]
+
+    def V(self, index: int) -> np.ndarray:
+        return self._state(index, 1)[0]
+
+    def SetConfig(self, beta1: Optional[float] = None, beta2: Optional[float] = None, eps: Optional[float] = None):
+        _check(lib().gg_adamw_set_config(self._h, None if beta1 is None else _f(beta1),
+                                         None if beta2 is None else _f(beta2), None if eps is None else _f(eps)))
+
+    def PrepareGraph(self) -> None:
+        _check(lib().gg_adamw_prepare_graph(self._h))
+
+    def StepCaptured(self) -> None:
+        _check(lib().gg_adamw_step_captured(self._h))
+
+    def GraphStepCount(self) -> int:
+        out = C.c_int32()
+        _check(lib().gg_adamw_graph_step_count(self._h, C.byref(out)))
+        return out.value
+
+
+class SGD(_Optimizer):
+    def Buffer(self, index: int):
+        """(momentum buffer, initialised flag) of one parameter."""
+        return self._state(index, 2)
+
+
+def NewAdamW(params: Sequence[Parameter], lr: float, decay: float) -> AdamW:
+    names, handles, n = _param_arrays(params)
+    h = C.c_void_p()
+    _check(lib().gg_adamw_new(names, handles, n, _f(lr), _f(decay), C.byref(h)))
+    return AdamW(h, params)
+
+
+def NewAdamWGroups(params: Sequence[Parameter], lr: float, specs: Sequence[ParameterGroupSpec]) -> AdamW:
+    names, handles, n = _param_arrays(params)
+    g = _groups_struct(params, specs)
+    h = C.c_void_p()
+    _check(lib().gg_adamw_new_groups(names, handles, n, _f(lr), C.byref(g), C.byref(h)))
+    return AdamW(h, params)
+
+
+def NewSGD(params: Sequence[Parameter], options: SGDOptions) -> SGD:
+    names, handles, n = _param_arrays(params)
+    o = options.to_c()
+    h = C.c_void_p()
+    _check(lib().gg_sgd_new(names, handles, n, C.byref(o), C.byref(h)))
+    return SGD(h, params)
+
+
+def NewSGDGroups(params: Sequence[Parameter], options: SGDOptions, specs: Sequence[ParameterGroupSpec]) -> SGD:
+    names, handles, n = _param_arrays(params)
+    g = _groups_struct(params, specs)
+    o = options.to_c()
+    h = C.c_void_p()
+    _check(lib().gg_sgd_new_groups(names, handles, n, C.byref(o), C.byref(g), C.byref(h)))
+    return SGD(h, params)
+
+
+def ClipGradNorm(params: Sequence[Parameter], max_norm: float) -> float:
+    """Scales the present gradients in place on the device; returns NaN like the reference
+    (the norm stays on the device, read it with GradientNormToHost)."""
+    handles = (C.c_void_p * max(len(params), 1))(*[p.Value._h for p in params])
+    _check(lib().gg_clip_grad_norm(handles, len(params), _f(max_norm)))
+    return float("nan")
+
+
+def GradientNormToHost() -> float:
+    out = C.c_float()
+    _check(lib().gg_gradient_norm_to_host(C.byref(out)))
+    return out.value
+
+
+def ReleaseClipState() -> None:
+    lib().gg_release_clip_state()
+
+
+class OneCycle:
+    def __init__(self, max_lr: float, total: int, pct_start: float):
+        self._c = _OneCycle()
+        _check(lib().gg_onecycle_new(C.byref(C.c_double(max_lr)), total, C.byref(C.c_double(pct_start)), C.byref(self._c)))
+
+    @property
+    def StepCount(self) -> int:
+        return self._c.step_count
+
+    @StepCount.setter
+    def StepCount(self, v: int) -> None:
+        self._c.step_count = v
+
+    def LR(self) -> float:
+        out = C.c_double()
+        _check(lib().gg_onecycle_lr(C.byref(self._c), C.byref(out)))
+        return out.value
+
+    def Step(self, optimizer: _Optimizer) -> None:
+        _check(lib().gg_onecycle_step(C.byref(self._c), optimizer._h))
+
+    def fields(self):
+        c = self._c
+        return (c.max_lr, c.pct_start, c.div_factor, c.final_div_factor, c.total, c.step_count)
+
+
+def SaveTrainingCheckpoint(path: str, model: Sequence[Parameter], optimizer: _Optimizer, scheduler: OneCycle,
+                           metadata: Optional[Dict[str, str]] = None) -> None:
+    names, handles, n = _param_arrays(model)
+    metadata = metadata or {}
+    keys = (C.c_char_p * max(len(metadata), 1))(*[k.encode() for k in metadata])
+    vals = (C.c_char_p * max(len(metadata), 1))(*[v.encode() for v in metadata.values()])
+    _check(lib().gg_save_training_checkpoint(path.encode(), names, handles, n, optimizer._h, C.byref(scheduler._c),
+                                             keys, vals, len(metadata)))
+
+
+def LoadTrainingCheckpoint(path: str, model: Sequence[Parameter], optimizer: _Optimizer, scheduler: OneCycle) -> Dict[str, str]:
+    names, handles, n = _param_arrays(model)
+    buf = C.create_string_buffer(1 << 16)
+    _check(lib().gg_load_training_checkpoint(path.encode(), names, handles, n, optimizer._h, C.byref(scheduler._c), buf,
+                                             len(buf)))
+    return json.loads(buf.value.decode() or "{}")
+
+
+def safetensors_write(path: str, entries: Dict[str, np.ndarray], metadata: Optional[Dict[str, str]]) -> None:
+    """Host-only: writes float32 entries in the reference's container layout."""
+    names = list(entries)
+    arrays = [np.require(entries[k], np.float32, "C") for k in names]
+    c_names = (C.c_char_p * max(len(names), 1))(*[k.encode() for k in names])
+    c_data = (_f32p * max(len(names), 1))(*[a.ctypes.data_as(_f32p) for a in arrays])
+    shapes, offsets = [], [0]
+    for a in arrays:
+        shapes += list(a.shape)
+        offsets.append(len(shapes))
+    c_shapes = (C.c_int32 * max(len(shapes), 1))(*shapes)
+    c_off = (C.c_int32 * len(offsets))(*offsets)
+    md = metadata or {}
+    keys = (C.c_char_p * max(len(md), 1))(*[k.encode() for k in md])
+    vals = (C.c_char_p * max(len(md), 1))(*[v.encode() for v in md.values()])
+    _check(lib().gg_safetensors_write(path.encode(), c_names, c_data, c_shapes, c_off, len(names), keys, vals,
+                                      len(md) if metadata is not None else -1))
+
+
+def safetensors_describe(path: str) -> dict:
+    buf = C.create_string_buffer(1 << 20)
+    _check(lib().gg_safetensors_describe(path.encode(), buf, len(buf)))
+    return json.loads(buf.value.decode())

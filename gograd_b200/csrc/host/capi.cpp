@@ -1,0 +1,515 @@
+// Flat C handle API (include/gograd_host.h) over the C++ host mirror. Exceptions — the
+// mirror's counterpart of a Go panic — are turned into error codes here.
+#include <cstring>
+#include <functional>
+
+#include "../../../include/gograd_host.h"
+#include "autograd.hpp"
+
+using namespace autograd;
+
+struct gg_tensor {
+    std::shared_ptr<Tensor> t;
+};
+
+struct gg_optimizer {
+    std::unique_ptr<AdamW> adamw;
+    std::unique_ptr<SGD> sgd;
+    CheckpointOptimizer* base() { return adamw ? (CheckpointOptimizer*)adamw.get() : (CheckpointOptimizer*)sgd.get(); }
+    const CheckpointOptimizer* base() const {
+        return adamw ? (const CheckpointOptimizer*)adamw.get() : (const CheckpointOptimizer*)sgd.get();
+    }
+};
+
+namespace {
+thread_local std::string t_err;
+
+int fail(const std::string& message) {
+    t_err = message;
+    return 1;
+}
+
+int guarded(const std::function<std::string()>& fn) {
+    try {
+        std::string e = fn();
+        if (e.empty()) return 0;
+        return fail(e);
+    } catch (const std::exception& ex) {
+        return fail(ex.what());
+    }
+}
+
+std::vector<Parameter> make_params(const char* const* names, gg_tensor* const* tensors, int32_t n) {
+    std::vector<Parameter> params;
+    for (int32_t i = 0; i < n; i++) {
+        Parameter p;
+        p.Name = names && names[i] ? names[i] : "";
+        p.Value = tensors && tensors[i] ? tensors[i]->t : nullptr;
+        params.push_back(p);
+    }
+    return params;
+}
+
+std::vector<ParameterGroupSpec> make_specs(const std::vector<Parameter>& params, const gg_groups* g) {
+    std::vector<ParameterGroupSpec> specs;
+    if (!g) return specs;
+    for (int32_t i = 0; i < g->n_groups; i++) {
+        ParameterGroupSpec s;
+        s.Name = g->group_names[i] ? g->group_names[i] : "";
+        for (int32_t k = g->offsets[i]; k < g->offsets[i + 1]; k++) {
+            int32_t index = g->members[k];
+            if (index >= 0 && index < (int32_t)params.size()) {
+                s.Params.push_back(params[(size_t)index]);
+            } else {
+                Parameter stranger;  // a parameter the optimizer does not own
+                stranger.Name = "?";
+                stranger.Value = std::make_shared<Tensor>();
+                s.Params.push_back(stranger);
+            }
+        }
+        s.LRScale = g->lr_scales[i];
+        s.WeightDecay = g->decays[i];
+        specs.push_back(s);
+    }
+    return specs;
+}
+}  // namespace
+
+extern "C" {
+
+const char* gg_last_error(void) { return t_err.c_str(); }
+
+int gg_tensor_new(const float* values, const int32_t* shape, int32_t rank, int32_t device, int32_t requires_grad,
+                  gg_tensor** out) {
+    if (!out) return fail("out is NULL");
+    *out = nullptr;
+    return guarded([&]() -> std::string {
+        std::vector<int> s(shape, shape + rank);
+        long long n = 1;
+        for (int d : s) n *= d;
+        if (n < 0) return "autograd: negative dimension";
+        std::vector<float> v(values, values + n);
+        auto h = new gg_tensor();
+        std::string e = Tensor::New(v, s, device, requires_grad != 0, &h->t);
+        if (!e.empty()) {
+            delete h;
+            return e;
+        }
+        *out = h;
+        return "";
+    });
+}
+
+void gg_tensor_free(gg_tensor* t) { delete t; }
+int64_t gg_tensor_numel(const gg_tensor* t) { return t ? t->t->Numel() : -1; }
+
+int gg_tensor_to_host(const gg_tensor* t, float* out) {
+    return guarded([&]() -> std::string {
+        std::vector<float> v;
+        std::string e = t->t->ToHost(&v);
+        if (e.empty() && !v.empty()) memcpy(out, v.data(), v.size() * 4);
+        return e;
+    });
+}
+
+int gg_tensor_copy_from_host(gg_tensor* t, const float* values) {
+    return guarded([&]() { return t->t->CopyFromHost(std::vector<float>(values, values + t->t->Numel())); });
+}
+
+int gg_tensor_has_grad(const gg_tensor* t) { return t && t->t->gradBuf != 0 ? 1 : 0; }
+
+int gg_tensor_set_grad(gg_tensor* t, const float* values) {
+    return guarded([&]() -> std::string {
+        if (!values) {
+            t->t->FreeGrad();
+            return "";
+        }
+        return t->t->SetGrad(std::vector<float>(values, values + t->t->Numel()));
+    });
+}
+
+int gg_tensor_ensure_grad(gg_tensor* t) {
+    return guarded([&]() { return t->t->EnsureGrad(); });
+}
+
+int gg_tensor_grad_to_host(const gg_tensor* t, float* out) {
+    return guarded([&]() -> std::string {
+        std::vector<float> v;
+        std::string e = t->t->GradToHost(&v);
+        if (e.empty() && !v.empty()) memcpy(out, v.data(), v.size() * 4);
+        return e;
+    });
+}
+
+int gg_tensor_shadow_to_host(const gg_tensor* t, uint16_t* out) {
+    return guarded([&]() -> std::string {
+        std::vector<uint16_t> v;
+        std::string e = t->t->ShadowToHost(&v);
+        if (e.empty() && !v.empty()) memcpy(out, v.data(), v.size() * 2);
+        return e;
+    });
+}
+
+int gg_tensor_shadow_current(const gg_tensor* t) { return t && t->t->ShadowCurrent() ? 1 : 0; }
+
+uint64_t gg_tensor_address(const gg_tensor* t, int32_t which) {
+    if (!t) return 0;
+    return which == 0 ? t->t->buf : which == 1 ? t->t->gradBuf : t->t->bf16Buf;
+}
+
+int gg_adamw_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr, const float* decay,
+                 gg_optimizer** out) {
+    if (!out || !lr || !decay) return fail("NULL argument");
+    *out = nullptr;
+    return guarded([&]() -> std::string {
+        auto h = new gg_optimizer();
+        std::string e = AdamW::New(make_params(names, tensors, n), *lr, *decay, &h->adamw);
+        if (!e.empty()) {
+            delete h;
+            return e;
+        }
+        *out = h;
+        return "";
+    });
+}
+
+int gg_adamw_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr,
+                        const gg_groups* groups, gg_optimizer** out) {
+    if (!out || !lr) return fail("NULL argument");
+    *out = nullptr;
+    return guarded([&]() -> std::string {
+        auto params = make_params(names, tensors, n);
+        auto h = new gg_optimizer();
+        std::string e = AdamW::NewGroups(params, *lr, make_specs(params, groups), &h->adamw);
+        if (!e.empty()) {
+            delete h;
+            return e;
+        }
+        *out = h;
+        return "";
+    });
+}
+
+int gg_adamw_set_config(gg_optimizer* o, const float* beta1, const float* beta2, const float* eps) {
+    if (!o || !o->adamw) return fail("not an AdamW optimizer");
+    if (beta1) o->adamw->Beta1 = *beta1;
+    if (beta2) o->adamw->Beta2 = *beta2;
+    if (eps) o->adamw->Eps = *eps;
+    return 0;
+}
+
+static SGDOptions to_options(const gg_sgd_options* x) {
+    SGDOptions o;
+    o.LR = x->lr;
+    o.Momentum = x->momentum;
+    o.Dampening = x->dampening;
+    o.WeightDecay = x->weight_decay;
+    o.Nesterov = x->nesterov != 0;
+    o.Maximize = x->maximize != 0;
+    return o;
+}
+
+int gg_sgd_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const gg_sgd_options* options,
+               gg_optimizer** out) {
+    if (!out || !options) return fail("NULL argument");
+    *out = nullptr;
+    return guarded([&]() -> std::string {
+        auto h = new gg_optimizer();
+        std::string e = SGD::New(make_params(names, tensors, n), to_options(options), &h->sgd);
+        if (!e.empty()) {
+            delete h;
+            return e;
+        }
+        *out = h;
+        return "";
+    });
+}
+
+int gg_sgd_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n, const gg_sgd_options* options,
+                      const gg_groups* groups, gg_optimizer** out) {
+    if (!out || !options) return fail("NULL argument");
+    *out = nullptr;
+    return guarded([&]() -> std::string {
+        auto params = make_params(names, tensors, n);
+        auto specs = make_specs(params, groups);
+        if (specs.empty()) return "autograd: NewSGDGroups needs at least one parameter group";
+        auto h = new gg_optimizer();
+        std::string e = SGD::NewGroups(params, to_options(options), specs, &h->sgd);
+        if (!e.empty()) {
+            delete h;
+            return e;
+        }
+        *out = h;
+        return "";
+    });
+}
+
+int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devform) {
+    if (!o) return fail("optimizer is NULL");
+    EngineOptions& e = o->adamw ? o->adamw->Engine : o->sgd->Engine;
+    e.WriteShadow = write_shadow != 0;
+    e.ClipDevForm = clip_devform != 0;
+    return 0;
+}
+
+int gg_opt_step(gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        o->base()->Step();
+        return "";
+    });
+}
+
+int gg_opt_step_clipped(gg_optimizer* o, const float* max_norm) {
+    return guarded([&]() -> std::string {
+        if (o->adamw)
+            o->adamw->StepClipped(*max_norm);
+        else
+            o->sgd->StepClipped(*max_norm);
+        return "";
+    });
+}
+
+int gg_opt_last_norm(gg_optimizer* o, float* out) {
+    return guarded([&]() -> std::string {
+        if (!o->adamw) return "only AdamW keeps the norm of its last clipped step";
+        *out = o->adamw->LastGradNorm();
+        return "";
+    });
+}
+
+int gg_opt_zero_grad(gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        o->base()->ZeroGrad();
+        return "";
+    });
+}
+
+int gg_opt_get_lr(const gg_optimizer* o, float* out) {
+    *out = o->base()->LearningRate();
+    return 0;
+}
+
+int gg_opt_set_lr(gg_optimizer* o, const float* lr) {
+    return guarded([&]() -> std::string {
+        o->base()->SetLearningRate(*lr);
+        return "";
+    });
+}
+
+int64_t gg_opt_step_count(const gg_optimizer* o) { return o->adamw ? o->adamw->StepCount : o->sgd->StepCount; }
+
+int gg_opt_close(gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        o->base()->Close();
+        return "";
+    });
+}
+
+void gg_opt_free(gg_optimizer* o) { delete o; }
+
+int gg_opt_state(gg_optimizer* o, int32_t index, int32_t which, float* out, int32_t* initialized) {
+    return guarded([&]() -> std::string {
+        if (o->adamw) {
+            OptimizerState s;
+            std::string e = o->adamw->State(&s);
+            if (!e.empty()) return e;
+            if (index < 0 || index >= (int32_t)s.Moments.size() || which < 0 || which > 1) return "state index out of range";
+            const std::vector<float>& v = which == 0 ? s.Moments[(size_t)index].M : s.Moments[(size_t)index].V;
+            if (out && !v.empty()) memcpy(out, v.data(), v.size() * 4);
+            if (initialized) *initialized = 1;
+            return "";
+        }
+        SGDState s;
+        std::string e = o->sgd->State(&s);
+        if (!e.empty()) return e;
+        if (index < 0 || index >= (int32_t)s.Buffers.size() || which != 2) return "state index out of range";
+        if (initialized) *initialized = s.Initialized[(size_t)index] ? 1 : 0;
+        if (out && !s.Buffers[(size_t)index].empty()) memcpy(out, s.Buffers[(size_t)index].data(), s.Buffers[(size_t)index].size() * 4);
+        return "";
+    });
+}
+
+int gg_opt_group_scale(const gg_optimizer* o, int32_t index, float* step_size, float* decay) {
+    if (o->adamw)
+        o->adamw->groupScale(index, step_size, decay);
+    else
+        o->sgd->groupScale(index, step_size, decay);
+    return 0;
+}
+
+int gg_opt_save(gg_optimizer* o, const char* path) {
+    return guarded([&]() { return o->adamw ? o->adamw->SaveSafeTensors(path) : o->sgd->SaveSafeTensors(path); });
+}
+
+int gg_opt_load(gg_optimizer* o, const char* path) {
+    return guarded([&]() { return o->adamw ? o->adamw->LoadSafeTensors(path) : o->sgd->LoadSafeTensors(path); });
+}
+
+int gg_adamw_prepare_graph(gg_optimizer* o) {
+    return guarded([&]() -> std::string { return o->adamw ? o->adamw->PrepareGraph() : "not an AdamW optimizer"; });
+}
+
+int gg_adamw_step_captured(gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        if (!o->adamw) return "not an AdamW optimizer";
+        o->adamw->StepCaptured();
+        return "";
+    });
+}
+
+int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out) {
+    return guarded([&]() -> std::string {
+        if (!o->adamw) return "not an AdamW optimizer";
+        int step = 0;
+        std::string e = o->adamw->GraphStepCount(&step);
+        *out = step;
+        return e;
+    });
+}
+
+int gg_clip_grad_norm(gg_tensor* const* tensors, int32_t n, const float* max_norm) {
+    return guarded([&]() -> std::string {
+        std::vector<Parameter> params;
+        for (int32_t i = 0; i < n; i++) params.push_back(Parameter{"p" + std::to_string(i), tensors[i]->t});
+        ClipGradNorm(params, *max_norm);
+        return "";
+    });
+}
+
+int gg_gradient_norm_to_host(float* out) {
+    return guarded([&]() -> std::string {
+        *out = GradientNormToHost();
+        return "";
+    });
+}
+
+void gg_release_clip_state(void) { ReleaseClipState(); }
+
+static OneCycle to_cycle(const gg_onecycle* c) {
+    OneCycle o;
+    o.MaxLR = c->max_lr;
+    o.PctStart = c->pct_start;
+    o.DivFactor = c->div_factor;
+    o.FinalDivFactor = c->final_div_factor;
+    o.Total = c->total;
+    o.StepCount = c->step_count;
+    return o;
+}
+
+static void from_cycle(const OneCycle& o, gg_onecycle* c) {
+    c->max_lr = o.MaxLR;
+    c->pct_start = o.PctStart;
+    c->div_factor = o.DivFactor;
+    c->final_div_factor = o.FinalDivFactor;
+    c->total = o.Total;
+    c->step_count = o.StepCount;
+}
+
+int gg_onecycle_new(const double* max_lr, int32_t total, const double* pct_start, gg_onecycle* out) {
+    return guarded([&]() -> std::string {
+        from_cycle(OneCycle::New(*max_lr, total, *pct_start), out);
+        return "";
+    });
+}
+
+int gg_onecycle_lr(const gg_onecycle* c, double* out) {
+    *out = to_cycle(c).LR();
+    return 0;
+}
+
+int gg_onecycle_step(gg_onecycle* c, gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        OneCycle cyc = to_cycle(c);
+        cyc.Step(*o->base());
+        from_cycle(cyc, c);
+        return "";
+    });
+}
+
+int gg_save_training_checkpoint(const char* path, const char* const* names, gg_tensor* const* tensors, int32_t n,
+                                gg_optimizer* o, const gg_onecycle* scheduler, const char* const* user_keys,
+                                const char* const* user_values, int32_t n_user) {
+    return guarded([&]() -> std::string {
+        if (!o || !scheduler) return "autograd: model, optimizer and scheduler are required";
+        std::map<std::string, std::string> user;
+        for (int32_t i = 0; i < n_user; i++) user[user_keys[i]] = user_values[i];
+        OneCycle c = to_cycle(scheduler);
+        return SaveTrainingCheckpoint(path, make_params(names, tensors, n), o->base(), &c, user);
+    });
+}
+
+int gg_load_training_checkpoint(const char* path, const char* const* names, gg_tensor* const* tensors, int32_t n,
+                                gg_optimizer* o, gg_onecycle* scheduler, char* user_json, int32_t capacity) {
+    return guarded([&]() -> std::string {
+        if (!o || !scheduler) return "autograd: model, optimizer and scheduler are required";
+        OneCycle c = to_cycle(scheduler);
+        std::map<std::string, std::string> user;
+        std::string e = LoadTrainingCheckpoint(path, make_params(names, tensors, n), o->base(), &c, &user);
+        if (!e.empty()) return e;
+        from_cycle(c, scheduler);
+        if (user_json && capacity > 0) {
+            std::string j = "{";
+            bool first = true;
+            for (const auto& kv : user) {
+                j += (first ? "" : ",") + ggjson::quote(kv.first) + ":" + ggjson::quote(kv.second);
+                first = false;
+            }
+            j += "}";
+            strncpy(user_json, j.c_str(), (size_t)capacity - 1);
+            user_json[capacity - 1] = 0;
+        }
+        return "";
+    });
+}
+
+int gg_safetensors_write(const char* path, const char* const* names, const float* const* data, const int32_t* shapes,
+                         const int32_t* shape_offsets, int32_t n, const char* const* meta_keys,
+                         const char* const* meta_values, int32_t n_meta) {
+    return guarded([&]() -> std::string {
+        EntryMap entries;
+        for (int32_t i = 0; i < n; i++) {
+            SafeTensorEntry e;
+            long long count = 1;
+            for (int32_t k = shape_offsets[i]; k < shape_offsets[i + 1]; k++) {
+                e.Shape.push_back(shapes[k]);
+                count *= shapes[k];
+            }
+            if (count > 0) e.Values.assign(data[i], data[i] + count);
+            entries[names[i]] = std::move(e);
+        }
+        Metadata metadata;
+        for (int32_t i = 0; i < n_meta; i++) metadata[meta_keys[i]] = meta_values[i];
+        return write_safetensors(path, entries, n_meta >= 0 ? &metadata : nullptr);
+    });
+}
+
+int gg_safetensors_describe(const char* path, char* out, int32_t capacity) {
+    return guarded([&]() -> std::string {
+        EntryMap entries;
+        Metadata metadata;
+        std::string e = read_safetensors(path, &entries, &metadata);
+        if (!e.empty()) return e;
+        std::string j = "{\"entries\":{";
+        bool first = true;
+        for (const auto& kv : entries) {
+            double sum = 0;
+            for (float v : kv.second.Values) sum += v;
+            j += (first ? "" : ",") + ggjson::quote(kv.first) + ":{\"shape\":[";
+            for (size_t i = 0; i < kv.second.Shape.size(); i++) j += (i ? "," : "") + std::to_string(kv.second.Shape[i]);
+            j += "],\"sum\":" + ggjson::number_text(sum, false) + "}";
+            first = false;
+        }
+        j += "},\"metadata\":{";
+        first = true;
+        for (const auto& kv : metadata) {
+            j += (first ? "" : ",") + ggjson::quote(kv.first) + ":" + ggjson::quote(kv.second);
+            first = false;
+        }
+        j += "}}";
+        if ((int32_t)j.size() + 1 > capacity) return "description does not fit the buffer";
+        memcpy(out, j.c_str(), j.size() + 1);
+        return "";
+    });
+}
+
+}  // extern "C"

@@ -5,6 +5,7 @@
 #ifndef GG_JSON_MIN_HPP
 #define GG_JSON_MIN_HPP
 
+#include <cctype>
 #include <cmath>
 #include <cstdint>
 #include <cstdio>

@@ -121,7 +121,6 @@ inline std::string write_safetensors(const std::string& path, const EntryMap& en
     }
     ok = ok && fsync(fd) == 0;
     ok = (close(fd) == 0) && ok;
-    if (ok) ok = fchmodat(AT_FDCWD, name.data(), 0644, 0) == 0 || true;
     if (!ok || rename(name.data(), path.c_str()) != 0) {
         unlink(name.data());
         return "autograd: writing " + path + " failed";

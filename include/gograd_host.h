@@ -1,0 +1,128 @@
+/*
+ * gograd_host — flat C handle API over the C++ host mirror of gograd's optimizer surface
+ * (gograd_b200/csrc/host/autograd.hpp). It exists so that the behaviour a Go host keeps
+ * around the device work — constructor validation, parameter groups, the shared step
+ * counter, absent gradients, lazily initialised momentum, state snapshots and the
+ * safetensors checkpoint layout — can be driven and tested from any language without a Go
+ * toolchain. Every function returns 0 on success and non-zero on failure (the message is
+ * gg_last_error()); a failed call leaves optimizer and tensors unchanged. Floats travel by
+ * pointer, as in optengine.h.
+ *
+ * Reference surface mirrored (yh2237/gograd): autograd/nn.go:296-571 (Parameter, ClipGradNorm,
+ * AdamW, OneCycle), autograd/sgd.go, autograd/param_groups.go, autograd/optimizer.go,
+ * autograd/optimizer_state.go, autograd/sgd_state.go, autograd/training_checkpoint.go.
+ */
+#ifndef GOGRAD_HOST_H
+#define GOGRAD_HOST_H
+
+#include <stdint.h>
+
+#include "optengine.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gg_tensor gg_tensor;
+typedef struct gg_optimizer gg_optimizer;
+
+typedef struct gg_sgd_options { /* SGDOptions, autograd/sgd.go:16-19 */
+    float lr, momentum, dampening, weight_decay;
+    int32_t nesterov, maximize;
+} gg_sgd_options;
+
+typedef struct gg_onecycle { /* OneCycle, autograd/nn.go:539-542 */
+    double max_lr, pct_start, div_factor, final_div_factor;
+    int32_t total, step_count;
+} gg_onecycle;
+
+/* Parameter groups as flat arrays: group g is named group_names[g], owns the parameters
+ * members[offsets[g] .. offsets[g+1]) (indexes into the parameter list), scales the base rate
+ * by lr_scales[g] (0 selects 1) and decays with decays[g] (ParameterGroupSpec,
+ * autograd/param_groups.go:21-26). */
+typedef struct gg_groups {
+    int32_t n_groups;
+    const char* const* group_names;
+    const int32_t* offsets; /* n_groups + 1 entries */
+    const int32_t* members;
+    const float* lr_scales;
+    const float* decays;
+} gg_groups;
+
+OE_API const char* gg_last_error(void);
+
+/* ---- tensors: contiguous float32 CUDA leaves (autograd/tensor.go:19-52) ---- */
+OE_API int gg_tensor_new(const float* values, const int32_t* shape, int32_t rank, int32_t device, int32_t requires_grad,
+                         gg_tensor** out);
+OE_API void gg_tensor_free(gg_tensor* t);
+OE_API int64_t gg_tensor_numel(const gg_tensor* t);
+OE_API int gg_tensor_to_host(const gg_tensor* t, float* out);
+OE_API int gg_tensor_copy_from_host(gg_tensor* t, const float* values);
+OE_API int gg_tensor_has_grad(const gg_tensor* t);                 /* 1 when a gradient buffer exists */
+OE_API int gg_tensor_set_grad(gg_tensor* t, const float* values);  /* NULL makes the gradient absent */
+OE_API int gg_tensor_ensure_grad(gg_tensor* t);                    /* present and zero when it was absent */
+OE_API int gg_tensor_grad_to_host(const gg_tensor* t, float* out);
+OE_API int gg_tensor_shadow_to_host(const gg_tensor* t, uint16_t* out);
+OE_API int gg_tensor_shadow_current(const gg_tensor* t);           /* 1 when the bf16 shadow matches the value */
+OE_API uint64_t gg_tensor_address(const gg_tensor* t, int32_t which); /* 0 value, 1 gradient, 2 shadow */
+
+/* ---- optimizers (autograd/nn.go:385-537, autograd/sgd.go:76-257) ---- */
+OE_API int gg_adamw_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr,
+                        const float* decay, gg_optimizer** out);            /* NewAdamW */
+OE_API int gg_adamw_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr,
+                               const gg_groups* groups, gg_optimizer** out); /* NewAdamWGroups */
+OE_API int gg_adamw_set_config(gg_optimizer* o, const float* beta1, const float* beta2, const float* eps); /* exported fields */
+OE_API int gg_sgd_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const gg_sgd_options* options,
+                      gg_optimizer** out);                                   /* NewSGD */
+OE_API int gg_sgd_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n,
+                             const gg_sgd_options* options, const gg_groups* groups, gg_optimizer** out);
+OE_API int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devform);
+OE_API int gg_opt_step(gg_optimizer* o);                                /* Step */
+OE_API int gg_opt_step_clipped(gg_optimizer* o, const float* max_norm); /* norm + Step with the clip folded in */
+OE_API int gg_opt_last_norm(gg_optimizer* o, float* out);
+OE_API int gg_opt_zero_grad(gg_optimizer* o);                           /* ZeroGrad */
+OE_API int gg_opt_get_lr(const gg_optimizer* o, float* out);            /* LearningRate */
+OE_API int gg_opt_set_lr(gg_optimizer* o, const float* lr);             /* SetLearningRate */
+OE_API int64_t gg_opt_step_count(const gg_optimizer* o);
+OE_API int gg_opt_close(gg_optimizer* o);                               /* Close: idempotent */
+OE_API void gg_opt_free(gg_optimizer* o);
+/* state of parameter `index`: which = 0 AdamW m, 1 AdamW v, 2 SGD momentum buffer; *initialized
+ * receives the SGD flag (always 1 for AdamW). out may be NULL to query the flag only. */
+OE_API int gg_opt_state(gg_optimizer* o, int32_t index, int32_t which, float* out, int32_t* initialized);
+OE_API int gg_opt_group_scale(const gg_optimizer* o, int32_t index, float* step_size, float* decay); /* groupScale */
+OE_API int gg_opt_save(gg_optimizer* o, const char* path);              /* SaveSafeTensors */
+OE_API int gg_opt_load(gg_optimizer* o, const char* path);              /* LoadSafeTensors */
+OE_API int gg_adamw_prepare_graph(gg_optimizer* o);                     /* PrepareGraph */
+OE_API int gg_adamw_step_captured(gg_optimizer* o);                     /* the capture branch of Step */
+OE_API int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out);    /* GraphStepCount */
+
+/* ---- clip (autograd/nn.go:310-334, autograd/cuda_clip.go) ---- */
+OE_API int gg_clip_grad_norm(gg_tensor* const* tensors, int32_t n, const float* max_norm);
+OE_API int gg_gradient_norm_to_host(float* out);
+OE_API void gg_release_clip_state(void);
+
+/* ---- schedule and training checkpoint (autograd/nn.go:539-571, autograd/training_checkpoint.go) ---- */
+OE_API int gg_onecycle_new(const double* max_lr, int32_t total, const double* pct_start, gg_onecycle* out);
+OE_API int gg_onecycle_lr(const gg_onecycle* c, double* out);
+OE_API int gg_onecycle_step(gg_onecycle* c, gg_optimizer* o);
+OE_API int gg_save_training_checkpoint(const char* path, const char* const* names, gg_tensor* const* tensors, int32_t n,
+                                       gg_optimizer* o, const gg_onecycle* scheduler, const char* const* user_keys,
+                                       const char* const* user_values, int32_t n_user);
+/* user_json receives the caller metadata as a JSON object text (truncated to capacity). */
+OE_API int gg_load_training_checkpoint(const char* path, const char* const* names, gg_tensor* const* tensors, int32_t n,
+                                       gg_optimizer* o, gg_onecycle* scheduler, char* user_json, int32_t capacity);
+
+/* ---- safetensors container, host only (autograd/safetensors.go:30-98, safetensors_stream.go:28-96) ---- */
+/* Writes F32 entries (entry i: names[i], data[i], shape = shapes[shape_offsets[i] .. shape_offsets[i+1])) and
+ * string metadata exactly as the reference's writer lays them out. Needs no GPU. */
+OE_API int gg_safetensors_write(const char* path, const char* const* names, const float* const* data,
+                                const int32_t* shapes, const int32_t* shape_offsets, int32_t n,
+                                const char* const* meta_keys, const char* const* meta_values, int32_t n_meta);
+/* Validates a file with the reference reader's rules and returns a JSON description
+ * {"entries":{name:{"shape":[..],"sum":float64 sum of the values}},"metadata":{..}} in out. */
+OE_API int gg_safetensors_describe(const char* path, char* out, int32_t capacity);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GOGRAD_HOST_H */
