@@ -547,18 +547,20 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
         float4* o4 = (float4*)out;
         // U x n 128-bit loads are issued before the first add: a remote load takes a few
         // microseconds, so bytes in flight per SM decide the NVLink throughput.
-        for (uint64_t i0 = tid; i0 < nvec; i0 += U * stride) {
+        // Loads go through L2 only (ld.global.cg): peer data must not linger in L1, and on B200 this
+        // flavour pulls 4 % faster over NVLink than streaming (.cs) loads (656 vs 629 GB/s).
+        for (uint64_t i0 = tid; i0 < nvec; i0 += (uint64_t)U * stride) {
             float4 v[U][NP];
 #pragma unroll
             for (int u = 0; u < U; u++) {
-                const uint64_t i = i0 + u * stride;
+                const uint64_t i = i0 + (uint64_t)u * stride;
 #pragma unroll
                 for (int k = 0; k < NP; k++)
-                    if (k < (int)n && i < nvec) v[u][k] = __ldcs((const float4*)((const float*)pg.base[k] + first) + i);
+                    if (k < (int)n && i < nvec) v[u][k] = __ldcg((const float4*)((const float*)pg.base[k] + first) + i);
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
-                const uint64_t i = i0 + u * stride;
+                const uint64_t i = i0 + (uint64_t)u * stride;
                 if (i < nvec) {
                     float4 s = v[u][0];
 #pragma unroll
@@ -586,8 +588,8 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
         done = nvec << 2;
     }
     for (uint64_t i = done + tid; i < numel; i += stride) {
-        float s = ((const float*)pg.base[0])[first + i];
-        for (uint32_t k = 1; k < n; k++) s = __fadd_rn(s, ((const float*)pg.base[k])[first + i]);
+        float s = __ldcg((const float*)pg.base[0] + first + i);
+        for (uint32_t k = 1; k < n; k++) s = __fadd_rn(s, __ldcg((const float*)pg.base[k] + first + i));
         s = __fmul_rn(s, scale);
         out[i] = s;
         double x = (double)s;
