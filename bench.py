@@ -201,18 +201,28 @@ def run_single(args):
     stream = torch.cuda.current_stream()
     step_no = [0]
 
+    is_sgd = ps.optimizer == "sgd"
+    bytes_update = (20 if hp.get("momentum", 0) > 0 else 12) if is_sgd else 28
+    bytes_update += 2 if ps.bf16_shadow else 0
+
     def hparams():
         step_no[0] += 1
+        if is_sgd:
+            return eng.SGDHParams(hp["lr"], hp["momentum"], hp["dampening"], ps.max_norm, flags)
         b1, b2 = workload.bias_corrections(hp["beta1"], hp["beta2"], step_no[0])
         return eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], b1, b2, ps.max_norm, flags)
 
     def one_step(events=None):
         if events is not None:
             events[0].record(stream)
-        plan.grad_norm(0, stream)
+        if ps.max_norm > 0:
+            plan.grad_norm(0, stream)
         if events is not None:
             events[1].record(stream)
-        plan.adamw_step(hparams(), stream)
+        if is_sgd:
+            plan.sgd_step(hparams(), stream)
+        else:
+            plan.adamw_step(hparams(), stream)
         if events is not None:
             events[2].record(stream)
 
@@ -241,7 +251,7 @@ def run_single(args):
 
     # ---- end to end through the host-buffer entry point -------------------------------
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not is_sgd:
         try:
             host_grads = [torch.empty(t.numel(), dtype=torch.float32).pin_memory() for t in state.g]
             for hg, g in zip(host_grads, state.g):
@@ -264,9 +274,10 @@ def run_single(args):
     clocks = sampler.stop()
 
     peak, peak_kind = measured_peak()
+    BYTES_UPDATE, BYTES_NORM = bytes_update, (4 if ps.max_norm > 0 else 0)
     achieved = BYTES_UPDATE * n_params / (upd_ms * 1e-3) / 1e9
-    traffic = ncu_traffic_per_param().get("oe_adamw_fused_bytes_per_param")
-    roofline = {"bound": "hbm", "kernel": "oe_adamw_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
+    traffic = ncu_traffic_per_param().get("oe_adamw_fused_bytes_per_param") if (not is_sgd and ps.bf16_shadow) else None
+    roofline = {"bound": "hbm", "kernel": "oe_sgd_fused" if is_sgd else "oe_adamw_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": peak_kind,
                 "traffic": None if traffic is None else traffic * n_params,
                 "algorithmic_bytes_per_launch": BYTES_UPDATE * n_params, "kernel_ms": upd_ms,
@@ -283,11 +294,12 @@ def run_single(args):
         cpu_baseline, _, _ = cpu_reference_run(ps, args.cpu_sample_params, 5, 1, os.cpu_count() or 1)
 
     line = {
-        "metric": METRIC, "value": n_params / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": 1,
+        "metric": METRIC if key == "llama1b" else f"fused {ps.optimizer} step throughput ({key})",
+        "value": n_params / (ms_per_step * 1e-3) / 1e9, "unit": UNIT, "n_gpus": 1,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": key, "title": ps.title, "params": n_params, "tensors": len(ps.params),
-                   "optimizer": "adamw", "max_norm": ps.max_norm, "bf16_shadow": ps.bf16_shadow,
+                   "optimizer": ps.optimizer, "max_norm": ps.max_norm, "bf16_shadow": ps.bf16_shadow,
                    "chunk_elems": plan.info(5), "grid_update": plan.info(3), "grid_norm": plan.info(4),
                    "variant": args.variant or "default",
                    "l2": "inputs larger than L2: %.1f GB of p/g/m/v/shadow per step" % ((18 * n_params) / 1e9),
