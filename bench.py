@@ -249,6 +249,34 @@ def run_single(args):
     upd_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
     norm_value, _ = plan.read_norm(stream)
 
+    # ---- optional: the same step captured once in a CUDA graph and replayed ----------------
+    graph_info = None
+    if args.graph:
+        step_dev = torch.full((1,), step_no[0], dtype=torch.int32, device="cuda:0")
+        lr_dev = torch.full((1,), hp["lr"], dtype=torch.float32, device="cuda:0")
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            if ps.max_norm > 0:
+                plan.grad_norm(0)
+            if is_sgd:
+                plan.sgd_step(eng.SGDHParams(hp["lr"], hp["momentum"], hp["dampening"], ps.max_norm, flags,
+                                             step_dev=step_dev.data_ptr(), lr_dev=lr_dev.data_ptr()))
+            else:
+                plan.adamw_step(eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], max_norm=ps.max_norm,
+                                                 flags=flags, step_dev=step_dev.data_ptr(), lr_dev=lr_dev.data_ptr()))
+        for _ in range(args.warmup):
+            g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        graph_info = {"ms_per_step": a.elapsed_time(b) / args.steps,
+                      "value": n_params / (a.elapsed_time(b) / args.steps * 1e-3) / 1e9,
+                      "note": "one captured step (device step counter and learning rate) replayed"}
+
     # ---- end to end through the host-buffer entry point -------------------------------
     e2e = None
     if not args.no_e2e and not is_sgd:
@@ -307,6 +335,8 @@ def run_single(args):
         "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks,
         "gpu_launches": launches,
     }
+    if graph_info:
+        line["graph_replay"] = graph_info
     print(json.dumps(line))
     plan.close()
     return 0
@@ -323,6 +353,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=0)
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="N > 1: fused peer-memory kernels, or NCCL reduce-scatter / all-gather around the kernels")
+    ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-params", type=int, default=120_000_000)

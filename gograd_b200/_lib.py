@@ -19,12 +19,12 @@ class oe_tensor_desc(C.Structure):
 class oe_adamw_hparams(C.Structure):
     _fields_ = [("lr", C.c_float), ("beta1", C.c_float), ("beta2", C.c_float), ("eps", C.c_float),
                 ("bc1", C.c_float), ("bc2", C.c_float), ("max_norm", C.c_float), ("flags", C.c_uint32),
-                ("step_dev", C.c_uint64)]
+                ("step_dev", C.c_uint64), ("lr_dev", C.c_uint64)]
 
 
 class oe_sgd_hparams(C.Structure):
     _fields_ = [("lr", C.c_float), ("momentum", C.c_float), ("dampening", C.c_float), ("max_norm", C.c_float),
-                ("flags", C.c_uint32), ("reserved", C.c_uint32)]
+                ("flags", C.c_uint32), ("reserved", C.c_uint32), ("step_dev", C.c_uint64), ("lr_dev", C.c_uint64)]
 
 
 class EngineError(RuntimeError):

@@ -139,6 +139,9 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
     k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
     const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
     const bool zero_grad = (a.flags & OE_F_ZERO_GRAD) != 0;
+    // A captured step bakes its launch parameters into the graph; a device-resident rate
+    // lets a schedule change it between replays without capturing again.
+    const float base_lr = a.lr_dev != 0 ? *(const float*)a.lr_dev : a.lr;
 
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
@@ -149,7 +152,7 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
         float* __restrict__ v = (float*)t->state2 + cv.base;
         uint16_t* __restrict__ sh = (want_shadow && t->shadow) ? (uint16_t*)t->shadow + cv.base : nullptr;
         // Group scaling in fp32 exactly as AdamW.groupScale (autograd/nn.go:461-465).
-        const float step = __fmul_rn(a.lr, t->lr_scale);
+        const float step = __fmul_rn(base_lr, t->lr_scale);
         const float omd = __fsub_rn(1.0f, __fmul_rn(step, t->weight_decay));
         uint32_t done = 0;
         if ((t->aligned & (OE_ALIGNED_BASE | OE_ALIGNED_STATE2)) == (OE_ALIGNED_BASE | OE_ALIGNED_STATE2)) {
@@ -272,6 +275,7 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
     k.maximize = (a.flags & OE_F_MAXIMIZE) != 0;
     const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
     const bool zero_grad = (a.flags & OE_F_ZERO_GRAD) != 0;
+    const float base_lr = a.lr_dev != 0 ? *(const float*)a.lr_dev : a.lr;
 
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
         oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
@@ -285,7 +289,7 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
         const bool first = has_buf && t->state2 != 0 ? (*(const float*)t->state2 == 0.0f) : true;
         uint16_t* __restrict__ sh = (want_shadow && t->shadow) ? (uint16_t*)t->shadow + cv.base : nullptr;
         // SGD.groupScale (autograd/sgd.go:127-130): the decay is not scaled by the rate.
-        const float lr = __fmul_rn(a.lr, t->lr_scale);
+        const float lr = __fmul_rn(base_lr, t->lr_scale);
         const float decay = t->weight_decay;
         uint32_t done = 0;
         if (t->aligned & OE_ALIGNED_BASE) {

@@ -562,7 +562,7 @@ int validate_adamw(const oe_plan* p, const oe_adamw_hparams* hp) {
         return fail(OE_ERR_INVALID, "invalid optimizer configuration");
     if (hp->step_dev == 0 && (!(hp->bc1 > 0.0f) || !(hp->bc2 > 0.0f) || !isfinite(hp->bc1) || !isfinite(hp->bc2)))
         return fail(OE_ERR_INVALID, "bias corrections must be positive and finite (step >= 1)");
-    if (hp->step_dev & 3u) return fail(OE_ERR_INVALID, "step_dev not 4-byte aligned");
+    if ((hp->step_dev | hp->lr_dev) & 3u) return fail(OE_ERR_INVALID, "step_dev / lr_dev not 4-byte aligned");
     if (isnan(hp->max_norm)) return fail(OE_ERR_INVALID, "max_norm is NaN");
     if (hp->flags & ~(OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD))
         return fail(OE_ERR_INVALID, "oe_adamw_step: unknown flag");
@@ -591,6 +591,7 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     a.flags = hp->flags;
     a.norm = hp->max_norm > 0.0f ? (uint64_t)p->d_norm : 0;
     a.step_dev = hp->step_dev;
+    a.lr_dev = hp->lr_dev;
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
     if (peers) {
         oe_peer_set ps = *peers;
@@ -633,8 +634,14 @@ extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t str
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
     if ((rc = check_chunk_count(plan)) != 0) return rc;
-    if (plan->n_chunks == 0) return 0;
+    if ((hp->step_dev | hp->lr_dev) & 3u) return fail(OE_ERR_INVALID, "step_dev / lr_dev not 4-byte aligned");
     CtxGuard guard(d, plan->dc->ctx);
+    if (hp->step_dev) {
+        uint64_t sd = hp->step_dev;
+        void* inc_args[] = {&sd};
+        if ((rc = launch(d, plan->dc->k.step_increment, "oe_step_increment", 1, 32, (CUstream)stream, inc_args)) != 0) return rc;
+    }
+    if (plan->n_chunks == 0) return 0;
     oe_sgd_args a;
     memset(&a, 0, sizeof(a));
     a.lr = hp->lr;
@@ -643,6 +650,7 @@ extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t str
     a.max_norm = hp->max_norm;
     a.flags = hp->flags;
     a.norm = hp->max_norm > 0.0f ? (uint64_t)plan->d_norm : 0;
+    a.lr_dev = hp->lr_dev;
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
     rc = launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);

@@ -47,6 +47,7 @@ typedef struct oe_adamw_args {
     int64_t step;     /* host step counter (after increment); used when step_dev == 0 */
     uint64_t norm;    /* const oe_dev_norm* or 0                                 */
     uint64_t step_dev;/* const int32_t* device step counter (capture mode) or 0  */
+    uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
 } oe_adamw_args;
 
 typedef struct oe_sgd_args {
@@ -55,6 +56,7 @@ typedef struct oe_sgd_args {
     uint32_t flags;   /* OE_F_NESTEROV | OE_F_MAXIMIZE | clip/shadow bits        */
     uint32_t pad;
     uint64_t norm;
+    uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
 } oe_sgd_args;
 
 /* Ranks of a sharded step: byte distance from this rank's buffer to rank k's buffer of the

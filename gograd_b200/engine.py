@@ -60,10 +60,11 @@ class AdamWHParams:
     max_norm: float = 0.0
     flags: int = 0
     step_dev: int = 0
+    lr_dev: int = 0
 
     def to_c(self) -> _lib.oe_adamw_hparams:
         return _lib.oe_adamw_hparams(self.lr, self.beta1, self.beta2, self.eps, self.bc1, self.bc2, self.max_norm,
-                                     self.flags, self.step_dev)
+                                     self.flags, self.step_dev, self.lr_dev)
 
 
 @dataclass
@@ -73,9 +74,12 @@ class SGDHParams:
     dampening: float = 0.0
     max_norm: float = 0.0
     flags: int = 0
+    step_dev: int = 0
+    lr_dev: int = 0
 
     def to_c(self) -> _lib.oe_sgd_hparams:
-        return _lib.oe_sgd_hparams(self.lr, self.momentum, self.dampening, self.max_norm, self.flags, 0)
+        return _lib.oe_sgd_hparams(self.lr, self.momentum, self.dampening, self.max_norm, self.flags, 0,
+                                   self.step_dev, self.lr_dev)
 
 
 def _desc_array(descs: Sequence[TensorDesc]):

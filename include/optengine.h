@@ -91,6 +91,10 @@ typedef struct oe_adamw_hparams {
     uint64_t step_dev; /* device int32 step counter for captured steps (AdamW.PrepareGraph,
                           autograd/nn.go:350-361): incremented on the device, bias corrections
                           computed there; 0 = eager mode                                             */
+    uint64_t lr_dev;   /* device float holding the base rate, read by the kernel instead of lr when
+                          non-zero: a captured step then follows a schedule (OneCycle.Step ->
+                          SetLearningRate, autograd/nn.go:571) without being captured again, which the
+                          reference cannot do (it bakes lr into the launch, autograd/nn.go:480-483)          */
 } oe_adamw_hparams;
 
 /* SGD hyper-parameters of one step (SGDOptions, autograd/sgd.go:16-19). */
@@ -100,6 +104,9 @@ typedef struct oe_sgd_hparams {
     float max_norm;    /* as in oe_adamw_hparams                                                     */
     uint32_t flags;    /* OE_NESTEROV | OE_MAXIMIZE | OE_CLIP_DEVFORM | OE_WRITE_SHADOW | OE_ZERO_GRAD */
     uint32_t reserved;
+    uint64_t step_dev; /* device int32 step counter incremented by a captured step (SGD.PrepareGraph,
+                          sgd_step, autograd/cuda_sgd.go:18,99-125); 0 = eager mode                        */
+    uint64_t lr_dev;   /* as in oe_adamw_hparams                                                     */
 } oe_sgd_hparams;
 
 typedef struct oe_plan oe_plan;

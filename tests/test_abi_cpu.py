@@ -28,8 +28,8 @@ def test_header_symbols_are_exported_and_bound():
 def test_struct_layouts_match_the_header():
     from gograd_b200 import _lib
     assert C.sizeof(_lib.oe_tensor_desc) == 56
-    assert C.sizeof(_lib.oe_adamw_hparams) == 40
-    assert C.sizeof(_lib.oe_sgd_hparams) == 24
+    assert C.sizeof(_lib.oe_adamw_hparams) == 48
+    assert C.sizeof(_lib.oe_sgd_hparams) == 40
     assert _lib.oe_adamw_hparams.step_dev.offset == 32
 
 
