@@ -398,3 +398,39 @@ def safetensors_describe(path: str) -> dict:
     buf = C.create_string_buffer(1 << 20)
     _check(lib().gg_safetensors_describe(path.encode(), buf, len(buf)))
     return json.loads(buf.value.decode())
+
+
+class _AdamWConfig(C.Structure):
+    _fields_ = [("step_count", C.c_int32), ("lr", C.c_float), ("weight_decay", C.c_float), ("beta1", C.c_float),
+                ("beta2", C.c_float), ("eps", C.c_float)]
+
+
+def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], m: Sequence[np.ndarray],
+                      v: Sequence[np.ndarray], step_count: int, lr: float, weight_decay: float, beta1: float,
+                      beta2: float, eps: float, groups: Sequence[tuple]) -> None:
+    """Host-only: writes a "gograd-adamw" state file from gathered moments.
+    groups: (name, member indexes, lr_scale, weight_decay) per group."""
+    n = len(names)
+    c_names = (C.c_char_p * max(n, 1))(*[x.encode() for x in names])
+    flat, offsets = [], [0]
+    for sh in shapes:
+        flat += list(sh)
+        offsets.append(len(flat))
+    c_shapes = (C.c_int32 * max(len(flat), 1))(*flat)
+    c_off = (C.c_int32 * len(offsets))(*offsets)
+    ms = [np.require(x, np.float32, "C") for x in m]
+    vs = [np.require(x, np.float32, "C") for x in v]
+    c_m = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in ms])
+    c_v = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in vs])
+    cfg = _AdamWConfig(step_count, lr, weight_decay, beta1, beta2, eps)
+    g_names = (C.c_char_p * max(len(groups), 1))(*[g[0].encode() for g in groups])
+    g_off, g_mem = [0], []
+    for g in groups:
+        g_mem += list(g[1])
+        g_off.append(len(g_mem))
+    c_goff = (C.c_int32 * len(g_off))(*g_off)
+    c_gmem = (C.c_int32 * max(len(g_mem), 1))(*g_mem)
+    c_scales = (C.c_float * max(len(groups), 1))(*[g[2] for g in groups])
+    c_decays = (C.c_float * max(len(groups), 1))(*[g[3] for g in groups])
+    gs = _Groups(len(groups), g_names, c_goff, c_gmem, c_scales, c_decays)
+    _check(lib().gg_adamw_state_write(path.encode(), n, c_names, c_shapes, c_off, c_m, c_v, C.byref(cfg), C.byref(gs)))

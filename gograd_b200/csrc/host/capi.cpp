@@ -483,6 +483,51 @@ int gg_safetensors_write(const char* path, const char* const* names, const float
     });
 }
 
+int gg_adamw_state_write(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                         const int32_t* shape_offsets, const float* const* m, const float* const* v,
+                         const gg_adamw_config* config, const gg_groups* groups) {
+    return guarded([&]() -> std::string {
+        if (!config || !groups) return "NULL argument";
+        OptimizerState s;
+        s.StepCount = config->step_count;
+        s.LR = config->lr;
+        s.WeightDecay = config->weight_decay;
+        s.Beta1 = config->beta1;
+        s.Beta2 = config->beta2;
+        s.Eps = config->eps;
+        s.Moments.resize((size_t)n);
+        for (int32_t i = 0; i < n; i++) {
+            s.Names.push_back(names[i]);
+            std::vector<int> shape(shapes + shape_offsets[i], shapes + shape_offsets[i + 1]);
+            long long count = 1;
+            for (int d : shape) count *= d;
+            s.Shapes.push_back(shape);
+            s.Moments[(size_t)i].M.assign(m[i], m[i] + count);
+            s.Moments[(size_t)i].V.assign(v[i], v[i] + count);
+        }
+        for (int32_t g = 0; g < groups->n_groups; g++) {
+            OptimizerGroupState gs;
+            gs.Name = groups->group_names[g];
+            for (int32_t k = groups->offsets[g]; k < groups->offsets[g + 1]; k++) {
+                int32_t index = groups->members[k];
+                if (index < 0 || index >= n) return "autograd: group member out of range";
+                gs.Names.push_back(names[index]);
+            }
+            float scale = 0;
+            std::string e = normalizeLRScale(groups->lr_scales[g], &scale);
+            if (!e.empty()) return e;
+            gs.LRScale = scale;
+            gs.WeightDecay = groups->decays[g];
+            s.Groups.push_back(gs);
+        }
+        EntryMap entries;
+        Metadata metadata;
+        std::string e = optimizerEntries(std::move(s), &entries, &metadata);
+        if (!e.empty()) return e;
+        return write_safetensors(path, entries, &metadata);
+    });
+}
+
 int gg_safetensors_describe(const char* path, char* out, int32_t capacity) {
     return guarded([&]() -> std::string {
         EntryMap entries;

@@ -378,29 +378,11 @@ oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
     __shared__ double warp_sums[OE_THREADS / 32];
     __shared__ uint32_t is_last;
     double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
-    // The chunk entry and the tensor row behind it are two dependent loads; the next
-    // chunk's are fetched while the current chunk streams, so a 16 KB work unit does not
-    // pay that latency on its critical path.
-    const float* next_g = nullptr;
-    uint32_t next_n = 0, next_aligned = 0;
-    if (blockIdx.x < n_chunks) {
-        oe_chunk_view nv = oe_view(tensors, chunks, blockIdx.x, chunk_elems);
-        next_g = (const float*)nv.t->grad + nv.base;
-        next_n = nv.n;
-        next_aligned = nv.t->aligned;
-    }
     for (uint32_t c = blockIdx.x; c < n_chunks; c += gridDim.x) {
-        const float* __restrict__ g = next_g;
-        const uint32_t cur_n = next_n, cur_aligned = next_aligned;
-        if (c + gridDim.x < n_chunks) {
-            oe_chunk_view nv = oe_view(tensors, chunks, c + gridDim.x, chunk_elems);
-            next_g = (const float*)nv.t->grad + nv.base;
-            next_n = nv.n;
-            next_aligned = nv.t->aligned;
-        }
-        struct { uint32_t n; } cv = {cur_n};
+        oe_chunk_view cv = oe_view(tensors, chunks, c, chunk_elems);
+        const float* __restrict__ g = (const float*)cv.t->grad + cv.base;
         uint32_t done = 0;
-        if (cur_aligned & OE_ALIGNED_BASE) {
+        if (cv.t->aligned & OE_ALIGNED_BASE) {
             const uint32_t nvec = cv.n >> 2;
             const float4* g4 = (const float4*)g;
             for (uint32_t i0 = threadIdx.x; i0 < nvec; i0 += OE_THREADS * OE_NORM_UNROLL) {

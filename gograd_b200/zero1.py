@@ -185,14 +185,7 @@ class Zero1AdamW(Zero1Schedule):
         self.v = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
         self.grads = [self.grad_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
         self.shadows = [self.shadow_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
-        lo = self.lo
-        descs = []
-        for pc in self.my_pieces:
-            a, b = pc.flat_offset, pc.flat_offset + pc.length
-            scale, decay = group_of[pc.tensor]
-            descs.append(engine.TensorDesc(self.master[a - lo:b - lo], self.grad_flat[a:b], self.m[a - lo:b - lo],
-                                           self.v[a - lo:b - lo], self.shadow_flat[a:b], scale, decay))
-        self.plan = engine.Plan(descs, device, chunk_elems)
+        self.plan = engine.Plan(self._descs(), device, chunk_elems)
         self.sumsq = torch.as_tensor(_RawCuda(self.plan.norm_address(), (1,), "<f8"), device=dev)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._imported: List[int] = []
@@ -200,6 +193,16 @@ class Zero1AdamW(Zero1Schedule):
         self.shadow_deltas: Optional[List[int]] = None
         if comm == "peer":
             self._map_peers()
+
+    def _descs(self):
+        """One descriptor per piece of a tensor inside this rank's shard."""
+        lo, descs = self.lo, []
+        for pc in self.my_pieces:
+            a, b = pc.flat_offset, pc.flat_offset + pc.length
+            scale, decay = self.group_of[pc.tensor]
+            descs.append(self.engine.TensorDesc(self.master[a - lo:b - lo], self.grad_flat[a:b], self.m[a - lo:b - lo],
+                                                self.v[a - lo:b - lo], self.shadow_flat[a:b], scale, decay))
+        return descs
 
     # ---- peer mapping (CUDA IPC through the C ABI) -------------------------------------
     def _map_peers(self) -> None:
@@ -278,6 +281,92 @@ class Zero1AdamW(Zero1Schedule):
 
     def grad_norm(self) -> float:
         return self.plan.read_norm()[0]
+
+    # ---- checkpoint I/O in the reference's per-tensor layout -----------------------------
+    def groups(self):
+        """(name, member indexes, lr_scale, weight_decay) per distinct group value, in order of first
+        appearance; a single group is called "default" as the flat constructors of the reference do."""
+        seen = {}
+        for i, key in enumerate(self.group_of):
+            seen.setdefault(key, []).append(i)
+        if len(seen) == 1:
+            (scale, decay), members = next(iter(seen.items()))
+            return [("default", members, scale, decay)]
+        return [(f"group{k}", members, scale, decay) for k, ((scale, decay), members) in enumerate(seen.items())]
+
+    def save_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
+        """Gathers the sharded moments and lets rank 0 write them as a "gograd-adamw" state file:
+        entries m.<i> / v.<i> of shape [numel] per parameter plus the configuration metadata, the
+        layout an unsharded AdamW reads back (autograd/optimizer_state.go:142-226)."""
+        torch, dist = self.torch, self.dist
+        gathered = {}
+        for key, shard in (("m", self.m), ("v", self.v)):
+            parts = [torch.empty_like(shard) for _ in range(self.world)] if self.rank == 0 else None
+            if self.world > 1:
+                dist.gather(shard, parts, dst=0, group=self.pg)
+            else:
+                parts = [shard]
+            if self.rank == 0:
+                gathered[key] = torch.cat(parts).cpu().numpy()
+        if self.rank == 0:
+            from . import autograd as host
+            L = self.layout
+            m = [gathered["m"][o:o + n] for o, n in zip(L.offsets, L.numels)]
+            v = [gathered["v"][o:o + n] for o, n in zip(L.offsets, L.numels)]
+            groups = self.groups()
+            host.adamw_state_write(path, list(names), [list(s) for s in shapes], m, v, self.step_count, self.lr,
+                                   groups[0][3], self.beta1, self.beta2, self.eps, groups)
+        if self.world > 1:
+            dist.barrier(group=self.pg)
+
+    def load_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
+        """Every rank reads the file and takes its shard of m and v. The file is checked first
+        (format, names, shapes, sizes, finite moments, v >= 0, group layout) and nothing is changed
+        when a check fails (autograd/optimizer_state.go:228-259)."""
+        import json
+        import struct
+
+        import numpy as np
+        with open(path, "rb") as f:
+            (hlen,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(hlen))
+            base = 8 + hlen
+            meta = header.pop("__metadata__", {})
+            if meta.get("format") != "gograd-adamw" or meta.get("version") != "1":
+                raise ValueError("autograd: not an optimizer state")
+            cfg = json.loads(meta["optimizer"])
+            n = len(self.layout.numels)
+            if cfg["StepCount"] != int(meta["step_count"]) or len(header) != 2 * n:
+                raise ValueError("autograd: optimizer state count or step mismatch")
+            if list(cfg["Names"] or []) != list(names) or [list(s) for s in (cfg["Shapes"] or [])] != [list(s) for s in shapes]:
+                raise ValueError("autograd: optimizer parameter name or shape mismatch")
+            saved_groups = cfg.get("Groups") or []
+            live = self.groups()
+            if len(saved_groups) != len(live) or any(
+                    [names[i] for i in g[1]] != sg["Names"] for g, sg in zip(live, saved_groups)):
+                raise ValueError("autograd: saved parameter groups do not match the live optimizer")
+            staged = {"m": np.zeros(self.layout.shard_len, np.float32), "v": np.zeros(self.layout.shard_len, np.float32)}
+            for pc in self.my_pieces:
+                for key in ("m", "v"):
+                    entry = header.get(f"{key}.{pc.tensor}")
+                    if entry is None or entry["dtype"] != "F32" or entry["shape"] != [self.layout.numels[pc.tensor]]:
+                        raise ValueError(f"autograd: optimizer state is missing parameter {pc.tensor}")
+                    f.seek(base + entry["data_offsets"][0] + 4 * pc.tensor_offset)
+                    values = np.frombuffer(f.read(4 * pc.length), dtype="<f4")
+                    if not np.all(np.isfinite(values)) or (key == "v" and np.any(values < 0)):
+                        raise ValueError(f"autograd: invalid optimizer moment {pc.tensor}")
+                    a = pc.flat_offset - self.lo
+                    staged[key][a:a + pc.length] = values
+        self.m.copy_(self.torch.from_numpy(staged["m"]))
+        self.v.copy_(self.torch.from_numpy(staged["v"]))
+        # the saved groups carry their own scale and decay (autograd/param_groups.go:225-251)
+        for g, sg in zip(live, saved_groups):
+            scale = float(np.float32(sg["LRScale"])) or 1.0
+            for i in g[1]:
+                self.group_of[i] = (scale, float(np.float32(sg["WeightDecay"])))
+        self.plan.update(self._descs())
+        self.step_count = int(cfg["StepCount"])
+        self.lr, self.beta1, self.beta2, self.eps = (float(np.float32(cfg[k])) for k in ("LR", "Beta1", "Beta2", "Eps"))
 
     def close(self) -> None:
         self.torch.cuda.synchronize()

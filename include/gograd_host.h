@@ -118,6 +118,16 @@ OE_API int gg_load_training_checkpoint(const char* path, const char* const* name
 OE_API int gg_safetensors_write(const char* path, const char* const* names, const float* const* data,
                                 const int32_t* shapes, const int32_t* shape_offsets, int32_t n,
                                 const char* const* meta_keys, const char* const* meta_values, int32_t n_meta);
+/* Writes an AdamW state file ("gograd-adamw": entries m.<i>, v.<i> of shape [numel], metadata with the
+ * optimizer configuration, autograd/optimizer_state.go:142-160) from host arrays: the export path of a
+ * sharded optimizer whose gathered moments never lived in one AdamW object. Needs no GPU. */
+typedef struct gg_adamw_config {
+    int32_t step_count;
+    float lr, weight_decay, beta1, beta2, eps;
+} gg_adamw_config;
+OE_API int gg_adamw_state_write(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                                const int32_t* shape_offsets, const float* const* m, const float* const* v,
+                                const gg_adamw_config* config, const gg_groups* groups);
 /* Validates a file with the reference reader's rules and returns a JSON description
  * {"entries":{name:{"shape":[..],"sum":float64 sum of the values}},"metadata":{..}} in out. */
 OE_API int gg_safetensors_describe(const char* path, char* out, int32_t capacity);
