@@ -9,6 +9,7 @@ LIB_PATH = os.path.join(_HERE, "liboptengine.so")
 
 OE_ERR_INVALID, OE_ERR_NO_DRIVER, OE_ERR_NOT_INIT, OE_ERR_ARCH, OE_ERR_LIMIT, OE_ERR_DEVICE = -1, -2, -3, -4, -5, -6
 OE_CLIP_DEVFORM, OE_WRITE_SHADOW, OE_ZERO_GRAD, OE_NESTEROV, OE_MAXIMIZE, OE_PARTIAL_ONLY = 1, 2, 4, 8, 16, 32
+OE_ACCUMULATE = 64
 
 
 class oe_tensor_desc(C.Structure):
@@ -57,6 +58,7 @@ PROTOTYPES = {
     "oe_clip_grad_norm": (_i, [_plan, C.POINTER(C.c_float), _u32, _u64]),
     "oe_read_norm": (_i, [_plan, C.POINTER(C.c_float), C.POINTER(C.c_double), _u64]),
     "oe_adamw_step": (_i, [_plan, C.POINTER(oe_adamw_hparams), _u64]),
+    "oe_adamw_step_chunks": (_i, [_plan, C.POINTER(oe_adamw_hparams), _u64, _u64, _u64]),
     "oe_sgd_step": (_i, [_plan, C.POINTER(oe_sgd_hparams), _u64]),
     "oe_zero_grads": (_i, [_plan, _u64]),
     "oe_cast_bf16": (_i, [_i, _u64, _u64, _u64, _u64]),

@@ -613,6 +613,8 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
     for (uint32_t i = threadIdx.x; i < gridDim.x; i += OE_THREADS) s += __ldcg(partials + i);
     double total = oe_block_sum(s, warp_sums);
     if (threadIdx.x == 0) {
+        // A shard reduced piece by piece (one launch per staged piece) adds up in launch order.
+        if (pg.flags & OE_F_ACCUMULATE) total = rec->sumsq + total;
         rec->sumsq = total;
         if (!(pg.flags & OE_F_PARTIAL_ONLY)) rec->norm = (float)sqrt(total);
         rec->ticket = 0u;

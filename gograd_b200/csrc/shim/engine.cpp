@@ -3,6 +3,7 @@
 // driver API bound at run time (driver.h); the kernels come from an sm_100a cubin
 // embedded in the library (cubin_blob.S).
 #include <math.h>
+#include <stdint.h>
 #include <string.h>
 
 #include <map>
@@ -571,7 +572,7 @@ int validate_adamw(const oe_plan* p, const oe_adamw_hparams* hp) {
 }
 
 int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUstream stream,
-                 const oe_peer_set* peers = nullptr) {
+                 const oe_peer_set* peers = nullptr, uint64_t first_chunk = 0, uint64_t range_chunks = UINT64_MAX) {
     if (hp->step_dev) {
         uint64_t sd = hp->step_dev;
         void* inc_args[] = {&sd};
@@ -593,15 +594,22 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     a.step_dev = hp->step_dev;
     a.lr_dev = hp->lr_dev;
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
+    CUdeviceptr chunk_table = p->d_chunks;
+    if (range_chunks != UINT64_MAX) {  // a contiguous range of the chunk table
+        chunk_table += first_chunk * sizeof(oe_dev_chunk);
+        n_chunks = (uint32_t)range_chunks;
+        if (n_chunks == 0) return 0;
+    }
     if (peers) {
         oe_peer_set ps = *peers;
-        void* peer_args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &a, &ps};
+        void* peer_args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a, &ps};
         return launch(d, p->dc->k.adamw_peers, "oe_adamw_fused_peers", grid_for(p, p->dc->occ_adamw_peers), kThreads,
                       stream, peer_args);
     }
-    void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &a};
-    return launch(d, p->dc->k.adamw[p->variant], kAdamwNames[p->variant], grid_for(p, p->dc->occ_adamw[p->variant]),
-                  kThreads, stream, args);
+    uint32_t grid = grid_for(p, p->dc->occ_adamw[p->variant]);
+    if (grid > n_chunks) grid = n_chunks;
+    void* args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a};
+    return launch(d, p->dc->k.adamw[p->variant], kAdamwNames[p->variant], grid, kThreads, stream, args);
 }
 }  // namespace
 
@@ -613,6 +621,20 @@ extern "C" int oe_adamw_step(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t
     if ((rc = validate_adamw(plan, hp)) != 0) return rc;
     CtxGuard guard(d, plan->dc->ctx);
     return launch_adamw(d, plan, hp, (CUstream)stream);
+}
+
+extern "C" int oe_adamw_step_chunks(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t first_chunk, uint64_t n_chunks,
+                                    uint64_t stream) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = validate_adamw(plan, hp)) != 0) return rc;
+    if (hp->step_dev != 0) return fail(OE_ERR_INVALID, "oe_adamw_step_chunks: a device step counter cannot be split over calls");
+    if (first_chunk > plan->n_chunks || n_chunks > plan->n_chunks - first_chunk)
+        return fail(OE_ERR_INVALID, "oe_adamw_step_chunks: range outside the plan's work units");
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_adamw(d, plan, hp, (CUstream)stream, nullptr, first_chunk, n_chunks);
 }
 
 extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream) {
@@ -864,7 +886,7 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
                                     uint64_t numel, uint64_t out, const float* scale, uint32_t flags, uint64_t stream) {
     if (!plan || !rank_bases || !scale) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: NULL argument");
     if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_peer_reduce_grads: 1 to 8 ranks are supported");
-    if (flags & ~OE_PARTIAL_ONLY) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
+    if (flags & ~(OE_PARTIAL_ONLY | OE_ACCUMULATE)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
     if (!isfinite(*scale)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: scale is not finite");
     if (numel > 0 && (out == 0 || (out & 3u))) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad output address");
     oe_peer_grads pg;

@@ -84,5 +84,6 @@ typedef struct oe_peer_grads {
 #define OE_F_NESTEROV     0x8u
 #define OE_F_MAXIMIZE     0x10u
 #define OE_F_PARTIAL_ONLY 0x20u /* norm pass: leave sumsq, do not finalise        */
+#define OE_F_ACCUMULATE   0x40u /* reduce pass: add to the record's sumsq instead of replacing it */
 
 #endif

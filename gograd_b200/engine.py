@@ -6,7 +6,7 @@ from dataclasses import dataclass
 from typing import Optional, Sequence
 
 from . import _lib
-from ._lib import (OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,
+from ._lib import (OE_ACCUMULATE, OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,
                    EngineError, check, lib)
 
 _initialised = set()
@@ -147,6 +147,11 @@ class Plan:
         c = hp.to_c()
         check(lib().oe_adamw_step(self._h, C.byref(c), _stream(stream)))
 
+    def adamw_step_chunks(self, hp: AdamWHParams, first_chunk: int, n_chunks: int, stream=None) -> None:
+        """The update over a contiguous range of the plan's work units (oe_adamw_step_chunks)."""
+        c = hp.to_c()
+        check(lib().oe_adamw_step_chunks(self._h, C.byref(c), first_chunk, n_chunks, _stream(stream)))
+
     def sgd_step(self, hp: SGDHParams, stream=None) -> None:
         c = hp.to_c()
         check(lib().oe_sgd_step(self._h, C.byref(c), _stream(stream)))
@@ -236,4 +241,4 @@ def launch_count_reset() -> None:
 
 __all__ = ["AdamWHParams", "SGDHParams", "TensorDesc", "Plan", "cast_bf16", "init", "launch_count",
            "launch_count_reset", "EngineError", "OE_CLIP_DEVFORM", "OE_WRITE_SHADOW", "OE_ZERO_GRAD", "OE_NESTEROV",
-           "OE_MAXIMIZE", "OE_PARTIAL_ONLY"]
+           "OE_MAXIMIZE", "OE_PARTIAL_ONLY", "OE_ACCUMULATE"]

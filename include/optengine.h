@@ -60,6 +60,7 @@ extern "C" {
 #define OE_NESTEROV      0x8u  /* SGDOptions.Nesterov (autograd/sgd.go:16-19)                        */
 #define OE_MAXIMIZE      0x10u /* SGDOptions.Maximize                                                */
 #define OE_PARTIAL_ONLY  0x20u /* oe_grad_norm: leave the sum of squares, do not take the root       */
+#define OE_ACCUMULATE    0x40u /* oe_peer_reduce_grads: add this call's sum of squares to the record     */
 
 /* One optimizer parameter. Mirrors what the reference keeps per parameter:
  * Tensor.buf / Tensor.gradBuf (autograd/tensor.go:19-52), AdamW.mGPU/vGPU
@@ -232,9 +233,18 @@ OE_API int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, co
  * rank k's gradient buffer; the kernel reads elements [first_elem, first_elem+numel) of each, adds
  * them in ascending rank order (deterministic), multiplies by *scale (1/n for a mean), writes the
  * reduced shard to `out` (may be this rank's own range, in place) and leaves the float64 sum of
- * squares of the reduced shard in the plan's norm record (and the norm, unless OE_PARTIAL_ONLY). */
+ * squares of the reduced shard in the plan's norm record (and the norm, unless OE_PARTIAL_ONLY).
+ * With OE_ACCUMULATE the sum is added to the record instead of replacing it, so a shard can be
+ * reduced piece by piece. The bases may equally point at local staging copies of the peers' ranges:
+ * only the address arithmetic base + 4*(first_elem + i) matters. */
 OE_API int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
                                 uint64_t numel, uint64_t out, const float* scale, uint32_t flags, uint64_t stream);
+
+/* oe_adamw_step over a contiguous range of the plan's work units (first_chunk .. first_chunk+n_chunks of
+ * oe_plan_info(plan, 1) units, in parameter order): lets a caller pipeline the update piece by piece
+ * against copies of the pieces already updated. Eager mode only (step_dev must be 0). */
+OE_API int oe_adamw_step_chunks(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t first_chunk, uint64_t n_chunks,
+                                uint64_t stream);
 
 /* oe_adamw_step whose bf16 shadow stores go to every rank's shadow buffer: shadow_deltas[k] is the
  * byte distance from this rank's shadow buffer to rank k's mapping (0 for the rank itself). The

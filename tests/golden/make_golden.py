@@ -16,7 +16,7 @@ from pathlib import Path
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--reference", type=Path, default=Path("/root/reference"))
+    ap.add_argument("--reference", type=Path, required=True, help="path of a gograd checkout")
     ap.add_argument("--output", type=Path, default=Path(__file__).resolve().parent / "optimizer_vectors.json")
     args = ap.parse_args()
     td = args.reference / "testdata"

@@ -251,3 +251,54 @@ def test_sharded_state_file_loads_into_unsharded_adamw_and_back(tmp_path):
         z2.close()
     finally:
         dist.destroy_process_group()
+
+
+def test_chunk_range_steps_and_accumulated_norm_equal_whole_launches():
+    """Piecewise forms of the two sharded-step kernels, on one GPU: the update over consecutive ranges of
+    work units equals one launch over the plan, and a shard reduced range by range with
+    OE_ACCUMULATE leaves the same reduced values and a sum of squares equal up to summation order."""
+    import gograd_b200 as eng
+    from gograd_b200.engine import OE_ACCUMULATE, OE_PARTIAL_ONLY, OE_WRITE_SHADOW
+    from gograd_b200.workload import bias_corrections
+
+    eng.init(0)
+    rng = np.random.default_rng(4)
+    sizes = [20000, 5, 4097, 12289]
+    state = {}
+    for tag in ("whole", "ranged"):
+        r = np.random.default_rng(4)
+        state[tag] = [[torch.from_numpy(r.normal(0, s, n).astype(np.float32)).cuda() for s in (.02, .01)] +
+                      [torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda"),
+                       torch.zeros(n, dtype=torch.int16, device="cuda")] for n in sizes]
+    plans = {tag: eng.Plan([eng.TensorDesc(p, g, m, v, sh, 1.0, 0.1) for p, g, m, v, sh in state[tag]])
+             for tag in state}
+    b1, b2 = bias_corrections(0.9, 0.999, 1)
+    hp = eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, b1, b2, 0.0, OE_WRITE_SHADOW)
+    plans["whole"].adamw_step(hp)
+    total = plans["ranged"].n_chunks
+    assert total == sum(-(-n // 4096) for n in sizes)
+    for first, count in ((0, 2), (2, 0), (2, 3), (5, total - 5)):
+        plans["ranged"].adamw_step_chunks(hp, first, count)
+    with pytest.raises(eng.engine.EngineError):
+        plans["ranged"].adamw_step_chunks(hp, total, 1)
+    for a, b in zip(state["whole"], state["ranged"]):
+        for x, y in zip(a, b):
+            assert torch.equal(x, y)
+    # reduction of a flat buffer in three ranges against one launch (two "ranks" on one device)
+    n = 3 * 8192
+    g0 = torch.from_numpy(rng.normal(0, 1e-2, n).astype(np.float32)).cuda()
+    g1 = torch.from_numpy(rng.normal(0, 1e-2, n).astype(np.float32)).cuda()
+    out_whole, out_ranged = torch.empty(n, device="cuda"), torch.empty(n, device="cuda")
+    plan = plans["whole"]
+    plan.peer_reduce_grads([g0.data_ptr(), g1.data_ptr()], 0, n, out_whole.data_ptr(), 0.5, OE_PARTIAL_ONLY)
+    _, whole_sq = plan.read_norm()
+    for k in range(3):
+        plan.peer_reduce_grads([g0.data_ptr(), g1.data_ptr()], k * 8192, 8192, out_ranged.data_ptr() + 4 * k * 8192, 0.5,
+                               OE_PARTIAL_ONLY | (OE_ACCUMULATE if k else 0))
+    _, ranged_sq = plan.read_norm()
+    assert torch.equal(out_whole, out_ranged)
+    assert abs(ranged_sq - whole_sq) <= 1e-12 * whole_sq
+    want = ((g0 + g1) * 0.5).double().pow(2).sum().item()
+    assert abs(whole_sq - want) <= 1e-12 * want
+    for p in plans.values():
+        p.close()
