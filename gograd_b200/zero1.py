@@ -98,6 +98,29 @@ class ShardLayout:
         return flat_index // self.shard_len
 
 
+def layout_fingerprint(layout: ShardLayout, group_of, hparams) -> str:
+    """A digest of everything the ranks of a sharded step must agree on."""
+    import hashlib
+    h = hashlib.sha256()
+    h.update(repr((layout.world, layout.align, layout.shard_len, layout.numels)).encode())
+    h.update(repr([(float(a), float(b)) for a, b in group_of]).encode())
+    h.update(repr([float(x) for x in hparams]).encode())
+    return h.hexdigest()
+
+
+def verify_same_layout(dist, fingerprint: str, group=None) -> None:
+    """Every rank publishes its fingerprint; a rank that was built from another parameter list,
+    other groups or other hyper-parameters would pull the wrong ranges of its peers' buffers, so
+    all ranks raise (each naming the ranks that differ from rank 0) before any device work."""
+    world = dist.get_world_size(group)
+    everyone = [None] * world
+    dist.all_gather_object(everyone, fingerprint, group=group)
+    odd = [r for r, f in enumerate(everyone) if f != everyone[0]]
+    if odd:
+        raise RuntimeError(f"sharded optimizer: ranks {odd} were configured differently from rank 0 "
+                           "(parameter sizes, groups or hyper-parameters); refusing to start")
+
+
 class _RawCuda:
     """Lets torch view a device address it does not own (the plan's norm record)."""
 
@@ -172,6 +195,8 @@ class Zero1AdamW(Zero1Schedule):
                          dist.get_world_size(process_group))
         self.device = device
         self.comm = comm
+        verify_same_layout(dist, layout_fingerprint(self.layout, group_of, (lr, beta1, beta2, eps, max_norm)),
+                           process_group)
         # The peer path reads other ranks' gradient buffers directly: by default a tiny
         # stream-ordered all-reduce at the start of a step makes sure they are complete. A
         # caller that already synchronised its ranks after backward can switch it off.

@@ -118,3 +118,51 @@ def test_llama1b_full_size_properties():
     norm2, sumsq2 = plan.read_norm()
     assert sumsq2 == 4.0 * sumsq and norm2 == np.float32(2.0) * np.float32(norm)
     plan.close()
+
+
+def test_indexing_beyond_2_to_32_elements():
+    """Flat shards of the 8B set are longer than 2^32 elements, so the reduce kernel indexes in 64 bits.
+    Two emulated ranks with 2^32 + 12,288 + 3 elements each (34 GB on the device): the reduced values
+    at sampled positions on both sides of the 2^31 and 2^32 boundaries and at the ragged end, and the
+    sum of squares against an independent float64 reduction."""
+    import gograd_b200 as eng
+    from gograd_b200.engine import OE_PARTIAL_ONLY
+
+    eng.init(0)
+    n = (1 << 32) + 12_288 + 3
+    free, _ = torch.cuda.mem_get_info()
+    if free < 40 * (1 << 30):
+        pytest.skip("needs 40 GB of free device memory")
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    g0 = torch.empty(n, dtype=torch.float32, device="cuda").normal_(0, 1e-3, generator=gen)
+    g1 = torch.empty(n, dtype=torch.float32, device="cuda").normal_(0, 1e-3, generator=gen)
+    windows = [(0, 4096), ((1 << 31) - 2048, (1 << 31) + 2048), ((1 << 32) - 2048, (1 << 32) + 2048), (n - 5000, n)]
+    want = [((g0[a:b] + g1[a:b]) * 0.5).cpu() for a, b in windows]
+    want_sq = 0.0
+    step = 1 << 28
+    for a in range(0, n, step):
+        want_sq += float(((g0[a:a + step] + g1[a:a + step]) * 0.5).double().pow(2).sum().item())
+    dummy = torch.zeros(8, device="cuda")
+    plan = eng.Plan([eng.TensorDesc(dummy, dummy)])
+    plan.peer_reduce_grads([g0.data_ptr(), g1.data_ptr()], 0, n, g0.data_ptr(), 0.5, OE_PARTIAL_ONLY)  # in place
+    _, got_sq = plan.read_norm()
+    assert abs(got_sq - want_sq) <= 1e-10 * want_sq
+    for (a, b), w in zip(windows, want):
+        assert torch.equal(g0[a:b].cpu(), w), (a, b)
+    plan.close()
+    del g0, g1
+    torch.cuda.empty_cache()
+    # the plan-based kernels take one tensor of more than 2^31 elements (a single descriptor)
+    m_elems = (1 << 31) + 4096 + 1
+    p = torch.full((m_elems,), 0.5, dtype=torch.float32, device="cuda")
+    g = torch.full((m_elems,), 2.0, dtype=torch.float32, device="cuda")
+    g[-1] = 3.0
+    plan = eng.Plan([eng.TensorDesc(p, g)])
+    plan.grad_norm()
+    norm, sumsq = plan.read_norm()
+    assert sumsq == 4.0 * (m_elems - 1) + 9.0
+    plan.sgd_step(eng.SGDHParams(0.125))
+    torch.cuda.synchronize()
+    assert float(p[0].item()) == 0.25 and float(p[(1 << 31) + 5].item()) == 0.25 and float(p[-1].item()) == 0.125
+    assert float(p.min().item()) == 0.125 and float(p.max().item()) == 0.25
+    plan.close()

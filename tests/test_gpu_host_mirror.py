@@ -378,3 +378,40 @@ def test_onecycle_schedule_values(ag):
         assert abs(c.LR() - want(step)) <= 1e-15
     with pytest.raises(ag.HostError, match="invalid OneCycle"):
         ag.OneCycle(0.1, 1, 0.25)
+
+
+def test_two_threads_clip_concurrently_and_read_their_own_norm(ag):
+    """autograd/cuda_concurrency_test.go:247-304: clip state belongs to the calling OS thread, so two
+    training runs clipping at the same time neither share a plan nor read each other's norm."""
+    import threading
+    results, errors = {}, []
+    barrier = threading.Barrier(2)
+
+    def run(tag, scale):
+        try:
+            rng = np.random.default_rng(hash(tag) % 1000)
+            grads = [rng.normal(0, scale, n).astype(np.float32) for n in (50_000, 17, 4096)]
+            params = [ag.Parameter(f"{tag}{i}", ag.Tensor(np.zeros(g.size, np.float32))) for i, g in enumerate(grads)]
+            want = math.sqrt(sum(float(np.sum(g.astype(np.float64) ** 2)) for g in grads))
+            for rep in range(20):
+                for p, g in zip(params, grads):
+                    p.Value.set_grad(g)
+                barrier.wait(timeout=60)
+                ag.ClipGradNorm(params, 1.0)
+                got = ag.GradientNormToHost()
+                assert abs(got - want) <= 1e-4 * want, (tag, rep, got, want)
+                coef = np.float32(1.0) / (np.float32(got) + np.float32(1e-6)) if got > 1.0 else np.float32(1.0)
+                assert np.array_equal(params[1].Value.grad_to_host(), grads[1] * coef)
+            results[tag] = got
+            ag.ReleaseClipState()
+        except Exception as e:  # surfaced in the main thread below
+            errors.append((tag, repr(e)))
+            barrier.abort()
+
+    threads = [threading.Thread(target=run, args=("a", 0.5)), threading.Thread(target=run, args=("b", 2.0))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(timeout=120)
+    assert not errors, errors
+    assert set(results) == {"a", "b"} and abs(results["a"] - results["b"]) > 1.0

@@ -176,3 +176,43 @@ def test_two_gloo_ranks_match_unsharded_oracle():
         assert np.array_equal(flat_m[o:o + n], ref.m[i]) and np.array_equal(flat_v[o:o + n], ref.v[i])
         for rank, lo, master, m, v, shadow, norms in results:
             assert np.array_equal(shadow[o:o + n], oracle.f32_to_bf16(ref.params[i])), f"rank {rank} shadow[{i}]"
+
+
+def _mismatch_worker(rank, world, port, queue):
+    import torch.distributed as dist
+    from gograd_b200.zero1 import layout_fingerprint, verify_same_layout
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    numels = list(NUMELS)
+    if rank == 1:
+        numels[2] += 1          # one rank was built from another model
+    fp = layout_fingerprint(ShardLayout(numels, world), GROUPS, (1e-3, .9, .95, 1e-8, 1.0))
+    try:
+        verify_same_layout(dist, fp)
+        queue.put((rank, "accepted"))
+    except RuntimeError as e:
+        queue.put((rank, str(e)))
+    same = layout_fingerprint(ShardLayout(NUMELS, world), GROUPS, (1e-3, .9, .95, 1e-8, 1.0))
+    verify_same_layout(dist, same)   # identical configurations pass
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ranks_with_different_layouts_refuse_to_start():
+    """A rank configured from another parameter list is detected on the host, on every rank, before
+    any kernel could read the wrong ranges of a peer's buffer."""
+    import torch.multiprocessing as mp
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_mismatch_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all("ranks [1] were configured differently" in results[r] for r in range(world)), results
