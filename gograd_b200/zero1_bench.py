@@ -20,6 +20,8 @@ def run(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
+    # NCCL's own banner/debug lines go to stderr: stdout carries exactly one JSON line.
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29531")
     torch.cuda.set_device(local)
