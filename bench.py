@@ -342,6 +342,68 @@ def run_single(args):
     return 0
 
 
+def run_secondary(args):
+    """Times the other kernels of the path on one large synthetic tensor set (CUDA events, median):
+    SGD update, in-place clip, stand-alone bf16 cast, gradient zeroing, the allocation-free norm."""
+    import torch
+
+    import gograd_b200 as eng
+    from gograd_b200 import _lib, paramsets, workload
+
+    ps = paramsets.get(args.workload if args.workload != "auto" else "llama1b")
+    torch.cuda.set_device(0)
+    eng.init(0)
+    state = workload.materialize(ps, "cuda:0")
+    n = state.numel
+    stream = torch.cuda.current_stream()
+    peak, peak_kind = measured_peak()
+
+    def timed(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for a, b in ev:
+            a.record(stream)
+            fn()
+            b.record(stream)
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in ev)
+
+    out = {}
+
+    def record(name, bytes_per_param, ms):
+        gbs = bytes_per_param * n / (ms * 1e-3) / 1e9
+        out[name] = {"bytes_per_param": bytes_per_param, "ms": ms, "GB/s": gbs, "frac_of_peak": gbs / peak}
+
+    flags1 = [torch.zeros(1, device="cuda:0") for _ in state.p]
+    descs = [eng.TensorDesc(state.p[i], state.g[i], state.s1[i], flags1[i], state.shadow[i]) for i in range(len(state.p))]
+    plan = eng.Plan(descs, 0, args.chunk)
+    record("oe_sgd_fused momentum (20 B)", 20, timed(lambda: plan.sgd_step(eng.SGDHParams(1e-3, 0.9), stream)))
+    record("oe_sgd_fused momentum + shadow (22 B)", 22,
+           timed(lambda: plan.sgd_step(eng.SGDHParams(1e-3, 0.9, flags=eng.engine.OE_WRITE_SHADOW), stream)))
+    plain = eng.Plan([eng.TensorDesc(state.p[i], state.g[i]) for i in range(len(state.p))], 0, args.chunk)
+    record("oe_sgd_fused plain (12 B)", 12, timed(lambda: plain.sgd_step(eng.SGDHParams(1e-3), stream)))
+    plain.grad_norm(0, stream)
+    record("oe_grad_sumsq + oe_scale_grads, clipping (4 + 8 B)", 12, timed(lambda: plain.clip_grad_norm(1e-3, 0, stream)))
+    record("oe_grad_sumsq + oe_scale_grads, not clipping (4 + 0 B)", 4, timed(lambda: plain.clip_grad_norm(1e30, 0, stream)))
+    record("oe_zero_grads (4 B)", 4, timed(lambda: plain.zero_grads(stream)))
+    big = max(range(len(state.p)), key=lambda i: state.p[i].numel())
+    src, dst = state.p[big], state.shadow[big]
+    ms = timed(lambda: eng.cast_bf16(src, dst, stream))
+    out["oe_cast_bf16 (6 B), one %d-element tensor" % src.numel()] = {
+        "bytes_per_param": 6, "ms": ms, "GB/s": 6 * src.numel() / (ms * 1e-3) / 1e9,
+        "frac_of_peak": 6 * src.numel() / (ms * 1e-3) / 1e9 / peak}
+    norm_out = torch.zeros(1, device="cuda:0")
+    ms = timed(lambda: _lib.check(_lib.lib().oe_grad_norm_static(0, src.data_ptr(), src.numel(), norm_out.data_ptr(),
+                                                                 int(stream.cuda_stream))))
+    out["oe_grad_norm_static (4 B), same tensor"] = {"bytes_per_param": 4, "ms": ms,
+                                                      "GB/s": 4 * src.numel() / (ms * 1e-3) / 1e9,
+                                                      "frac_of_peak": 4 * src.numel() / (ms * 1e-3) / 1e9 / peak}
+    print(json.dumps({"secondary_kernels": out, "params": n, "workload": ps.key, "peak_GBs": peak, "peak_kind": peak_kind}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -353,6 +415,7 @@ def main():
     ap.add_argument("--chunk", type=int, default=0)
     ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
                     help="N > 1: fused peer-memory kernels, or NCCL reduce-scatter / all-gather around the kernels")
+    ap.add_argument("--secondary", action="store_true", help="time the other kernels of the path instead of the step")
     ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -361,6 +424,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.secondary:
+        return run_secondary(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:
         from gograd_b200 import zero1_bench
