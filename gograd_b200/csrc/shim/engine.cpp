@@ -24,6 +24,7 @@ namespace {
 constexpr uint32_t kThreads = 256;             // must equal OE_THREADS of the kernels
 constexpr uint32_t kDefaultChunkElems = 4096;  // one pass of the update CTA: 256 threads x 4 vectors x 4 floats
 constexpr int kMaxDevices = 64;
+constexpr uint32_t kNormSpan = 2;               // must equal OE_NORM_SPAN of the kernels
 
 thread_local std::string t_error;
 
@@ -489,7 +490,10 @@ namespace {
 int launch_sumsq(const oe_driver* d, oe_plan* p, uint32_t flags, CUstream stream) {
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
     void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &p->d_norm, &p->d_partials, &flags};
-    return launch(d, p->dc->k.sumsq, "oe_grad_sumsq", grid_for(p, p->dc->occ_sumsq), kThreads, stream, args);
+    uint32_t grid = grid_for(p, p->dc->occ_sumsq);
+    uint32_t spans = (n_chunks + kNormSpan - 1) / kNormSpan;  // the kernel walks the table in spans of work units
+    if (grid > spans) grid = spans ? spans : 1;
+    return launch(d, p->dc->k.sumsq, "oe_grad_sumsq", grid, kThreads, stream, args);
 }
 
 int check_chunk_count(const oe_plan* p) {
