@@ -10,6 +10,12 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run with -m gpu on a B200)")
+    # A fresh checkout has no built libraries (they are not tracked): build them once.
+    built = [os.path.join(ROOT, "gograd_b200", "liboptengine.so"), os.path.join(ROOT, "gograd_b200", "libgograd_host.so"),
+             os.path.join(ROOT, "oracle", "liboptim_oracle.so")]
+    if not all(os.path.exists(p) for p in built):
+        import __graft_entry__
+        __graft_entry__.build()
 
 
 def pytest_collection_modifyitems(config, items):
