@@ -60,3 +60,21 @@ def test_parameter_set_sizes():
     assert [len(paramsets.get(k).params) for k in ("mlp", "cnn", "gpt", "llama1b", "llama8b")] == [4, 14, 145, 219, 291]
     sample = paramsets.scaled(paramsets.get("llama1b"), 120_000_000)
     assert len(sample.params) == 10 and sample.numel == 116_133_888
+
+
+def test_headers_are_plain_c(tmp_path):
+    """The boundary is a C ABI: both public headers compile as pedantic C11 and the struct sizes a
+    foreign binding hard-codes are the ones the compiler sees."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    src = tmp_path / "abi.c"
+    src.write_text('#include "optengine.h"\n#include "gograd_host.h"\n'
+                   "int main(void) { return sizeof(oe_tensor_desc) == 56 && sizeof(oe_adamw_hparams) == 48 &&\n"
+                   "                        sizeof(oe_sgd_hparams) == 40 && sizeof(gg_sgd_options) == 24 ? 0 : 1; }\n")
+    exe = tmp_path / "abi"
+    subprocess.run([cc, "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"),
+                    str(src), "-o", str(exe)], check=True)
+    assert subprocess.run([str(exe)]).returncode == 0
