@@ -1,0 +1,24 @@
+"""A plain-C program links liboptengine.so and drives the path with no Python in between."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_c_client_runs(tmp_path):
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    lib_dir = os.path.join(ROOT, "gograd_b200")
+    exe = tmp_path / "c_client"
+    subprocess.run([cc, "-std=c11", "-Wall", "-Wextra", os.path.join(lib_dir, "csrc", "examples", "c_client.c"),
+                    "-I", os.path.join(ROOT, "include"), "-L", lib_dir, "-loptengine", f"-Wl,-rpath,{lib_dir}", "-lm",
+                    "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert "c_client ok" in out.stdout
