@@ -313,6 +313,16 @@ def NewSGDGroups(params: Sequence[Parameter], options: SGDOptions, specs: Sequen
     return SGD(h, params)
 
 
+def PartitionParameters(params: Sequence[Parameter], assign) -> List[ParameterGroupSpec]:
+    """One spec per label returned by assign(name), in order of first appearance."""
+    names, handles, n = _param_arrays(params)
+    labels = (C.c_char_p * max(n, 1))(*[(assign(p.Name) or "").encode() for p in params])
+    buf = C.create_string_buffer(1 << 16)
+    _check(lib().gg_partition_parameters(names, handles, labels, n, buf, len(buf)))
+    by_name = {p.Name: p for p in params}
+    return [ParameterGroupSpec(g["Name"], [by_name[x] for x in g["Params"]]) for g in json.loads(buf.value.decode())]
+
+
 def ClipGradNorm(params: Sequence[Parameter], max_norm: float) -> float:
     """Scales the present gradients in place on the device; returns NaN like the reference
     (the norm stays on the device, read it with GradientNormToHost)."""

@@ -367,6 +367,27 @@ int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out) {
     });
 }
 
+int gg_partition_parameters(const char* const* names, gg_tensor* const* tensors, const char* const* labels, int32_t n,
+                            char* out, int32_t capacity) {
+    return guarded([&]() -> std::string {
+        std::vector<std::string> l;
+        for (int32_t i = 0; i < n; i++) l.push_back(labels && labels[i] ? labels[i] : "");
+        std::vector<ParameterGroupSpec> specs;
+        std::string e = PartitionParameters(make_params(names, tensors, n), l, &specs);
+        if (!e.empty()) return e;
+        std::string j = "[";
+        for (size_t g = 0; g < specs.size(); g++) {
+            j += std::string(g ? "," : "") + "{\"Name\":" + ggjson::quote(specs[g].Name) + ",\"Params\":[";
+            for (size_t k = 0; k < specs[g].Params.size(); k++) j += (k ? "," : "") + ggjson::quote(specs[g].Params[k].Name);
+            j += "]}";
+        }
+        j += "]";
+        if ((int32_t)j.size() + 1 > capacity) return "partition does not fit the buffer";
+        memcpy(out, j.c_str(), j.size() + 1);
+        return "";
+    });
+}
+
 int gg_clip_grad_norm(gg_tensor* const* tensors, int32_t n, const float* max_norm) {
     return guarded([&]() -> std::string {
         std::vector<Parameter> params;

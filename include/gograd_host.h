@@ -96,6 +96,12 @@ OE_API int gg_adamw_prepare_graph(gg_optimizer* o);                     /* Prepa
 OE_API int gg_adamw_step_captured(gg_optimizer* o);                     /* the capture branch of Step */
 OE_API int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out);    /* GraphStepCount */
 
+/* PartitionParameters (autograd/param_groups.go:63-102): labels[i] is what the caller's assign(name)
+ * returns for parameter i. Writes the resulting specs, in order of first appearance of each label, as
+ * JSON [{"Name":label,"Params":[names...]},...] into out. */
+OE_API int gg_partition_parameters(const char* const* names, gg_tensor* const* tensors, const char* const* labels,
+                                   int32_t n, char* out, int32_t capacity);
+
 /* ---- clip (autograd/nn.go:310-334, autograd/cuda_clip.go) ---- */
 OE_API int gg_clip_grad_norm(gg_tensor* const* tensors, int32_t n, const float* max_norm);
 OE_API int gg_gradient_norm_to_host(float* out);
