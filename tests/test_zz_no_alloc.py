@@ -13,7 +13,6 @@ other norm tests use. It also checks that an over-long input is refused before a
 Collected last on purpose (file name), and self-contained: it passes alone in a fresh
 process and after the rest of the suite.
 """
-import ctypes as C
 
 import numpy as np
 import pytest
