@@ -370,7 +370,7 @@ __device__ __forceinline__ double oe_block_sum(double x, double* warp_sums) {
     return total;  // valid in thread 0
 }
 
-// Level 1: every CTA accumulates its chunks in double (the host oracle sums in
+// Level 1: every CTA accumulates its chunks in double (the reference's host code sums in
 // float64 too, autograd/nn.go:319-324) and writes one partial. Level 2: the CTA that
 // arrives last adds the partials in index order, so the result depends only on the
 // grid size, never on timing; it stores sum, norm = (float)sqrt(sum) and re-arms the
