@@ -209,6 +209,79 @@ def test_all_real_ranks_of_the_box(comm):
             assert np.array_equal(shadow[o:o + n], own), f"rank {rank} shadow[{i}] ({comm})"
 
 
+def test_sharded_state_file_loads_into_unsharded_adamw_and_back(tmp_path):
+    """The sharded optimizer writes its gathered moments in the reference's per-tensor layout
+    ("gograd-adamw": m.<i>, v.<i>, configuration metadata). The unsharded host-mirror AdamW loads that
+    file and both continue bit for bit; the file the unsharded optimizer writes loads back into a
+    sharded one. One rank on one GPU is enough to exercise the layout code."""
+    import torch.distributed as dist
+    from gograd_b200 import autograd as ag
+    from gograd_b200.zero1 import Zero1AdamW
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        names = [f"t{i}" for i in range(len(NUMELS))]
+        shapes = [[n] for n in NUMELS]
+        groups = [(1.0, 0.1)] * len(NUMELS)
+        z = Zero1AdamW(NUMELS, groups, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], 0, comm="peer")
+        L = z.layout
+        weights = torch.zeros(L.total)
+        for o, w in zip(L.offsets, _weights()):
+            weights[o:o + w.size] = torch.from_numpy(w)
+        z.load_master(weights.cuda())
+
+        def sharded_step(opt, step):
+            opt.grad_flat.zero_()
+            for view, g in zip(opt.grads, _grads(0, step)):
+                view.copy_(torch.from_numpy(g))
+            opt.step()
+
+        for step in (1, 2):
+            sharded_step(z, step)
+        path = str(tmp_path / "sharded.safetensors")
+        z.save_state(path, names, shapes)
+        d = ag.safetensors_describe(path)
+        assert d["metadata"]["format"] == "gograd-adamw" and d["metadata"]["step_count"] == "2"
+        assert sorted(d["entries"]) == sorted([f"m.{i}" for i in range(len(NUMELS))] + [f"v.{i}" for i in range(len(NUMELS))])
+        # unsharded optimizer over the same weights
+        torch.cuda.synchronize()
+        flat = z.master.cpu().numpy()
+        params = [ag.Parameter(n, ag.Tensor(flat[o:o + k])) for n, o, k in zip(names, L.offsets, NUMELS)]
+        u = ag.NewAdamW(params, 1.0, 0.1)
+        u.LoadSafeTensors(path)
+        assert u.StepCount == 2 and u.LearningRate() == np.float32(HP["lr"])
+        sharded_step(z, 3)
+        for p, g in zip(params, _grads(0, 3)):
+            p.Value.set_grad(g)
+        u.StepClipped(HP["max_norm"])
+        torch.cuda.synchronize()
+        flat = z.master.cpu().numpy()
+        for p, o, k in zip(params, L.offsets, NUMELS):
+            assert np.array_equal(p.Value.to_host(), flat[o:o + k]), p.Name
+        # and back: the unsharded file into a fresh sharded optimizer
+        back = str(tmp_path / "unsharded.safetensors")
+        u.SaveSafeTensors(back)
+        z2 = Zero1AdamW(NUMELS, groups, 9.0, 0.5, 0.5, 1e-3, HP["max_norm"], 0, comm="nccl")
+        z2.load_master(z.master.new_zeros(L.total).index_copy_(0, torch.arange(L.shard_len, device="cuda"), z.master))
+        z2.load_state(back, names, shapes)
+        assert z2.step_count == 3 and np.float32(z2.lr) == np.float32(HP["lr"]) and np.float32(z2.beta2) == np.float32(HP["beta2"])
+        assert torch.equal(z2.m, z.m) and torch.equal(z2.v, z.v)
+        sharded_step(z, 4)
+        sharded_step(z2, 4)
+        torch.cuda.synchronize()
+        assert torch.equal(z2.master, z.master) and torch.equal(z2.shadow_flat, z.shadow_flat)
+        with pytest.raises(ValueError, match="name or shape"):
+            z2.load_state(back, names[::-1], shapes)
+        z.close()
+        z2.close()
+    finally:
+        dist.destroy_process_group()
+
+
 def test_chunk_range_steps_and_accumulated_norm_equal_whole_launches():
     """Piecewise forms of the two sharded-step kernels, on one GPU: the update over consecutive ranges of
     work units equals one launch over the plan, and a shard reduced range by range with
