@@ -20,8 +20,12 @@ def run(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     world = int(os.environ.get("WORLD_SIZE", str(args.gpus)))
-    # NCCL's own banner/debug lines go to stderr: stdout carries exactly one JSON line.
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # stdout carries exactly one JSON line: whatever libraries print on file descriptor 1 while the
+    # ranks run (NCCL's version banner, for one) is sent to stderr until the line is written.
+    import sys
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29531")
     torch.cuda.set_device(local)
@@ -139,7 +143,10 @@ def run(args) -> int:
                        "grad_norm": norm_value},
             "roofline": roofline, "cpu_baseline": None, "e2e": e2e, "clocks": clocks, "gpu_launches": launches,
         }
+        sys.stdout.flush()
+        os.dup2(real_stdout, 1)
         print(json.dumps(line), flush=True)
+        os.dup2(2, 1)
     opt.close()
     dist.destroy_process_group()
     return 0
