@@ -51,6 +51,9 @@ def lib() -> C.CDLL:
         h.gg_tensor_numel.restype = C.c_int64
         h.gg_opt_step_count.restype = C.c_int64
         h.gg_tensor_address.restype = C.c_uint64
+        h.gg_tensor_shadow_lease.restype = C.c_uint64
+        h.gg_tensor_shadow_release.restype = None
+        h.gg_tensor_shadow_release.argtypes = [C.c_void_p, C.c_uint64]
         h.gg_tensor_free.restype = None
         h.gg_opt_free.restype = None
         h.gg_release_clip_state.restype = None
@@ -124,6 +127,17 @@ class Tensor:
 
     def address(self, which: int = 0) -> int:
         return int(lib().gg_tensor_address(self._h, which))
+
+    def shadow_lease(self) -> int:
+        """Takes a lease on the current bf16 shadow and returns its device address."""
+        return int(lib().gg_tensor_shadow_lease(self._h))
+
+    def shadow_release(self, address: int) -> None:
+        lib().gg_tensor_shadow_release(self._h, address)
+
+    @property
+    def leased_shadows(self) -> int:
+        return int(lib().gg_tensor_leased_shadows(self._h))
 
     def close(self) -> None:
         if self._h:

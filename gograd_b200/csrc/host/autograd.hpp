@@ -55,10 +55,20 @@ class Tensor {
     std::string EnsureShadow();                              // allocates the bf16 buffer (not the cast)
     std::string ShadowToHost(std::vector<uint16_t>* out) const;
     bool ShadowCurrent() const { return bf16Buf != 0 && bf16Version == version; }
+    // Leases (autograd/cuda_autocast.go:77-94): a graph node that keeps a raw pointer to the shadow
+    // for its backward pass takes a lease; while leases are out, an optimizer step must not
+    // overwrite that buffer — it gets a fresh one to write into, and the leased buffer lives until
+    // its last lease is returned. AcquireShadowLease returns the leased address (0 without a shadow).
+    uint64_t AcquireShadowLease();
+    void ReleaseShadowLease(uint64_t address);
+    std::string ShadowForWriting();  // EnsureShadow, or a fresh buffer when the current one is leased
+    int LeasedShadowBuffers() const { return (int)retired_.size() + (leases_ > 0 ? 1 : 0); }
     void Close();
 
    private:
     bool closed_ = false;
+    int leases_ = 0;                                  // leases on the current bf16Buf
+    std::vector<std::pair<uint64_t, int>> retired_;   // replaced buffers that still have leases
 };
 
 struct Parameter {

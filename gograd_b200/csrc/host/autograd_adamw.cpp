@@ -102,7 +102,7 @@ std::string AdamW::refreshPlan() {
         Tensor& t = *Params[i].Value;
         if (t.Numel() == 0) continue;
         if (Engine.WriteShadow && t.gradBuf != 0) {
-            std::string e = t.EnsureShadow();
+            std::string e = t.ShadowForWriting();  // never the buffer a graph node still leases
             if (!e.empty()) return e;
         }
         const ParameterGroup& g = groups_[groupOf_[i]];

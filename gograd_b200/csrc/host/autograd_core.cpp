@@ -61,6 +61,8 @@ void Tensor::Close() {
     oe_mem_free(Device, buf);
     oe_mem_free(Device, gradBuf);
     oe_mem_free(Device, bf16Buf);
+    for (auto& r : retired_) oe_mem_free(Device, r.first);
+    retired_.clear();
     buf = gradBuf = bf16Buf = 0;
 }
 
@@ -121,6 +123,38 @@ std::string Tensor::EnsureShadow() {
     if (bf16Buf != 0 || Numel() == 0) return "";
     GG_TRY(oe_mem_alloc(Device, (uint64_t)Numel() * 2, &bf16Buf), "oe_mem_alloc");
     return "";
+}
+
+uint64_t Tensor::AcquireShadowLease() {
+    if (bf16Buf == 0) return 0;
+    leases_++;
+    return bf16Buf;
+}
+
+void Tensor::ReleaseShadowLease(uint64_t address) {
+    if (address == 0) return;
+    if (address == bf16Buf && leases_ > 0) {
+        leases_--;
+        return;
+    }
+    for (size_t i = 0; i < retired_.size(); i++) {
+        if (retired_[i].first != address) continue;
+        if (--retired_[i].second <= 0) {
+            oe_mem_free(Device, address);  // the last reader is gone
+            retired_.erase(retired_.begin() + (long)i);
+        }
+        return;
+    }
+}
+
+std::string Tensor::ShadowForWriting() {
+    if (bf16Buf != 0 && leases_ > 0) {
+        // Someone still reads the current shadow: keep it alive for them and write elsewhere.
+        retired_.push_back({bf16Buf, leases_});
+        bf16Buf = 0;
+        leases_ = 0;
+    }
+    return EnsureShadow();
 }
 
 std::string Tensor::ShadowToHost(std::vector<uint16_t>* out) const {

@@ -145,7 +145,7 @@ std::string SGD::refreshPlan() {
     for (size_t i = 0; i < Params.size(); i++) {
         Tensor& t = *Params[i].Value;
         if (Engine.WriteShadow && t.gradBuf != 0) {
-            std::string e = t.EnsureShadow();
+            std::string e = t.ShadowForWriting();  // never the buffer a graph node still leases
             if (!e.empty()) return e;
         }
         const ParameterGroup& g = groups_[groupOf_[i]];

@@ -157,6 +157,12 @@ uint64_t gg_tensor_address(const gg_tensor* t, int32_t which) {
     return which == 0 ? t->t->buf : which == 1 ? t->t->gradBuf : t->t->bf16Buf;
 }
 
+uint64_t gg_tensor_shadow_lease(gg_tensor* t) { return t ? t->t->AcquireShadowLease() : 0; }
+void gg_tensor_shadow_release(gg_tensor* t, uint64_t address) {
+    if (t) t->t->ReleaseShadowLease(address);
+}
+int gg_tensor_leased_shadows(const gg_tensor* t) { return t ? t->t->LeasedShadowBuffers() : 0; }
+
 int gg_adamw_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr, const float* decay,
                  gg_optimizer** out) {
     if (!out || !lr || !decay) return fail("NULL argument");

@@ -65,6 +65,12 @@ OE_API int gg_tensor_grad_to_host(const gg_tensor* t, float* out);
 OE_API int gg_tensor_shadow_to_host(const gg_tensor* t, uint16_t* out);
 OE_API int gg_tensor_shadow_current(const gg_tensor* t);           /* 1 when the bf16 shadow matches the value */
 OE_API uint64_t gg_tensor_address(const gg_tensor* t, int32_t which); /* 0 value, 1 gradient, 2 shadow */
+/* bf16 shadow leases (autograd/cuda_autocast.go:77-94): a reader that keeps the shadow's address across an
+ * optimizer step takes a lease; the step then writes a fresh buffer and the leased one stays valid until
+ * released. gg_tensor_shadow_lease returns the leased device address (0 when there is no shadow). */
+OE_API uint64_t gg_tensor_shadow_lease(gg_tensor* t);
+OE_API void gg_tensor_shadow_release(gg_tensor* t, uint64_t address);
+OE_API int gg_tensor_leased_shadows(const gg_tensor* t); /* buffers currently kept alive by leases */
 
 /* ---- optimizers (autograd/nn.go:385-537, autograd/sgd.go:76-257) ---- */
 OE_API int gg_adamw_new(const char* const* names, gg_tensor* const* tensors, int32_t n, const float* lr,

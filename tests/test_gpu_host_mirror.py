@@ -415,3 +415,43 @@ def test_two_threads_clip_concurrently_and_read_their_own_norm(ag):
         t.join(timeout=120)
     assert not errors, errors
     assert set(results) == {"a", "b"} and abs(results["a"] - results["b"]) > 1.0
+
+
+def test_shadow_lease_survives_an_optimizer_step(ag):
+    """autograd/cuda_autocast.go:77-94, autograd/audit_bf16_lease_test.go: a reader that leased the bf16
+    shadow before the step (a graph node waiting for its backward pass) keeps a valid, unchanged
+    buffer; the step writes its new shadow elsewhere; returning the lease frees the old buffer; with
+    no lease out the step rewrites the shadow in place."""
+    import ctypes as C
+    from gograd_b200 import _lib
+    rng = np.random.default_rng(12)
+    w = ag.Tensor(rng.normal(0, .05, 5000).astype(np.float32))
+    p = [ag.Parameter("w", w)]
+    opt = ag.NewAdamW(p, 1e-2, 0.0)
+    opt.SetEngine(write_shadow=True)
+
+    def bf16_at(address, n):
+        out = np.empty(n, np.uint16)
+        _lib.check(_lib.lib().oe_memcpy_d2h(0, out.ctypes.data_as(C.c_void_p), address, 2 * n, 0))
+        _lib.check(_lib.lib().oe_stream_sync(0, 0))
+        return out
+
+    w.set_grad(rng.normal(0, .1, 5000).astype(np.float32))
+    opt.Step()
+    first = w.shadow_to_host().copy()
+    first_address = w.address(2)
+    lease = w.shadow_lease()
+    assert lease == first_address and w.leased_shadows == 1
+    opt.Step()                                   # must not overwrite the leased buffer
+    assert w.address(2) != first_address and w.shadow_current
+    assert np.array_equal(bf16_at(lease, 5000), first), "the leased shadow changed under its reader"
+    second = w.shadow_to_host()
+    assert not np.array_equal(second, first)
+    want = torch.from_numpy(w.to_host()).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+    assert np.array_equal(second, want)
+    assert w.leased_shadows == 1
+    w.shadow_release(lease)
+    assert w.leased_shadows == 0
+    in_place = w.address(2)
+    opt.Step()                                   # nobody reads the shadow: rewritten in place
+    assert w.address(2) == in_place and w.shadow_current
