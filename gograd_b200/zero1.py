@@ -121,6 +121,54 @@ def verify_same_layout(dist, fingerprint: str, group=None) -> None:
                            "(parameter sizes, groups or hyper-parameters); refusing to start")
 
 
+class RankLost(RuntimeError):
+    """A rank did not reach the step the others are about to launch."""
+
+    def __init__(self, step: int, missing: Sequence[int], detail: str = ""):
+        self.step, self.missing = step, list(missing)
+        who = f"ranks {self.missing}" if self.missing else "a rank (the store no longer answers)"
+        super().__init__(f"sharded optimizer: {who} did not reach step {step}; nothing was launched"
+                         + (f" ({detail})" if detail else ""))
+
+
+class PeerLiveness:
+    """Host-side roll call before a sharded step.
+
+    Every rank writes a key for the step it is about to launch into the job's key-value
+    store and waits, with a short limit, for the keys of all the others. A rank that raised,
+    exited or never joined is so found on the host, between steps, before any kernel reads a
+    peer's buffer or a collective is enqueued that could never complete; the step counter
+    and the optimizer state of the surviving ranks are left as they were. The wait is a host
+    wait on the store: no GPU work is involved and nothing on a device can block on it."""
+
+    def __init__(self, store, rank: int, world: int, timeout_s: float = 5.0, prefix: str = "oe/alive"):
+        if timeout_s <= 0:
+            raise ValueError("timeout_s must be positive")
+        self.store, self.rank, self.world, self.timeout_s, self.prefix = store, rank, world, timeout_s, prefix
+
+    def _key(self, step: int, rank: int) -> str:
+        return f"{self.prefix}/{step}/{rank}"
+
+    def arrive(self, step: int) -> None:
+        from datetime import timedelta
+        keys = [self._key(step, r) for r in range(self.world)]
+        try:
+            self.store.set(keys[self.rank], "1")
+            self.store.wait(keys, timedelta(seconds=self.timeout_s))
+        except Exception as e:  # a timeout or a lost connection: find out who is missing
+            missing = []
+            try:
+                missing = [r for r in range(self.world) if not self.store.check([keys[r]])]
+            except Exception:
+                pass
+            raise RankLost(step, missing, type(e).__name__) from e
+        if step > 2:  # every rank that passed step-1 has finished reading the keys of step-2
+            try:
+                self.store.delete_key(self._key(step - 2, self.rank))
+            except Exception:
+                pass
+
+
 class _RawCuda:
     """Lets torch view a device address it does not own (the plan's norm record)."""
 
@@ -147,12 +195,15 @@ class Zero1Schedule:
         self.layout = ShardLayout(numels, world)
         self.lo, self.hi = self.layout.shard_range(rank)
         self.my_pieces = self.layout.pieces(rank)
+        self.liveness: Optional[PeerLiveness] = None   # set one to have every step begin with a roll call
 
     def bias_corrections(self) -> Tuple[float, float]:
         from .workload import bias_corrections
         return bias_corrections(self.beta1, self.beta2, self.step_count)
 
     def step(self) -> None:
+        if self.liveness is not None:
+            self.liveness.arrive(self.step_count + 1)   # raises RankLost before anything is launched
         self.step_count += 1          # one shared counter, as AdamW.Step keeps (autograd/nn.go:492)
         self.reduce_grads()           # mean over ranks of this rank's shard + its sum of squares
         self.combine_sumsq()          # sum over ranks -> global norm

@@ -209,6 +209,81 @@ def test_all_real_ranks_of_the_box(comm):
             assert np.array_equal(shadow[o:o + n], own), f"rank {rank} shadow[{i}] ({comm})"
 
 
+def _leaving_rank_main(rank, world, port, queue):
+    """Rank 1 leaves after step 1, between steps: every rank has synchronised its device and met
+    the others in the store first, so nothing of the leaving rank is in flight anywhere."""
+    from datetime import timedelta
+
+    import torch.distributed as dist
+    from gograd_b200.zero1 import PeerLiveness, RankLost, Zero1AdamW
+    os.environ["NCCL_NVLS_ENABLE"] = "0"          # plain peer transport only; no switch-side objects
+    torch.cuda.set_device(rank)
+    store = dist.TCPStore("127.0.0.1", port, is_master=False, timeout=timedelta(seconds=60))
+    dist.init_process_group("nccl", store=dist.PrefixStore("pg", store), rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank, comm="peer")
+    opt.liveness = PeerLiveness(store, rank, world, timeout_s=2.0)
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+
+    def load(step):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+
+    load(1)
+    opt.step()
+    torch.cuda.synchronize()
+    store.set(f"idle/{rank}", "1")
+    store.wait([f"idle/{r}" for r in range(world)], timedelta(seconds=60))   # every device is idle now
+    if rank == 1:
+        result = "left between steps"
+    else:
+        before = [t.clone() for t in (opt.master, opt.m, opt.v, opt.shadow_flat.view(torch.int16))]
+        load(2)
+        try:
+            opt.step()
+            result = "stepped"
+        except RankLost as e:
+            torch.cuda.synchronize()               # the context still answers
+            after = (opt.master, opt.m, opt.v, opt.shadow_flat.view(torch.int16))
+            same = all(bool(torch.equal(a, b)) for a, b in zip(before, after))
+            result = (e.missing, e.step, opt.step_count, same)
+    queue.put((rank, result))
+    queue.close()
+    queue.join_thread()
+    opt.close()                                    # local: unmaps the peers' buffers, frees the plan
+    os._exit(0)                                    # no communicator teardown against a rank that is gone
+
+
+def test_a_rank_that_left_is_found_before_the_next_launch():
+    """Two real ranks on the peer path. Rank 1 exits between steps with nothing in flight; rank 0's
+    next step starts with the roll call, which names rank 1 within its limit and launches nothing:
+    the step counter, the shard of p/m/v and the shadow keep their values and the device still works."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from datetime import timedelta
+
+    import torch.distributed as dist
+    import torch.multiprocessing as mp
+    world = 2
+    server = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False, timeout=timedelta(seconds=60))
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_leaving_rank_main, args=(r, world, server.port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert results[1] == "left between steps"
+    assert results[0] == ([1], 2, 1, True), results
+
+
 def test_sharded_state_file_loads_into_unsharded_adamw_and_back(tmp_path):
     """The sharded optimizer writes its gathered moments in the reference's per-tensor layout
     ("gograd-adamw": m.<i>, v.<i>, configuration metadata). The unsharded host-mirror AdamW loads that

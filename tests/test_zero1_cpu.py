@@ -216,3 +216,75 @@ def test_ranks_with_different_layouts_refuse_to_start():
         p.join(timeout=60)
         assert p.exitcode == 0
     assert all("ranks [1] were configured differently" in results[r] for r in range(world)), results
+
+
+def _roll_call_worker(rank, world, port, queue):
+    from datetime import timedelta
+
+    import torch.distributed as dist
+    from gograd_b200.zero1 import PeerLiveness, RankLost
+    store = dist.TCPStore("127.0.0.1", port, is_master=False, timeout=timedelta(seconds=30))
+    dist.init_process_group("gloo", store=dist.PrefixStore("pg", store), rank=rank, world_size=world)
+    opt = OracleRank(NUMELS, GROUPS, HP, rank, world, dist, _weights())
+    opt.liveness = PeerLiveness(store, rank, world, timeout_s=2.0)
+
+    def load(step):
+        opt.grad_flat[:] = 0
+        for o, g in zip(opt.layout.offsets, _inputs(rank, step)):
+            opt.grad_flat[o:o + g.size] = g
+
+    load(1)
+    opt.step()
+    if rank == 1:
+        queue.put((rank, "left between steps"))   # no kernel, no collective of this rank is in flight
+        return
+    before = (opt.master.copy(), opt.m.copy(), opt.v.copy(), opt.shadow_flat.copy())
+    load(2)
+    try:
+        opt.step()
+        queue.put((rank, "stepped"))
+    except RankLost as e:
+        same = all(np.array_equal(a, b) for a, b in zip(before, (opt.master, opt.m, opt.v, opt.shadow_flat)))
+        queue.put((rank, (e.missing, e.step, opt.step_count, same)))
+
+
+def test_a_rank_that_left_is_found_on_the_host_before_the_next_step():
+    """Three gloo ranks; rank 1 leaves after step 1. The others learn of it from the roll call in
+    the key-value store within its limit: step 2 launches nothing, the step counter and the state
+    keep their values, and the error names the missing rank."""
+    from datetime import timedelta
+
+    import torch.distributed as dist
+    import torch.multiprocessing as mp
+    world = 3
+    server = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False, timeout=timedelta(seconds=30))
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_roll_call_worker, args=(r, world, server.port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert results[1] == "left between steps"
+    for r in (0, 2):
+        assert results[r] == ([1], 2, 1, True), results
+
+
+def test_roll_call_passes_when_everyone_is_there():
+    from datetime import timedelta
+
+    import torch.distributed as dist
+    from gograd_b200.zero1 import PeerLiveness
+    server = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False, timeout=timedelta(seconds=30))
+    a, b = PeerLiveness(server, 0, 2, 1.0), PeerLiveness(server, 1, 2, 1.0)
+    import threading
+    for step in range(1, 6):
+        t = threading.Thread(target=b.arrive, args=(step,))
+        t.start()
+        a.arrive(step)
+        t.join()
+    assert not server.check(["oe/alive/1/0"]) and server.check(["oe/alive/5/0"])
+    with pytest.raises(ValueError):
+        PeerLiveness(server, 0, 2, 0.0)
