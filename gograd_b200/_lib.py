@@ -53,6 +53,7 @@ PROTOTYPES = {
     "oe_plan_info": (C.c_int64, [_plan, _i]),
     "oe_plan_norm_address": (_u64, [_plan]),
     "oe_plan_set_variant": (_i, [_plan, C.c_char_p]),
+    "oe_plan_set_grad_scale": (_i, [_plan, C.POINTER(C.c_float)]),
     "oe_grad_norm": (_i, [_plan, _u32, _u64]),
     "oe_norm_finalize": (_i, [_plan, _u64]),
     "oe_clip_grad_norm": (_i, [_plan, C.POINTER(C.c_float), _u32, _u64]),

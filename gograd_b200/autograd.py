@@ -34,6 +34,10 @@ class _OneCycle(C.Structure):
                 ("final_div_factor", C.c_double), ("total", C.c_int32), ("step_count", C.c_int32)]
 
 
+class _Accumulator(C.Structure):
+    _fields_ = [("groups", C.c_int32), ("pending", C.c_int32)]
+
+
 class _Groups(C.Structure):
     _fields_ = [("n_groups", C.c_int32), ("group_names", C.POINTER(C.c_char_p)), ("offsets", C.POINTER(C.c_int32)),
                 ("members", C.POINTER(C.c_int32)), ("lr_scales", _f32p), ("decays", _f32p)]
@@ -57,6 +61,7 @@ def lib() -> C.CDLL:
         h.gg_tensor_free.restype = None
         h.gg_opt_free.restype = None
         h.gg_release_clip_state.restype = None
+        h.gg_accumulator_reset.restype = None
         _lib = h
     return _lib
 
@@ -236,6 +241,10 @@ class _Optimizer:
     def SetEngine(self, write_shadow: bool = False, clip_devform: bool = False) -> None:
         _check(lib().gg_opt_set_engine(self._h, int(write_shadow), int(clip_devform)))
 
+    def SetGradScale(self, scale: float) -> None:
+        """Step and StepClipped read every gradient element as float32(g * scale) from now on."""
+        _check(lib().gg_opt_set_grad_scale(self._h, _f(scale)))
+
     def groupScale(self, index: int):
         a, b = C.c_float(), C.c_float()
         _check(lib().gg_opt_group_scale(self._h, index, C.byref(a), C.byref(b)))
@@ -353,6 +362,29 @@ def GradientNormToHost() -> float:
 
 def ReleaseClipState() -> None:
     lib().gg_release_clip_state()
+
+
+class GradAccumulator:
+    """The bookkeeping of autograd.GradAccumulator (autograd/accumulate.go:15-71)."""
+
+    def __init__(self, groups: int):
+        self._a = _Accumulator()
+        _check(lib().gg_accumulator_new(groups, C.byref(self._a)))
+
+    def MicroBatch(self):
+        """What Backward does around the differentiation: (seed 1/groups, group complete?)."""
+        seed, done = C.c_float(), C.c_int32()
+        _check(lib().gg_accumulator_micro_batch(C.byref(self._a), C.byref(seed), C.byref(done)))
+        return np.float32(seed.value), bool(done.value)
+
+    def Pending(self) -> int:
+        return self._a.pending
+
+    def Groups(self) -> int:
+        return self._a.groups
+
+    def Reset(self) -> None:
+        lib().gg_accumulator_reset(C.byref(self._a))
 
 
 class OneCycle:

@@ -167,6 +167,10 @@ struct EngineOptions {
     bool WriteShadow = false;
     bool ClipDevForm = false;  // the CUDA kernels' fminf(1, .) rule instead of the host rule
     uint64_t Stream = 0;
+    // Step and StepClipped read every gradient element as (float)(g * GradScale): the 1/groups
+    // factor of gradient accumulation, applied in the pass that reads the gradients anyway
+    // instead of through the seed of every backward.
+    float GradScale = 1.0f;
 };
 
 class AdamW : public CheckpointOptimizer {
@@ -265,6 +269,20 @@ class SGD : public CheckpointOptimizer {
 float ClipGradNorm(const std::vector<Parameter>& params, float maxNorm);
 float GradientNormToHost();  // last norm of the calling thread on its device (autograd/nn.go:17-27)
 void ReleaseClipState();     // frees the calling thread's clip plans
+
+// GradAccumulator's bookkeeping (autograd/accumulate.go:15-71). Backward itself belongs to the
+// autograd graph; MicroBatch() is what Backward does around it: it hands out the seed 1/groups,
+// counts the micro-batch and reports whether the group is complete. A caller that accumulates
+// unseeded gradients passes SeedScale() to EngineOptions::GradScale instead.
+struct GradAccumulator {
+    int groups = 0, pending = 0;
+    static std::string New(int groups, GradAccumulator* out);
+    std::string MicroBatch(float* seed, bool* complete);
+    float SeedScale() const { return 1.0f / (float)groups; }
+    int Pending() const { return pending; }
+    int Groups() const { return groups; }
+    void Reset() { pending = 0; }
+};
 
 // OneCycle schedule (autograd/nn.go:539-571).
 struct OneCycle {

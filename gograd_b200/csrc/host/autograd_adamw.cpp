@@ -126,6 +126,7 @@ std::string AdamW::refreshPlan() {
 void AdamW::run(float maxNorm, bool captured) {
     if (closed_) throw std::runtime_error("autograd: AdamW is closed");
     if (captured && graphStep_ == 0) throw std::runtime_error("autograd: call AdamW.PrepareGraph before capture");
+    if (!std::isfinite(Engine.GradScale) || !(Engine.GradScale > 0)) throw std::runtime_error("autograd: invalid gradient scale");
     if (!captured) {
         if (graphStep_ != 0) {
             std::string e = SyncGraphStepCount();
@@ -135,6 +136,8 @@ void AdamW::run(float maxNorm, bool captured) {
     }
     std::string e = refreshPlan();
     if (!e.empty()) throw std::runtime_error(e);
+    int rc = oe_plan_set_grad_scale(plan_, &Engine.GradScale);
+    if (rc != 0) throw std::runtime_error(engine_error("oe_plan_set_grad_scale", rc));
     oe_adamw_hparams hp;
     memset(&hp, 0, sizeof hp);
     hp.lr = LR;
@@ -149,7 +152,6 @@ void AdamW::run(float maxNorm, bool captured) {
     }
     hp.max_norm = maxNorm;
     hp.flags = (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u);
-    int rc = 0;
     if (maxNorm > 0 && (rc = oe_grad_norm(plan_, 0, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_grad_norm", rc));
     if ((rc = oe_adamw_step(plan_, &hp, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_adamw_step", rc));
     if (!captured) {

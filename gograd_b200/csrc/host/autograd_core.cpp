@@ -394,6 +394,26 @@ void ReleaseClipState() {
 }
 
 // -------------------------------------------------------------------------------------
+// GradAccumulator bookkeeping (autograd/accumulate.go:21-71)
+// -------------------------------------------------------------------------------------
+std::string GradAccumulator::New(int groups, GradAccumulator* out) {
+    if (groups < 1) return "autograd: gradient accumulation needs at least one micro-batch";
+    out->groups = groups;
+    out->pending = 0;
+    return "";
+}
+
+std::string GradAccumulator::MicroBatch(float* seed, bool* complete) {
+    if (groups < 1) return "autograd: invalid gradient accumulator";
+    if (seed) *seed = 1.0f / (float)groups;  // what Backward seeds differentiation with
+    pending++;
+    bool done = pending >= groups;
+    if (done) pending = 0;
+    if (complete) *complete = done;
+    return "";
+}
+
+// -------------------------------------------------------------------------------------
 // OneCycle (autograd/nn.go:539-571)
 // -------------------------------------------------------------------------------------
 OneCycle OneCycle::New(double maxLR, int total, double pctStart) {

@@ -172,8 +172,11 @@ void SGD::run(float maxNorm) {
     std::string e = validateOpen();
     if (!e.empty()) throw std::runtime_error(e);
     if (StepCount >= INT32_MAX) throw std::runtime_error("autograd: SGD step count overflow");
+    if (!std::isfinite(Engine.GradScale) || !(Engine.GradScale > 0)) throw std::runtime_error("autograd: invalid gradient scale");
     StepCount++;
     if (!(e = refreshPlan()).empty()) throw std::runtime_error(e);
+    int rc = oe_plan_set_grad_scale(plan_, &Engine.GradScale);
+    if (rc != 0) throw std::runtime_error(engine_error("oe_plan_set_grad_scale", rc));
     oe_sgd_hparams hp;
     memset(&hp, 0, sizeof hp);
     hp.lr = LR;
@@ -182,7 +185,6 @@ void SGD::run(float maxNorm) {
     hp.max_norm = maxNorm;
     hp.flags = (options_.Nesterov ? OE_NESTEROV : 0u) | (options_.Maximize ? OE_MAXIMIZE : 0u) |
                (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u);
-    int rc = 0;
     if (maxNorm > 0 && (rc = oe_grad_norm(plan_, 0, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_grad_norm", rc));
     if ((rc = oe_sgd_step(plan_, &hp, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_sgd_step", rc));
     for (Parameter& p : Params) {

@@ -1,5 +1,6 @@
 // Flat C handle API (include/gograd_host.h) over the C++ host mirror. Exceptions — the
 // mirror's counterpart of a Go panic — are turned into error codes here.
+#include <cmath>
 #include <cstring>
 #include <functional>
 
@@ -258,6 +259,13 @@ int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devfor
     return 0;
 }
 
+int gg_opt_set_grad_scale(gg_optimizer* o, const float* scale) {
+    if (!o || !scale) return fail("optimizer or scale is NULL");
+    if (!std::isfinite(*scale) || !(*scale > 0)) return fail("autograd: invalid gradient scale");
+    (o->adamw ? o->adamw->Engine : o->sgd->Engine).GradScale = *scale;
+    return 0;
+}
+
 int gg_opt_step(gg_optimizer* o) {
     return guarded([&]() -> std::string {
         o->base()->Step();
@@ -430,6 +438,33 @@ static void from_cycle(const OneCycle& o, gg_onecycle* c) {
     c->final_div_factor = o.FinalDivFactor;
     c->total = o.Total;
     c->step_count = o.StepCount;
+}
+
+int gg_accumulator_new(int32_t groups, gg_accumulator* out) {
+    if (!out) return fail("accumulator is NULL");
+    GradAccumulator a;
+    std::string e = GradAccumulator::New(groups, &a);
+    if (!e.empty()) return fail(e);
+    out->groups = a.groups;
+    out->pending = a.pending;
+    return 0;
+}
+
+int gg_accumulator_micro_batch(gg_accumulator* a, float* seed_out, int32_t* complete_out) {
+    if (!a) return fail("autograd: invalid gradient accumulator");
+    GradAccumulator acc;
+    acc.groups = a->groups;
+    acc.pending = a->pending;
+    bool complete = false;
+    std::string e = acc.MicroBatch(seed_out, &complete);
+    if (!e.empty()) return fail(e);
+    a->pending = acc.pending;
+    if (complete_out) *complete_out = complete ? 1 : 0;
+    return 0;
+}
+
+void gg_accumulator_reset(gg_accumulator* a) {
+    if (a) a->pending = 0;
 }
 
 int gg_onecycle_new(const double* max_lr, int32_t total, const double* pct_start, gg_onecycle* out) {

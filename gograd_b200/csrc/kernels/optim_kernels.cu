@@ -78,14 +78,16 @@ __device__ __forceinline__ oe_chunk_view oe_view(const oe_dev_tensor* tensors, c
 // AdamW
 // ---------------------------------------------------------------------------------
 struct oe_adamw_consts {
-    float b1, b2, omb1, omb2, eps, bc1, bc2, coef;
+    float b1, b2, omb1, omb2, eps, bc1, bc2, coef, gscale;
 };
 
 // One element of AdamW.Step's host loop (autograd/nn.go:522-527), g already the
-// stored gradient: g*coef rounds exactly like the in-place clip followed by a reload.
+// stored gradient: g*coef rounds exactly like the in-place clip followed by a reload. The
+// plan's gradient scale comes first, rounded on its own: the update sees what it would have
+// seen had the gradient been stored as (float)(g*scale). A scale of 1 changes no bit.
 __device__ __forceinline__ void oe_adamw_one(float& p, float g, float& m, float& v, const oe_adamw_consts& k,
                                              float step, float one_minus_decay) {
-    g = __fmul_rn(g, k.coef);
+    g = __fmul_rn(__fmul_rn(g, k.gscale), k.coef);
     float mi = __fadd_rn(__fmul_rn(k.b1, m), __fmul_rn(k.omb1, g));
     float vi = __fadd_rn(__fmul_rn(k.b2, v), __fmul_rn(__fmul_rn(k.omb2, g), g));
     m = mi;
@@ -140,6 +142,7 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
         k.bc2 = (float)(1.0 - pow((double)a.beta2, t));
     }
     k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
+    k.gscale = a.grad_scale;
     const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
     const bool zero_grad = (a.flags & OE_F_ZERO_GRAD) != 0;
     // A captured step bakes its launch parameters into the graph; a device-resident rate
@@ -249,14 +252,14 @@ extern "C" __global__ void oe_step_increment(int32_t* step) {
 // SGD (PyTorch semantics: coupled decay, momentum, dampening, Nesterov, maximize)
 // ---------------------------------------------------------------------------------
 struct oe_sgd_consts {
-    float momentum, one_minus_damp, coef;
+    float momentum, one_minus_damp, coef, gscale;
     bool nesterov, maximize;
 };
 
 // One element of SGD.Step's host loop (autograd/sgd.go:205-220).
 __device__ __forceinline__ void oe_sgd_one(float& p, float g, float& b, const oe_sgd_consts& k, float lr, float decay,
                                            bool first) {
-    g = __fmul_rn(g, k.coef);
+    g = __fmul_rn(__fmul_rn(g, k.gscale), k.coef);
     if (k.maximize) g = -g;
     g = __fadd_rn(g, __fmul_rn(decay, p));
     if (k.momentum > 0.0f) {
@@ -274,6 +277,7 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
     k.momentum = a.momentum;
     k.one_minus_damp = __fsub_rn(1.0f, a.dampening);
     k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
+    k.gscale = a.grad_scale;
     k.nesterov = (a.flags & OE_F_NESTEROV) != 0;
     k.maximize = (a.flags & OE_F_MAXIMIZE) != 0;
     const bool want_shadow = (a.flags & OE_F_WRITE_SHADOW) != 0;
@@ -377,7 +381,7 @@ __device__ __forceinline__ double oe_block_sum(double x, double* warp_sums) {
 // ticket, so the launch needs no memset and can be captured in a graph.
 extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
 oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
-              uint32_t chunk_elems, oe_dev_norm* out, double* partials, uint32_t flags) {
+              uint32_t chunk_elems, oe_dev_norm* out, double* partials, uint32_t flags, float gscale) {
     __shared__ double warp_sums[OE_THREADS / 32];
     __shared__ uint32_t is_last;
     double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
@@ -401,7 +405,9 @@ oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
                 }
 #pragma unroll
                 for (int u = 0; u < OE_NORM_UNROLL; u++) {
-                    double x = (double)G[u].x, y = (double)G[u].y, z = (double)G[u].z, w = (double)G[u].w;
+                    // the norm of the gradient as the update will read it: (float)(g*scale), then double
+                    double x = (double)__fmul_rn(G[u].x, gscale), y = (double)__fmul_rn(G[u].y, gscale);
+                    double z = (double)__fmul_rn(G[u].z, gscale), w = (double)__fmul_rn(G[u].w, gscale);
                     a0 = fma(x, x, a0);
                     a1 = fma(y, y, a1);
                     a2 = fma(z, z, a2);
@@ -411,7 +417,7 @@ oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
             done = nvec << 2;
         }
         for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
-            double x = (double)g[i];
+            double x = (double)__fmul_rn(g[i], gscale);
             a0 = fma(x, x, a0);
         }
     }

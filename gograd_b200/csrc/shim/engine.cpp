@@ -131,6 +131,7 @@ struct oe_plan {
     DeviceCtx* dc = nullptr;
     uint32_t chunk_elems = kDefaultChunkElems;
     int variant = 0;
+    float grad_scale = 1.0f;            // every kernel of the plan reads a gradient element as (float)(g * grad_scale)
     std::vector<oe_tensor_desc> descs;  // every parameter, with or without a gradient
     uint32_t n_active = 0;              // parameters with a gradient = rows of the device tensor table
     uint64_t n_chunks = 0;
@@ -483,13 +484,21 @@ extern "C" int oe_plan_set_variant(oe_plan* plan, const char* variant) {
     return fail(OE_ERR_INVALID, std::string("unknown update-kernel variant: ") + variant);
 }
 
+extern "C" int oe_plan_set_grad_scale(oe_plan* plan, const float* scale) {
+    if (!plan || !scale) return fail(OE_ERR_INVALID, "plan or scale is NULL");
+    if (!isfinite(*scale) || !(*scale > 0.0f)) return fail(OE_ERR_INVALID, "gradient scale must be finite and positive");
+    plan->grad_scale = *scale;
+    return 0;
+}
+
 // -------------------------------------------------------------------------------------
 // norm and clip
 // -------------------------------------------------------------------------------------
 namespace {
 int launch_sumsq(const oe_driver* d, oe_plan* p, uint32_t flags, CUstream stream) {
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
-    void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &p->d_norm, &p->d_partials, &flags};
+    float gscale = p->grad_scale;
+    void* args[] = {&p->d_tensors, &p->d_chunks, &n_chunks, &chunk_elems, &p->d_norm, &p->d_partials, &flags, &gscale};
     uint32_t grid = grid_for(p, p->dc->occ_sumsq);
     uint32_t spans = (n_chunks + kNormSpan - 1) / kNormSpan;  // the kernel walks the table in spans of work units
     if (grid > spans) grid = spans ? spans : 1;
@@ -527,6 +536,10 @@ extern "C" int oe_clip_grad_norm(oe_plan* plan, const float* max_norm, uint32_t 
     if (!plan || !max_norm) return fail(OE_ERR_INVALID, "plan or max_norm is NULL");
     if (flags & ~OE_CLIP_DEVFORM) return fail(OE_ERR_INVALID, "oe_clip_grad_norm: unknown flag");
     if (isnan(*max_norm)) return fail(OE_ERR_INVALID, "max_norm is NaN");
+    // The in-place clip rewrites the stored gradients; with a pending scale the next kernel
+    // would apply the scale a second time. The folded clip of the update kernels is the way.
+    if (plan->grad_scale != 1.0f && *max_norm > 0.0f)
+        return fail(OE_ERR_INVALID, "oe_clip_grad_norm: in-place clip with a gradient scale other than 1; use the clip folded into the step");
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
@@ -597,6 +610,7 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     a.norm = hp->max_norm > 0.0f ? (uint64_t)p->d_norm : 0;
     a.step_dev = hp->step_dev;
     a.lr_dev = hp->lr_dev;
+    a.grad_scale = p->grad_scale;
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
     CUdeviceptr chunk_table = p->d_chunks;
     if (range_chunks != UINT64_MAX) {  // a contiguous range of the chunk table
@@ -677,6 +691,7 @@ extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t str
     a.flags = hp->flags;
     a.norm = hp->max_norm > 0.0f ? (uint64_t)plan->d_norm : 0;
     a.lr_dev = hp->lr_dev;
+    a.grad_scale = plan->grad_scale;
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
     rc = launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
@@ -892,6 +907,10 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_peer_reduce_grads: 1 to 8 ranks are supported");
     if (flags & ~(OE_PARTIAL_ONLY | OE_ACCUMULATE)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
     if (!isfinite(*scale)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: scale is not finite");
+    // This kernel writes the scaled sum in place and takes its own factor; a plan-level scale
+    // would be applied again by the update that follows.
+    if (plan->grad_scale != 1.0f)
+        return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: the plan has a gradient scale other than 1; fold it into this call's scale");
     if (numel > 0 && (out == 0 || (out & 3u))) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad output address");
     oe_peer_grads pg;
     memset(&pg, 0, sizeof(pg));

@@ -48,13 +48,15 @@ typedef struct oe_adamw_args {
     uint64_t norm;    /* const oe_dev_norm* or 0                                 */
     uint64_t step_dev;/* const int32_t* device step counter (capture mode) or 0  */
     uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
+    float grad_scale; /* every gradient element is read as (float)(g * grad_scale) */
+    uint32_t pad;
 } oe_adamw_args;
 
 typedef struct oe_sgd_args {
     float lr, momentum, dampening;
     float max_norm;
     uint32_t flags;   /* OE_F_NESTEROV | OE_F_MAXIMIZE | clip/shadow bits        */
-    uint32_t pad;
+    float grad_scale; /* every gradient element is read as (float)(g * grad_scale) */
     uint64_t norm;
     uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
 } oe_sgd_args;

@@ -128,6 +128,10 @@ class Plan:
     def set_variant(self, name: str) -> None:
         check(lib().oe_plan_set_variant(self._h, name.encode()))
 
+    def set_grad_scale(self, scale: float) -> None:
+        """Norm and update kernels read every gradient element as float32(g * scale) from now on."""
+        check(lib().oe_plan_set_grad_scale(self._h, C.byref(C.c_float(scale))))
+
     def grad_norm(self, flags: int = 0, stream=None) -> None:
         check(lib().oe_grad_norm(self._h, flags, _stream(stream)))
 

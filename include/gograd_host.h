@@ -36,6 +36,10 @@ typedef struct gg_onecycle { /* OneCycle, autograd/nn.go:539-542 */
     int32_t total, step_count;
 } gg_onecycle;
 
+typedef struct gg_accumulator { /* GradAccumulator, autograd/accumulate.go:15-18 */
+    int32_t groups, pending;
+} gg_accumulator;
+
 /* Parameter groups as flat arrays: group g is named group_names[g], owns the parameters
  * members[offsets[g] .. offsets[g+1]) (indexes into the parameter list), scales the base rate
  * by lr_scales[g] (0 selects 1) and decays with decays[g] (ParameterGroupSpec,
@@ -83,6 +87,9 @@ OE_API int gg_sgd_new(const char* const* names, gg_tensor* const* tensors, int32
 OE_API int gg_sgd_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n,
                              const gg_sgd_options* options, const gg_groups* groups, gg_optimizer** out);
 OE_API int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devform);
+/* Step and step_clipped read every gradient element as (float)(g * *scale) from now on (default 1):
+ * the 1/groups factor of gradient accumulation folded into the pass that reads the gradients. */
+OE_API int gg_opt_set_grad_scale(gg_optimizer* o, const float* scale);
 OE_API int gg_opt_step(gg_optimizer* o);                                /* Step */
 OE_API int gg_opt_step_clipped(gg_optimizer* o, const float* max_norm); /* norm + Step with the clip folded in */
 OE_API int gg_opt_last_norm(gg_optimizer* o, float* out);
@@ -112,6 +119,14 @@ OE_API int gg_partition_parameters(const char* const* names, gg_tensor* const* t
 OE_API int gg_clip_grad_norm(gg_tensor* const* tensors, int32_t n, const float* max_norm);
 OE_API int gg_gradient_norm_to_host(float* out);
 OE_API void gg_release_clip_state(void);
+
+/* ---- gradient accumulation bookkeeping (autograd/accumulate.go:21-71) ----
+ * gg_accumulator_micro_batch is what GradAccumulator.Backward does around the differentiation
+ * itself: it writes the seed 1/groups, counts the micro-batch and reports (1/0) whether the group
+ * is complete. Pending and Groups are the struct's fields; reset is Reset. */
+OE_API int gg_accumulator_new(int32_t groups, gg_accumulator* out);
+OE_API int gg_accumulator_micro_batch(gg_accumulator* a, float* seed_out, int32_t* complete_out);
+OE_API void gg_accumulator_reset(gg_accumulator* a);
 
 /* ---- schedule and training checkpoint (autograd/nn.go:539-571, autograd/training_checkpoint.go) ---- */
 OE_API int gg_onecycle_new(const double* max_lr, int32_t total, const double* pct_start, gg_onecycle* out);

@@ -167,6 +167,18 @@ OE_API uint64_t oe_plan_norm_address(const oe_plan* plan);
  * "u1", "u2", "u8"); a tuning knob, results are identical. */
 OE_API int oe_plan_set_variant(oe_plan* plan, const char* variant);
 
+/* Gradient scale of the plan (default 1): from now on oe_grad_norm, oe_adamw_step*, oe_sgd_step and
+ * oe_adamw_step_from_host read every gradient element as (float)(g * *scale) — one fp32 rounding,
+ * before the clip coefficient — so norm and update are those of the reference optimizer fed with
+ * gradients stored at that scale. It folds the 1/groups factor of gradient accumulation
+ * (GradAccumulator.Backward seeds differentiation with it, autograd/accumulate.go:31-44; for a power
+ * of two the results are identical to seeding) or an unscale factor into the pass that reads the
+ * gradients anyway. A scale of 1 changes no bit. *scale must be finite and positive. While it is not
+ * 1, the in-place clip (oe_clip_grad_norm with max_norm > 0) and oe_peer_reduce_grads, which
+ * rewrite the stored gradients, are refused with OE_ERR_INVALID. The float travels by pointer like
+ * every float of this interface. */
+OE_API int oe_plan_set_grad_scale(oe_plan* plan, const float* scale);
+
 /* ---- gradient norm and clip --------------------------------------------------------------------- */
 
 /* Global L2 norm over every present gradient of the plan: per-CTA float64 partial

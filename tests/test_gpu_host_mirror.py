@@ -455,3 +455,50 @@ def test_shadow_lease_survives_an_optimizer_step(ag):
     in_place = w.address(2)
     opt.Step()                                   # nobody reads the shadow: rewritten in place
     assert w.address(2) == in_place and w.shadow_current
+
+
+def test_accumulated_gradients_read_at_the_seed_scale(ag):
+    """Four micro-batches (autograd/accumulate_test.go:97-141 splits a batch the same way). One run
+    stores each micro-batch gradient at the accumulator's seed 1/4, as Backward would; the other
+    stores them raw and hands the seed to the optimizer as its gradient scale. A power-of-two factor
+    commutes with the fp32 additions, so both runs end on the same bits, AdamW and SGD alike; an
+    invalid scale is refused and leaves the step counter where it was."""
+    rng = np.random.default_rng(31)
+    sizes = (1000, 7, 4096, 5001)
+    values = [rng.normal(0, .05, n).astype(np.float32) for n in sizes]
+    micro = [[rng.normal(0, .5, n).astype(np.float32) for n in sizes] for _ in range(8)]
+    for kind in ("adamw", "sgd"):
+        runs = []
+        for folded in (False, True):
+            params = params_of(ag, [(f"p{i}", v) for i, v in enumerate(values)])
+            if kind == "adamw":
+                opt = ag.NewAdamW(params, 1e-2, 0.1)
+            else:
+                opt = ag.NewSGD(params, ag.SGDOptions(LR=0.05, Momentum=0.9, WeightDecay=0.01))
+            acc = ag.GradAccumulator(4)
+            if folded:
+                opt.SetGradScale(float(acc.MicroBatch()[0]))
+                acc.Reset()
+            sums = [np.zeros(n, np.float32) for n in sizes]
+            for k in range(8):
+                seed, complete = acc.MicroBatch()
+                for i in range(len(sizes)):
+                    g = micro[k][i] if folded else (micro[k][i] * seed).astype(np.float32)
+                    sums[i] = (sums[i] + g).astype(np.float32)
+                assert complete == (k % 4 == 3)
+                if complete:
+                    for p, g in zip(params, sums):
+                        p.Value.set_grad(g)
+                    opt.StepClipped(1.0)
+                    sums = [np.zeros(n, np.float32) for n in sizes]
+            assert opt.StepCount == 2
+            runs.append([p.Value.to_host() for p in params])
+            if folded:
+                for bad in (0.0, -2.0, float("nan")):
+                    with pytest.raises(ag.HostError, match="invalid gradient scale"):
+                        opt.SetGradScale(bad)
+                opt.StepClipped(1.0)
+                assert opt.StepCount == 3
+            opt.Close()
+        for a, b in zip(*runs):
+            assert np.array_equal(a, b), kind

@@ -81,3 +81,30 @@ def test_empty_and_scalar_entries_round_trip(tmp_path):
     raw = open(path, "rb").read()
     (hlen,) = struct.unpack("<Q", raw[:8])
     assert b"__metadata__" not in raw[8:8 + hlen]
+
+
+def test_grad_accumulator_bookkeeping():
+    """GradAccumulator's counters and validation (autograd/accumulate.go:21-71, mirrored from
+    autograd/accumulate_test.go:146-224): no device is involved."""
+    for groups in (0, -1):
+        with pytest.raises(ag.HostError, match="at least one micro-batch"):
+            ag.GradAccumulator(groups)
+    acc = ag.GradAccumulator(2)
+    assert acc.Groups() == 2 and acc.Pending() == 0
+    completes = []
+    for micro in range(3):
+        seed, complete = acc.MicroBatch()
+        assert seed == np.float32(0.5)
+        completes.append(complete)
+    assert completes == [False, True, False] and acc.Pending() == 1
+    acc.Reset()
+    assert acc.Pending() == 0
+    seed, complete = ag.GradAccumulator(3).MicroBatch()
+    assert seed == np.float32(1) / np.float32(3) and not complete
+    one = ag.GradAccumulator(1)
+    assert one.MicroBatch() == (np.float32(1.0), True) and one.Pending() == 0
+    broken = ag.GradAccumulator(2)
+    broken._a.groups = 0
+    with pytest.raises(ag.HostError, match="invalid gradient accumulator"):
+        broken.MicroBatch()
+    assert broken.Pending() == 0, "a failed call changes nothing"
