@@ -82,12 +82,10 @@ struct oe_adamw_consts {
 };
 
 // One element of AdamW.Step's host loop (autograd/nn.go:522-527), g already the
-// stored gradient: g*coef rounds exactly like the in-place clip followed by a reload. The
-// plan's gradient scale comes first, rounded on its own: the update sees what it would have
-// seen had the gradient been stored as (float)(g*scale). A scale of 1 changes no bit.
+// stored gradient: g*coef rounds exactly like the in-place clip followed by a reload.
 __device__ __forceinline__ void oe_adamw_one(float& p, float g, float& m, float& v, const oe_adamw_consts& k,
                                              float step, float one_minus_decay) {
-    g = __fmul_rn(__fmul_rn(g, k.gscale), k.coef);
+    g = __fmul_rn(g, k.coef);
     float mi = __fadd_rn(__fmul_rn(k.b1, m), __fmul_rn(k.omb1, g));
     float vi = __fadd_rn(__fmul_rn(k.b2, v), __fmul_rn(__fmul_rn(k.omb2, g), g));
     m = mi;
@@ -121,7 +119,21 @@ __device__ __forceinline__ void oe_store_shadow1(uint16_t* sh, uint32_t index, u
     }
 }
 
-template <int UNROLL, bool PEERS>
+// The plan's gradient scale: a gradient element is read as (float)(g*scale), rounded on its
+// own before anything else, so the update sees what it would have seen had the gradient
+// been stored at that scale. Bodies are built with and without the multiply; a scale of
+// exactly 1 (the default) runs the body without it.
+template <bool SCALED>
+__device__ __forceinline__ void oe_scale4(float4& g, float s) {
+    if (SCALED) {
+        g.x = __fmul_rn(g.x, s);
+        g.y = __fmul_rn(g.y, s);
+        g.z = __fmul_rn(g.z, s);
+        g.w = __fmul_rn(g.w, s);
+    }
+}
+
+template <int UNROLL, bool PEERS, bool SCALED>
 __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ tensors,
                                               const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
                                               uint32_t chunk_elems, const oe_adamw_args& a, const oe_peer_set& peers) {
@@ -183,6 +195,7 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
                 for (int u = 0; u < UNROLL; u++) {
                     uint32_t i = i0 + u * OE_THREADS;
                     if (i < nvec) {
+                        oe_scale4<SCALED>(G[u], k.gscale);
                         oe_adamw_one(P[u].x, G[u].x, M[u].x, V[u].x, k, step, omd);
                         oe_adamw_one(P[u].y, G[u].y, M[u].y, V[u].y, k, step, omd);
                         oe_adamw_one(P[u].z, G[u].z, M[u].z, V[u].z, k, step, omd);
@@ -206,7 +219,7 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
         // of a tensor whose pointers do not allow 128-bit accesses.
         for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
             float pi = p[i], mi = m[i], vi = v[i];
-            oe_adamw_one(pi, g[i], mi, vi, k, step, omd);
+            oe_adamw_one(pi, SCALED ? __fmul_rn(g[i], k.gscale) : g[i], mi, vi, k, step, omd);
             p[i] = pi;
             m[i] = mi;
             v[i] = vi;
@@ -226,7 +239,10 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
          uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a) {                                       \
         oe_peer_set none;                                                                                  \
         none.n = 0;                                                                                        \
-        oe_adamw_body<unroll, false>(tensors, chunks, n_chunks, chunk_elems, a, none);                     \
+        if (a.grad_scale == 1.0f)                                                                          \
+            oe_adamw_body<unroll, false, false>(tensors, chunks, n_chunks, chunk_elems, a, none);          \
+        else                                                                                               \
+            oe_adamw_body<unroll, false, true>(tensors, chunks, n_chunks, chunk_elems, a, none);           \
     }
 // Default: four 128-bit vectors per stream in flight per thread, two CTAs per SM (measured
 // fastest on B200: fewer, fatter threads keep more bytes in flight than more CTAs do).
@@ -239,7 +255,10 @@ OE_ADAMW_VARIANT(oe_adamw_fused_u8, 8, 1)
 extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
 oe_adamw_fused_peers(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks,
                      uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a, const __grid_constant__ oe_peer_set peers) {
-    oe_adamw_body<4, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
+    if (a.grad_scale == 1.0f)
+        oe_adamw_body<4, true, false>(tensors, chunks, n_chunks, chunk_elems, a, peers);
+    else
+        oe_adamw_body<4, true, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
 }
 
 // Capture mode: one thread advances the device step counter before the update
@@ -259,7 +278,7 @@ struct oe_sgd_consts {
 // One element of SGD.Step's host loop (autograd/sgd.go:205-220).
 __device__ __forceinline__ void oe_sgd_one(float& p, float g, float& b, const oe_sgd_consts& k, float lr, float decay,
                                            bool first) {
-    g = __fmul_rn(__fmul_rn(g, k.gscale), k.coef);
+    g = __fmul_rn(g, k.coef);
     if (k.maximize) g = -g;
     g = __fadd_rn(g, __fmul_rn(decay, p));
     if (k.momentum > 0.0f) {
@@ -270,9 +289,10 @@ __device__ __forceinline__ void oe_sgd_one(float& p, float g, float& b, const oe
     p = __fsub_rn(p, __fmul_rn(lr, g));
 }
 
-extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
-oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
-             uint32_t chunk_elems, oe_sgd_args a) {
+template <bool SCALED>
+__device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ tensors,
+                                            const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+                                            uint32_t chunk_elems, const oe_sgd_args& a) {
     oe_sgd_consts k;
     k.momentum = a.momentum;
     k.one_minus_damp = __fsub_rn(1.0f, a.dampening);
@@ -319,6 +339,7 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
                 for (int u = 0; u < OE_UNROLL; u++) {
                     uint32_t i = i0 + u * OE_THREADS;
                     if (i < nvec) {
+                        oe_scale4<SCALED>(G[u], k.gscale);
                         oe_sgd_one(P[u].x, G[u].x, B[u].x, k, lr, decay, first);
                         oe_sgd_one(P[u].y, G[u].y, B[u].y, k, lr, decay, first);
                         oe_sgd_one(P[u].z, G[u].z, B[u].z, k, lr, decay, first);
@@ -340,13 +361,22 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
         for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
             float pi = p[i];
             float bi = (has_buf && !first) ? b[i] : 0.0f;
-            oe_sgd_one(pi, g[i], bi, k, lr, decay, first);
+            oe_sgd_one(pi, SCALED ? __fmul_rn(g[i], k.gscale) : g[i], bi, k, lr, decay, first);
             p[i] = pi;
             if (has_buf) b[i] = bi;
             if (sh) sh[i] = (uint16_t)oe_bf16_rne(pi);
             if (zero_grad) g[i] = 0.0f;
         }
     }
+}
+
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
+oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+             uint32_t chunk_elems, oe_sgd_args a) {
+    if (a.grad_scale == 1.0f)
+        oe_sgd_body<false>(tensors, chunks, n_chunks, chunk_elems, a);
+    else
+        oe_sgd_body<true>(tensors, chunks, n_chunks, chunk_elems, a);
 }
 
 // After an SGD update: every tensor that took part now has an initialised momentum
@@ -374,19 +404,15 @@ __device__ __forceinline__ double oe_block_sum(double x, double* warp_sums) {
     return total;  // valid in thread 0
 }
 
-// Level 1: every CTA accumulates its chunks in double (the reference's host code sums in
-// float64 too, autograd/nn.go:319-324) and writes one partial. Level 2: the CTA that
-// arrives last adds the partials in index order, so the result depends only on the
-// grid size, never on timing; it stores sum, norm = (float)sqrt(sum) and re-arms the
-// ticket, so the launch needs no memset and can be captured in a graph.
-extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
-oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
-              uint32_t chunk_elems, oe_dev_norm* out, double* partials, uint32_t flags, float gscale) {
-    __shared__ double warp_sums[OE_THREADS / 32];
-    __shared__ uint32_t is_last;
+// One CTA's share of the sum: OE_NORM_SPAN consecutive work units at a time (for a read-only
+// 4 B/param stream a longer contiguous run per CTA measured ~6 % faster than single
+// 4096-element units). SCALED: the norm of the gradient as the update will read it,
+// (float)(g*scale) converted to double.
+template <bool SCALED>
+__device__ __forceinline__ double oe_sumsq_walk(const oe_dev_tensor* __restrict__ tensors,
+                                                const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+                                                uint32_t chunk_elems, float gscale) {
     double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
-    // A CTA takes OE_NORM_SPAN consecutive work units at a time: for a read-only 4 B/param stream a
-    // longer contiguous run per CTA measured ~6 % faster than single 4096-element units.
     const uint32_t n_spans = (n_chunks + OE_NORM_SPAN - 1) / OE_NORM_SPAN;
     for (uint32_t sp = blockIdx.x; sp < n_spans; sp += gridDim.x)
     for (uint32_t c = sp * OE_NORM_SPAN; c < n_chunks && c < (sp + 1) * OE_NORM_SPAN; c++) {
@@ -405,9 +431,8 @@ oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
                 }
 #pragma unroll
                 for (int u = 0; u < OE_NORM_UNROLL; u++) {
-                    // the norm of the gradient as the update will read it: (float)(g*scale), then double
-                    double x = (double)__fmul_rn(G[u].x, gscale), y = (double)__fmul_rn(G[u].y, gscale);
-                    double z = (double)__fmul_rn(G[u].z, gscale), w = (double)__fmul_rn(G[u].w, gscale);
+                    oe_scale4<SCALED>(G[u], gscale);
+                    double x = (double)G[u].x, y = (double)G[u].y, z = (double)G[u].z, w = (double)G[u].w;
                     a0 = fma(x, x, a0);
                     a1 = fma(y, y, a1);
                     a2 = fma(z, z, a2);
@@ -417,11 +442,26 @@ oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
             done = nvec << 2;
         }
         for (uint32_t i = done + threadIdx.x; i < cv.n; i += OE_THREADS) {
-            double x = (double)__fmul_rn(g[i], gscale);
+            double x = (double)(SCALED ? __fmul_rn(g[i], gscale) : g[i]);
             a0 = fma(x, x, a0);
         }
     }
-    double block = oe_block_sum((a0 + a1) + (a2 + a3), warp_sums);
+    return (a0 + a1) + (a2 + a3);
+}
+
+// Level 1: every CTA accumulates its chunks in double (the reference's host code sums in
+// float64 too, autograd/nn.go:319-324) and writes one partial. Level 2: the CTA that
+// arrives last adds the partials in index order, so the result depends only on the
+// grid size, never on timing; it stores sum, norm = (float)sqrt(sum) and re-arms the
+// ticket, so the launch needs no memset and can be captured in a graph.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
+oe_grad_sumsq(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+              uint32_t chunk_elems, oe_dev_norm* out, double* partials, uint32_t flags, float gscale) {
+    __shared__ double warp_sums[OE_THREADS / 32];
+    __shared__ uint32_t is_last;
+    const double mine = gscale == 1.0f ? oe_sumsq_walk<false>(tensors, chunks, n_chunks, chunk_elems, gscale)
+                                       : oe_sumsq_walk<true>(tensors, chunks, n_chunks, chunk_elems, gscale);
+    double block = oe_block_sum(mine, warp_sums);
     if (threadIdx.x == 0) {
         partials[blockIdx.x] = block;
         __threadfence();
