@@ -255,8 +255,7 @@ def run_single(args):
     if args.graph:
         step_dev = torch.full((1,), step_no[0], dtype=torch.int32, device="cuda:0")
         lr_dev = torch.full((1,), hp["lr"], dtype=torch.float32, device="cuda:0")
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g):
+        def captured_step():
             if ps.max_norm > 0:
                 plan.grad_norm(0)
             if is_sgd:
@@ -265,18 +264,34 @@ def run_single(args):
             else:
                 plan.adamw_step(eng.AdamWHParams(hp["lr"], hp["beta1"], hp["beta2"], hp["eps"], max_norm=ps.max_norm,
                                                  flags=flags, step_dev=step_dev.data_ptr(), lr_dev=lr_dev.data_ptr()))
-        for _ in range(args.warmup):
-            g.replay()
-        torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(args.steps):
-            g.replay()
-        b.record()
-        torch.cuda.synchronize()
-        graph_info = {"ms_per_step": a.elapsed_time(b) / args.steps,
-                      "value": n_params / (a.elapsed_time(b) / args.steps * 1e-3) / 1e9,
+
+        def replay_ms(steps_per_graph):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(steps_per_graph):
+                    captured_step()
+            replays = max(1, args.steps // steps_per_graph)
+            for _ in range(args.warmup):
+                g.replay()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(replays):
+                g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) / (replays * steps_per_graph)
+
+        one = replay_ms(1)
+        graph_info = {"ms_per_step": one, "value": n_params / (one * 1e-3) / 1e9,
                       "note": "one captured step (device step counter and learning rate) replayed"}
+        if args.graph_steps > 1:
+            # several steps per graph: the host's cost of launching a graph is shared, what is
+            # left is the device-side time of a step
+            many = replay_ms(args.graph_steps)
+            graph_info["steps_per_graph"] = args.graph_steps
+            graph_info["ms_per_step_many"] = many
+            graph_info["value_many"] = n_params / (many * 1e-3) / 1e9
 
     # ---- end to end through the host-buffer entry point -------------------------------
     e2e = None
@@ -426,6 +441,8 @@ def main():
                     help="N > 1: fused peer-memory kernels, or NCCL reduce-scatter / all-gather around the kernels")
     ap.add_argument("--secondary", action="store_true", help="time the other kernels of the path instead of the step")
     ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")
+    ap.add_argument("--graph-steps", type=int, default=1,
+                    help="with --graph: also capture this many steps in one graph (shares the host's graph-launch cost)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-params", type=int, default=120_000_000)

@@ -145,11 +145,15 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
     k.eps = a.eps;
     k.bc1 = a.bc1;
     k.bc2 = a.bc2;
+    int32_t step_now = 0;
     if (a.step_dev != 0) {
-        // Capture mode: the step counter lives on the device and was advanced by
-        // oe_step_increment; bias correction as on the host, in double
-        // (autograd/nn.go:493-494).
-        double t = (double)(*(const int32_t*)a.step_dev);
+        // Capture mode: the step counter lives on the device. This launch is step
+        // counter+1 (the reference advances it with a launch of its own first,
+        // graph_adam_inc, autograd/cuda_kernels.go:595; here the CTA that finishes last
+        // stores the new value, see the end of this function). Bias correction as on
+        // the host, in double (autograd/nn.go:493-494).
+        step_now = *(const int32_t*)a.step_dev + 1;
+        double t = (double)step_now;
         k.bc1 = (float)(1.0 - pow((double)a.beta1, t));
         k.bc2 = (float)(1.0 - pow((double)a.beta2, t));
     }
@@ -229,6 +233,19 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
     }
     // Peer stores must be performed before the kernel is reported complete to other devices.
     if (PEERS) __threadfence_system();
+    if (a.step_dev != 0) {
+        // Every CTA read the counter before it got here, so the one that arrives last may
+        // store the new value; it also re-arms the arrival counter for the next replay.
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            uint32_t* ticket = (uint32_t*)a.ticket;
+            __threadfence();
+            if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+                *ticket = 0u;
+                *(int32_t*)a.step_dev = step_now;
+            }
+        }
+    }
 }
 
 // The update kernel is built in a few shapes (vectors in flight per thread x resident
@@ -261,8 +278,8 @@ oe_adamw_fused_peers(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chu
         oe_adamw_body<4, true, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
 }
 
-// Capture mode: one thread advances the device step counter before the update
-// (the reference's graph_adam_inc, autograd/cuda_kernels.go:595).
+// Advances a device step counter on its own: used when a captured step has no work unit
+// at all (no parameter has a gradient), so no update launch could do it.
 extern "C" __global__ void oe_step_increment(int32_t* step) {
     if (blockIdx.x == 0 && threadIdx.x == 0) step[0] += 1;
 }
@@ -373,6 +390,9 @@ __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ te
 extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
 oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
              uint32_t chunk_elems, oe_sgd_args a) {
+    // Capture mode: the launch advances the device step counter (the reference's sgd_step,
+    // autograd/cuda_sgd.go:18); nothing in the update reads it.
+    if (a.step_dev != 0 && blockIdx.x == 0 && threadIdx.x == 0) *(int32_t*)a.step_dev += 1;
     if (a.grad_scale == 1.0f)
         oe_sgd_body<false>(tensors, chunks, n_chunks, chunk_elems, a);
     else

@@ -32,7 +32,8 @@ typedef struct oe_dev_norm {
     float norm;       /* (float)sqrt(sumsq)                                      */
     uint32_t ticket;  /* arrival counter of the reduction; 0 between launches    */
     uint32_t error;   /* sticky device-side error word (0 = none)                */
-    uint32_t pad[3];
+    uint32_t step_ticket; /* arrival counter of a captured update; 0 between launches */
+    uint32_t pad[2];
 } oe_dev_norm;
 
 #define OE_ALIGNED_BASE   0x1u /* param, grad, state1 16-byte and shadow 8-byte aligned */
@@ -50,6 +51,7 @@ typedef struct oe_adamw_args {
     uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
     float grad_scale; /* every gradient element is read as (float)(g * grad_scale) */
     uint32_t pad;
+    uint64_t ticket;  /* uint32_t* arrival counter used to advance *step_dev (capture mode) */
 } oe_adamw_args;
 
 typedef struct oe_sgd_args {
@@ -59,6 +61,7 @@ typedef struct oe_sgd_args {
     float grad_scale; /* every gradient element is read as (float)(g * grad_scale) */
     uint64_t norm;
     uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
+    uint64_t step_dev;/* int32_t* device step counter advanced by the launch, or 0 */
 } oe_sgd_args;
 
 /* Ranks of a sharded step: byte distance from this rank's buffer to rank k's buffer of the

@@ -141,7 +141,9 @@ OE_API int oe_device_sm_count(int device);
  * (autograd/nn.go:495-505, autograd/cuda_sgd.go:71-97) and of its clip pointer table
  * (getClipPlan, autograd/cuda_clip.go:66-113, one write_clip_entry launch per tensor).
  * Parameters with grad == 0 stay in the plan but are left out of the tables.
- * chunk_elems = 0 selects the default work-unit size. Validates every descriptor
+ * chunk_elems = 0 selects the default work-unit size (4096 elements; 2048 or 1024 for a
+ * parameter list too small to give every SM two units); otherwise a multiple of 1024. The size
+ * is fixed for the life of the plan and never changes results. Validates every descriptor
  * before allocating anything. */
 OE_API int oe_plan_create(int device, const oe_tensor_desc* tensors, uint32_t n_tensors, uint32_t chunk_elems,
                    oe_plan** out);

@@ -604,3 +604,51 @@ def test_capture_mode_device_step_counter(eng, orc):
     rel_close("captured m", host(m), ref.m[0], 1e-6)
     rel_close("captured v", host(v), ref.v[0], 1e-6)
     plan.close()
+
+
+def test_device_step_counter_is_advanced_by_the_update_launch_itself(eng, orc):
+    """Capture mode costs no launch of its own: the update launch reads the counter, runs step
+    counter+1 and its last CTA stores the new value (any grid size, the sharded shape and SGD
+    included). Only a plan without a single gradient needs the stand-alone increment."""
+    rng = np.random.default_rng(10)
+    sizes = [5000, 300_000, 7]          # 1 unit, many units, a ragged tail: several grid sizes
+    for chunk in (0, 1024, 8192):
+        hp0 = [rng.normal(0, .02, n).astype(np.float32) for n in sizes]
+        ref = orc.OracleAdamW([x.copy() for x in hp0], lr=1e-3, weight_decay=0.01)
+        p = [dev(x) for x in hp0]
+        g = [torch.zeros_like(x) for x in p]
+        m = [torch.zeros_like(x) for x in p]
+        v = [torch.zeros_like(x) for x in p]
+        step = torch.zeros(1, dtype=torch.int32, device="cuda")
+        plan = eng.Plan([eng.TensorDesc(p[i], g[i], m[i], v[i], None, 1.0, 0.01) for i in range(3)], 0, chunk)
+        eng.launch_count_reset()
+        for t in range(1, 6):
+            grads = [rng.normal(0, .01, n).astype(np.float32) for n in sizes]
+            for gi, x in zip(g, grads):
+                gi.copy_(torch.from_numpy(x))
+            if t == 4:   # the sharded shape of the kernel, with this GPU as its only rank
+                plan.adamw_step_peers(eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, step_dev=step.data_ptr()), [0])
+            else:
+                plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, step_dev=step.data_ptr()))
+            ref.step(grads)
+            assert int(step.item()) == t
+        assert eng.launch_count("oe_step_increment") == 0 and eng.launch_count() == 5
+        for i in range(3):
+            assert np.array_equal(host(p[i]), ref.params[i]) and np.array_equal(host(v[i]), ref.v[i]), f"chunk {chunk} [{i}]"
+        # no gradient anywhere: the step still counts
+        plan.update([eng.TensorDesc(p[i], None, m[i], v[i], None, 1.0, 0.01) for i in range(3)])
+        plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, step_dev=step.data_ptr()))
+        assert int(step.item()) == 6 and eng.launch_count("oe_step_increment") == 1
+        plan.close()
+    # SGD: the update launch advances the counter, one launch more only for the momentum flags
+    x = dev(np.ones(5000, np.float32))
+    gx = torch.full_like(x, 0.5)
+    step = torch.zeros(1, dtype=torch.int32, device="cuda")
+    plan = eng.Plan([eng.TensorDesc(x, gx, None, None, None, 1.0, 0.0)])
+    eng.launch_count_reset()
+    for t in range(1, 4):
+        plan.sgd_step(eng.SGDHParams(0.1, step_dev=step.data_ptr()))
+        assert int(step.item()) == t
+    assert eng.launch_count() == 3 and eng.launch_count("oe_sgd_fused") == 3
+    assert float(x[0]) == np.float32(1.0) - np.float32(0.05) - np.float32(0.05) - np.float32(0.05)
+    plan.close()
