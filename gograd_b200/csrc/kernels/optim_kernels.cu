@@ -154,8 +154,14 @@ __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ 
         // the host, in double (autograd/nn.go:493-494).
         step_now = *(const int32_t*)a.step_dev + 1;
         double t = (double)step_now;
-        k.bc1 = (float)(1.0 - pow((double)a.beta1, t));
-        k.bc2 = (float)(1.0 - pow((double)a.beta2, t));
+        // The two double-precision pow calls are the longest dependent chain of a small launch:
+        // two warps take one each.
+        __shared__ float bc_shared[2];
+        if (threadIdx.x == 0) bc_shared[0] = (float)(1.0 - pow((double)a.beta1, t));
+        if (threadIdx.x == 32) bc_shared[1] = (float)(1.0 - pow((double)a.beta2, t));
+        __syncthreads();
+        k.bc1 = bc_shared[0];
+        k.bc2 = bc_shared[1];
     }
     k.coef = oe_clip_coefficient((const oe_dev_norm*)a.norm, a.max_norm, a.flags);
     k.gscale = a.grad_scale;
@@ -329,7 +335,7 @@ __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ te
         const bool has_buf = k.momentum > 0.0f && t->state1 != 0;
         float* __restrict__ b = has_buf ? (float*)t->state1 + cv.base : nullptr;
         // The per-tensor device flag says whether the momentum buffer holds a value
-        // yet (autograd/cuda_sgd.go:14); oe_sgd_mark sets it after this launch.
+        // yet (autograd/cuda_sgd.go:14); the last CTA of this launch sets it.
         const bool first = has_buf && t->state2 != 0 ? (*(const float*)t->state2 == 0.0f) : true;
         uint16_t* __restrict__ sh = (want_shadow && t->shadow) ? (uint16_t*)t->shadow + cv.base : nullptr;
         // SGD.groupScale (autograd/sgd.go:127-130): the decay is not scaled by the rate.
@@ -385,6 +391,25 @@ __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ te
             if (zero_grad) g[i] = 0.0f;
         }
     }
+    if (k.momentum > 0.0f) {
+        // Every tensor that took part now has an initialised momentum buffer (the reference's
+        // sgd_mark, one launch per tensor, autograd/cuda_sgd.go:14-16). Every CTA read the flags
+        // of its work units before it got here, so the CTA that arrives last may set them all;
+        // it also re-arms the arrival counter.
+        __shared__ uint32_t is_last;
+        uint32_t* ticket = (uint32_t*)a.ticket;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            is_last = (atomicAdd(ticket, 1u) == gridDim.x - 1) ? 1u : 0u;
+        }
+        __syncthreads();
+        if (is_last) {
+            for (uint32_t i = threadIdx.x; i < a.n_tensors; i += OE_THREADS)
+                if (tensors[i].state1 != 0 && tensors[i].state2 != 0) *(float*)tensors[i].state2 = 1.0f;
+            if (threadIdx.x == 0) *ticket = 0u;
+        }
+    }
 }
 
 extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
@@ -397,13 +422,6 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
         oe_sgd_body<false>(tensors, chunks, n_chunks, chunk_elems, a);
     else
         oe_sgd_body<true>(tensors, chunks, n_chunks, chunk_elems, a);
-}
-
-// After an SGD update: every tensor that took part now has an initialised momentum
-// buffer (the reference's sgd_mark, one launch per tensor; here one launch for all).
-extern "C" __global__ void oe_sgd_mark(const oe_dev_tensor* __restrict__ tensors, uint32_t n_tensors) {
-    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n_tensors && tensors[i].state1 != 0 && tensors[i].state2 != 0) *(float*)tensors[i].state2 = 1.0f;
 }
 
 // ---------------------------------------------------------------------------------

@@ -52,7 +52,7 @@ int fail_cu(const oe_driver* d, CUresult r, const char* op) {
 struct KernelSet {
     CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
     CUfunction adamw_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
-    CUfunction step_increment = nullptr, sgd = nullptr, sgd_mark = nullptr, sumsq = nullptr, norm_finalize = nullptr,
+    CUfunction step_increment = nullptr, sgd = nullptr, sumsq = nullptr, norm_finalize = nullptr,
                scale = nullptr, zero = nullptr, cast = nullptr;
 };
 const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2", "oe_adamw_fused_u8"};
@@ -358,7 +358,7 @@ extern "C" int oe_init(int device) {
         {&dc->k.peer_reduce[1], "oe_peer_reduce_sumsq_n4", &dc->occ_peer_reduce[1]},
         {&dc->k.peer_reduce[2], "oe_peer_reduce_sumsq_n8", &dc->occ_peer_reduce[2]},
         {&dc->k.step_increment, "oe_step_increment", nullptr}, {&dc->k.sgd, "oe_sgd_fused", &dc->occ_sgd},
-        {&dc->k.sgd_mark, "oe_sgd_mark", nullptr},             {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
+        {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
         {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
         {&dc->k.zero, "oe_zero_grads", &dc->occ_zero},         {&dc->k.cast, "oe_cast_bf16", &dc->occ_cast},
     };
@@ -713,14 +713,11 @@ extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t str
     a.lr_dev = hp->lr_dev;
     a.grad_scale = plan->grad_scale;
     a.step_dev = hp->step_dev;
+    a.ticket = (uint64_t)plan->d_norm + offsetof(oe_dev_norm, step_ticket);
+    a.n_tensors = plan->n_active;
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
-    rc = launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
-    if (rc || !(hp->momentum > 0.0f)) return rc;
-    uint32_t n = plan->n_active;
-    void* mark_args[] = {&plan->d_tensors, &n};
-    return launch(d, plan->dc->k.sgd_mark, "oe_sgd_mark", (n + kThreads - 1) / kThreads, kThreads, (CUstream)stream,
-                  mark_args);
+    return launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
 }
 
 extern "C" int oe_zero_grads(oe_plan* plan, uint64_t stream) {

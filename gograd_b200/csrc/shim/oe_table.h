@@ -32,7 +32,7 @@ typedef struct oe_dev_norm {
     float norm;       /* (float)sqrt(sumsq)                                      */
     uint32_t ticket;  /* arrival counter of the reduction; 0 between launches    */
     uint32_t error;   /* sticky device-side error word (0 = none)                */
-    uint32_t step_ticket; /* arrival counter of a captured update; 0 between launches */
+    uint32_t step_ticket; /* arrival counter of an update launch; 0 between launches */
     uint32_t pad[2];
 } oe_dev_norm;
 
@@ -62,6 +62,9 @@ typedef struct oe_sgd_args {
     uint64_t norm;
     uint64_t lr_dev;  /* const float* device-resident base rate, or 0 = use lr    */
     uint64_t step_dev;/* int32_t* device step counter advanced by the launch, or 0 */
+    uint64_t ticket;  /* uint32_t* arrival counter: the last CTA marks the momentum buffers initialised */
+    uint32_t n_tensors; /* rows of the tensor table */
+    uint32_t pad;
 } oe_sgd_args;
 
 /* Ranks of a sharded step: byte distance from this rank's buffer to rank k's buffer of the
