@@ -22,3 +22,23 @@ def test_c_client_runs(tmp_path):
     out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stderr
     assert "c_client ok" in out.stdout
+
+
+def test_c_step_rate_runs(tmp_path):
+    """Eager steps issued from C: one launch per step, and the program reports what a step costs
+    without an interpreter in between (a few microseconds; the bound asserted here is loose)."""
+    import re
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    lib_dir = os.path.join(ROOT, "gograd_b200")
+    exe = tmp_path / "c_step_rate"
+    subprocess.run([cc, "-std=gnu11", "-Wall", "-Wextra", os.path.join(lib_dir, "csrc", "examples", "c_step_rate.c"),
+                    "-I", os.path.join(ROOT, "include"), "-L", lib_dir, "-loptengine", f"-Wl,-rpath,{lib_dir}", "-lm",
+                    "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    print(out.stdout)
+    found = re.search(r"host issue ([0-9.]+) us/step, with the device drained ([0-9.]+) us/step", out.stdout)
+    assert found, out.stdout
+    assert float(found.group(2)) < 100.0
