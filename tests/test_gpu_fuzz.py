@@ -1,5 +1,6 @@
 """Seeded randomised comparison of the engine with the oracle: random tensor counts, ragged sizes,
-unaligned addresses, absent gradients, groups, clip rules, shadows, flags and both optimizers.
+unaligned addresses, absent gradients, groups, clip rules, shadows, flags, work-unit sizes, gradient
+scales, host or device step counters and both optimizers.
 Every fp32 output must be bit-identical to the oracle's, every shadow equal to RNE of the master."""
 import numpy as np
 import pytest
@@ -39,6 +40,11 @@ def test_random_configuration(seed):
     clip = float(rng.choice([0.0, 0.05, 1e9]))          # off, triggers, never triggers
     devform = bool(rng.integers(0, 2))
     steps = 3
+    extra = np.random.default_rng(5000 + seed)          # drawn apart: the cases above keep their configurations
+    grad_scale = float(extra.choice([1.0, 1.0, 0.25, 1.0 / 3.0, 1.0 / 1024.0]))
+    unit = int(extra.choice([0, 0, 1024, 2048, 8192]))
+    device_counter = bool(extra.integers(0, 2))
+    step_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
     host_p = [rng.normal(0, .05, n).astype(np.float32) for n in sizes]
     p = [_slice_with_offset(x, o) for x, o in zip(host_p, offsets)]
     g = [_slice_with_offset(np.zeros(n, np.float32), o) for n, o in zip(sizes, offsets)]
@@ -69,9 +75,16 @@ def test_random_configuration(seed):
             state2 = s2[i] if (use_adamw or momentum > 0) else None
             descs.append(eng.TensorDesc(p[i], g[i] if present[i] else None, state1, state2,
                                         sh[i] if shadow_on else None, scales[i], decays[i]))
-        plan = eng.Plan(descs) if plan is None else (plan.update(descs) or plan)
-        # the oracle clips in place first, with the rule under test
+        if plan is None:
+            plan = eng.Plan(descs, 0, unit)
+            plan.set_grad_scale(grad_scale)
+        else:
+            plan.update(descs)
+        # the oracle reads the gradients at the plan's scale, then clips in place with the rule under test
         clipped = [None if x is None else x.copy() for x in grads]
+        for x in clipped:
+            if x is not None:
+                oracle.scale_(x, grad_scale)
         if clip > 0:
             norm = np.float32(np.sqrt(oracle.sum_squares(clipped)))
             coef = oracle.clip_coefficient(float(norm), clip, devform=devform)
@@ -85,12 +98,19 @@ def test_random_configuration(seed):
         if use_adamw:
             ref.step(clipped)
             b1, b2 = bias_corrections(0.9, beta2, t)
-            plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, beta2, 1e-8, b1, b2, clip, flags))
+            if device_counter:
+                plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, beta2, 1e-8, max_norm=clip, flags=flags,
+                                                 step_dev=step_dev.data_ptr()))
+            else:
+                plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, beta2, 1e-8, b1, b2, clip, flags))
         else:
             ref.step(clipped)
             flags |= (OE_NESTEROV if nesterov else 0) | (OE_MAXIMIZE if maximize else 0)
-            plan.sgd_step(eng.SGDHParams(0.05, momentum, dampening, clip, flags))
+            plan.sgd_step(eng.SGDHParams(0.05, momentum, dampening, clip, flags,
+                                         step_dev=step_dev.data_ptr() if device_counter else 0))
         torch.cuda.synchronize()
+        if device_counter:
+            assert int(step_dev.item()) == t, "the launch advances the device step counter"
         what = f"seed {seed} step {t}"
         for i in range(n_tensors):
             assert np.array_equal(p[i].cpu().numpy(), ref.params[i]), f"{what}: p[{i}] size {sizes[i]} offset {offsets[i]}"
