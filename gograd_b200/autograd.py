@@ -62,6 +62,11 @@ def lib() -> C.CDLL:
         h.gg_opt_free.restype = None
         h.gg_release_clip_state.restype = None
         h.gg_accumulator_reset.restype = None
+        h.gg_state_stream_abort.restype = None
+        h.gg_state_stream_abort.argtypes = [C.c_void_p]
+        h.gg_state_stream_finish.argtypes = [C.c_void_p]
+        h.gg_state_stream_next.argtypes = [C.c_void_p, C.c_char_p, C.c_int32, C.POINTER(C.c_int64)]
+        h.gg_state_stream_append.argtypes = [C.c_void_p, C.c_char_p, _f32p, C.c_int64]
         _lib = h
     return _lib
 
@@ -461,11 +466,8 @@ class _AdamWConfig(C.Structure):
                 ("beta2", C.c_float), ("eps", C.c_float)]
 
 
-def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], m: Sequence[np.ndarray],
-                      v: Sequence[np.ndarray], step_count: int, lr: float, weight_decay: float, beta1: float,
-                      beta2: float, eps: float, groups: Sequence[tuple]) -> None:
-    """Host-only: writes a "gograd-adamw" state file from gathered moments.
-    groups: (name, member indexes, lr_scale, weight_decay) per group."""
+def _state_c_args(names, shapes, step_count, lr, weight_decay, beta1, beta2, eps, groups):
+    """The flat C arguments both state writers share; the returned tuple keeps every array alive."""
     n = len(names)
     c_names = (C.c_char_p * max(n, 1))(*[x.encode() for x in names])
     flat, offsets = [], [0]
@@ -474,10 +476,6 @@ def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence
         offsets.append(len(flat))
     c_shapes = (C.c_int32 * max(len(flat), 1))(*flat)
     c_off = (C.c_int32 * len(offsets))(*offsets)
-    ms = [np.require(x, np.float32, "C") for x in m]
-    vs = [np.require(x, np.float32, "C") for x in v]
-    c_m = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in ms])
-    c_v = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in vs])
     cfg = _AdamWConfig(step_count, lr, weight_decay, beta1, beta2, eps)
     g_names = (C.c_char_p * max(len(groups), 1))(*[g[0].encode() for g in groups])
     g_off, g_mem = [0], []
@@ -489,4 +487,59 @@ def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence
     c_scales = (C.c_float * max(len(groups), 1))(*[g[2] for g in groups])
     c_decays = (C.c_float * max(len(groups), 1))(*[g[3] for g in groups])
     gs = _Groups(len(groups), g_names, c_goff, c_gmem, c_scales, c_decays)
+    return n, c_names, c_shapes, c_off, cfg, gs, (g_names, c_goff, c_gmem, c_scales, c_decays)
+
+
+def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], m: Sequence[np.ndarray],
+                      v: Sequence[np.ndarray], step_count: int, lr: float, weight_decay: float, beta1: float,
+                      beta2: float, eps: float, groups: Sequence[tuple]) -> None:
+    """Host-only: writes a "gograd-adamw" state file from gathered moments.
+    groups: (name, member indexes, lr_scale, weight_decay) per group."""
+    n, c_names, c_shapes, c_off, cfg, gs, _keep = _state_c_args(names, shapes, step_count, lr, weight_decay, beta1,
+                                                                beta2, eps, groups)
+    ms = [np.require(x, np.float32, "C") for x in m]
+    vs = [np.require(x, np.float32, "C") for x in v]
+    c_m = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in ms])
+    c_v = (_f32p * max(n, 1))(*[x.ctypes.data_as(_f32p) for x in vs])
     _check(lib().gg_adamw_state_write(path.encode(), n, c_names, c_shapes, c_off, c_m, c_v, C.byref(cfg), C.byref(gs)))
+
+
+class AdamWStateStream:
+    """The same "gograd-adamw" file written front to back without holding the moments: the file's
+    layout is fixed by names, shapes, configuration and groups; the values then arrive entry by
+    entry in the order the file stores them, an entry possibly in consecutive pieces."""
+
+    def __init__(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], step_count: int, lr: float,
+                 weight_decay: float, beta1: float, beta2: float, eps: float, groups: Sequence[tuple]):
+        n, c_names, c_shapes, c_off, cfg, gs, _keep = _state_c_args(names, shapes, step_count, lr, weight_decay, beta1,
+                                                                    beta2, eps, groups)
+        self._h = C.c_void_p()
+        _check(lib().gg_adamw_state_stream_begin(path.encode(), n, c_names, c_shapes, c_off, C.byref(cfg), C.byref(gs),
+                                                 C.byref(self._h)))
+
+    def next(self):
+        """(entry name, values still missing) of the entry the file wants next; None at the end."""
+        buf = C.create_string_buffer(64)
+        remaining = C.c_int64()
+        _check(lib().gg_state_stream_next(self._h, buf, len(buf), C.byref(remaining)))
+        name = buf.value.decode()
+        return (name, remaining.value) if name else None
+
+    def append(self, entry: str, values: np.ndarray) -> None:
+        v = np.require(values, np.float32, "C").reshape(-1)
+        _check(lib().gg_state_stream_append(self._h, entry.encode(), v.ctypes.data_as(_f32p), C.c_int64(v.size)))
+
+    def finish(self) -> None:
+        h, self._h = self._h, None
+        _check(lib().gg_state_stream_finish(h))
+
+    def abort(self) -> None:
+        if self._h:
+            h, self._h = self._h, None
+            lib().gg_state_stream_abort(h)
+
+    def __del__(self):
+        try:
+            self.abort()
+        except Exception:
+            pass

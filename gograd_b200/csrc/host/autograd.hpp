@@ -297,6 +297,7 @@ std::string validateOneCycle(const OneCycle& c);
 // Entries / metadata of the checkpoint layout (autograd/optimizer_state.go:142-160,
 // autograd/sgd_state.go:150-194, autograd/optimizer.go:85-120).
 std::string optimizerEntries(OptimizerState state, EntryMap* entries, Metadata* metadata);
+void optimizerMetadata(const OptimizerState& state, Metadata* metadata);
 std::string optimizerStateFromEntries(const EntryMap& entries, const Metadata& metadata, int count, OptimizerState* out);
 std::string sgdEntries(SGDState state, EntryMap* entries, Metadata* metadata);
 std::string sgdStateFromEntries(const EntryMap& entries, const Metadata& metadata, SGDState* out);

@@ -143,6 +143,13 @@ std::string optimizerEntries(OptimizerState state, EntryMap* entries, Metadata* 
         (*entries)["m." + std::to_string(i)] = std::move(m);
         (*entries)["v." + std::to_string(i)] = std::move(v);
     }
+    optimizerMetadata(state, metadata);
+    return "";
+}
+
+// The metadata document of a "gograd-adamw" file: everything but the moments themselves
+// (autograd/optimizer_state.go:142-160).
+void optimizerMetadata(const OptimizerState& state, Metadata* metadata) {
     std::string config = "{\"StepCount\":" + std::to_string(state.StepCount) + ",\"Moments\":null,\"Names\":" +
                          string_list(state.Names, true) + ",\"Shapes\":" + shapes_json(state.Shapes) + ",\"LR\":" +
                          f32(state.LR) + ",\"WeightDecay\":" + f32(state.WeightDecay) + ",\"Beta1\":" + f32(state.Beta1) +
@@ -150,7 +157,6 @@ std::string optimizerEntries(OptimizerState state, EntryMap* entries, Metadata* 
                          groups_json(state.Groups) + "}";
     *metadata = {{"format", "gograd-adamw"}, {"version", "1"}, {"step_count", std::to_string(state.StepCount)},
                  {"optimizer", config}};
-    return "";
 }
 
 std::string optimizerStateFromEntries(const EntryMap& entries, const Metadata& metadata, int count, OptimizerState* out) {

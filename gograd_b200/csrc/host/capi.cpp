@@ -1,8 +1,10 @@
 // Flat C handle API (include/gograd_host.h) over the C++ host mirror. Exceptions — the
 // mirror's counterpart of a Go panic — are turned into error codes here.
+#include <climits>
 #include <cmath>
 #include <cstring>
 #include <functional>
+#include <memory>
 
 #include "../../../include/gograd_host.h"
 #include "autograd.hpp"
@@ -545,49 +547,127 @@ int gg_safetensors_write(const char* path, const char* const* names, const float
     });
 }
 
+namespace {
+// Names, shapes, configuration and groups of an AdamW state from the flat C arguments; the moments
+// stay with the caller.
+std::string state_from_c(int32_t n, const char* const* names, const int32_t* shapes, const int32_t* shape_offsets,
+                         const gg_adamw_config* config, const gg_groups* groups, OptimizerState* out) {
+    if (!config || !groups || (n > 0 && (!names || !shapes || !shape_offsets))) return "NULL argument";
+    OptimizerState s;
+    s.StepCount = config->step_count;
+    s.LR = config->lr;
+    s.WeightDecay = config->weight_decay;
+    s.Beta1 = config->beta1;
+    s.Beta2 = config->beta2;
+    s.Eps = config->eps;
+    for (int32_t i = 0; i < n; i++) {
+        s.Names.push_back(names[i]);
+        s.Shapes.push_back(std::vector<int>(shapes + shape_offsets[i], shapes + shape_offsets[i + 1]));
+    }
+    for (int32_t g = 0; g < groups->n_groups; g++) {
+        OptimizerGroupState gs;
+        gs.Name = groups->group_names[g];
+        for (int32_t k = groups->offsets[g]; k < groups->offsets[g + 1]; k++) {
+            int32_t index = groups->members[k];
+            if (index < 0 || index >= n) return "autograd: group member out of range";
+            gs.Names.push_back(names[index]);
+        }
+        float scale = 0;
+        std::string e = normalizeLRScale(groups->lr_scales[g], &scale);
+        if (!e.empty()) return e;
+        gs.LRScale = scale;
+        gs.WeightDecay = groups->decays[g];
+        s.Groups.push_back(gs);
+    }
+    *out = std::move(s);
+    return "";
+}
+}  // namespace
+
 int gg_adamw_state_write(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
                          const int32_t* shape_offsets, const float* const* m, const float* const* v,
                          const gg_adamw_config* config, const gg_groups* groups) {
     return guarded([&]() -> std::string {
-        if (!config || !groups) return "NULL argument";
         OptimizerState s;
-        s.StepCount = config->step_count;
-        s.LR = config->lr;
-        s.WeightDecay = config->weight_decay;
-        s.Beta1 = config->beta1;
-        s.Beta2 = config->beta2;
-        s.Eps = config->eps;
+        std::string e = state_from_c(n, names, shapes, shape_offsets, config, groups, &s);
+        if (!e.empty()) return e;
         s.Moments.resize((size_t)n);
         for (int32_t i = 0; i < n; i++) {
-            s.Names.push_back(names[i]);
-            std::vector<int> shape(shapes + shape_offsets[i], shapes + shape_offsets[i + 1]);
             long long count = 1;
-            for (int d : shape) count *= d;
-            s.Shapes.push_back(shape);
+            for (int d : s.Shapes[(size_t)i]) count *= d;
             s.Moments[(size_t)i].M.assign(m[i], m[i] + count);
             s.Moments[(size_t)i].V.assign(v[i], v[i] + count);
         }
-        for (int32_t g = 0; g < groups->n_groups; g++) {
-            OptimizerGroupState gs;
-            gs.Name = groups->group_names[g];
-            for (int32_t k = groups->offsets[g]; k < groups->offsets[g + 1]; k++) {
-                int32_t index = groups->members[k];
-                if (index < 0 || index >= n) return "autograd: group member out of range";
-                gs.Names.push_back(names[index]);
-            }
-            float scale = 0;
-            std::string e = normalizeLRScale(groups->lr_scales[g], &scale);
-            if (!e.empty()) return e;
-            gs.LRScale = scale;
-            gs.WeightDecay = groups->decays[g];
-            s.Groups.push_back(gs);
-        }
         EntryMap entries;
         Metadata metadata;
-        std::string e = optimizerEntries(std::move(s), &entries, &metadata);
+        e = optimizerEntries(std::move(s), &entries, &metadata);
         if (!e.empty()) return e;
         return write_safetensors(path, entries, &metadata);
     });
+}
+
+struct gg_state_stream {
+    SafeTensorStream stream;
+};
+
+int gg_adamw_state_stream_begin(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                                const int32_t* shape_offsets, const gg_adamw_config* config, const gg_groups* groups,
+                                gg_state_stream** out) {
+    return guarded([&]() -> std::string {
+        if (!path || !out) return "NULL argument";
+        OptimizerState s;
+        std::string e = state_from_c(n, names, shapes, shape_offsets, config, groups, &s);
+        if (!e.empty()) return e;
+        std::map<std::string, std::vector<int>> entry_shapes;
+        for (int32_t i = 0; i < n; i++) {
+            long long count = 0;
+            if (!safe_numel(s.Shapes[(size_t)i], INT32_MAX, &count)) return "autograd: invalid shape of " + s.Names[(size_t)i];
+            entry_shapes["m." + std::to_string(i)] = {(int)count};
+            entry_shapes["v." + std::to_string(i)] = {(int)count};
+        }
+        Metadata metadata;
+        optimizerMetadata(s, &metadata);
+        std::unique_ptr<gg_state_stream> h(new gg_state_stream());
+        e = h->stream.Begin(path, entry_shapes, &metadata);
+        if (!e.empty()) return e;
+        *out = h.release();
+        return "";
+    });
+}
+
+int gg_state_stream_next(const gg_state_stream* s, char* name_out, int32_t capacity, int64_t* remaining_out) {
+    if (!s || !name_out || !remaining_out || capacity < 1) return fail("NULL argument");
+    std::string name;
+    long long remaining = 0;
+    if (!s->stream.Next(&name, &remaining)) {
+        name_out[0] = 0;
+        *remaining_out = 0;
+        return 0;
+    }
+    if ((size_t)capacity <= name.size()) return fail("name buffer too small");
+    memcpy(name_out, name.c_str(), name.size() + 1);
+    *remaining_out = remaining;
+    return 0;
+}
+
+int gg_state_stream_append(gg_state_stream* s, const char* entry, const float* values, int64_t count) {
+    return guarded([&]() -> std::string {
+        if (!s || !entry || (count > 0 && !values)) return "NULL argument";
+        return s->stream.Append(entry, values, count);
+    });
+}
+
+int gg_state_stream_finish(gg_state_stream* s) {
+    if (!s) return fail("NULL argument");
+    std::string e = s->stream.Finish();
+    delete s;
+    return e.empty() ? 0 : fail(e);
+}
+
+void gg_state_stream_abort(gg_state_stream* s) {
+    if (!s) return;
+    s->stream.Abort();
+    delete s;
 }
 
 int gg_safetensors_describe(const char* path, char* out, int32_t capacity) {

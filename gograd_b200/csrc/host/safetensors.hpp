@@ -55,21 +55,22 @@ inline bool safe_numel(const std::vector<int>& shape, long long limit, long long
     return true;
 }
 
-inline std::string write_safetensors(const std::string& path, const EntryMap& entries, const Metadata* metadata) {
-    // Go marshals map[string]any with sorted keys; "__metadata__" sorts before any
-    // name starting with a letter but not before every possible name, so merge by key.
+// The JSON header of a container holding F32 entries of the given shapes in sorted-name order
+// with contiguous offsets, padded with spaces to a multiple of 8 (autograd/safetensors.go:30-98).
+// Go marshals map[string]any with sorted keys; "__metadata__" sorts before any name starting
+// with a letter but not before every possible name, so it is merged by key.
+inline std::string safetensors_header(const std::map<std::string, std::vector<int>>& shapes, const Metadata* metadata,
+                                      std::string* out) {
     std::map<std::string, std::string> header;  // name -> JSON text
     long long offset = 0;
-    for (const auto& kv : entries) {
+    for (const auto& kv : shapes) {
         const std::string& name = kv.first;
-        const SafeTensorEntry& e = kv.second;
         long long count = 0;
-        if (!safe_numel(e.Shape, (long long)e.Values.size(), &count) || count != (long long)e.Values.size() ||
-            name == "__metadata__")
+        if (!safe_numel(kv.second, (long long)1 << 40, &count) || name == "__metadata__")
             return "autograd: incompatible tensor " + name;
         long long end = offset + count * 4;
         std::string j = "{\"dtype\":\"F32\",\"shape\":[";
-        for (size_t i = 0; i < e.Shape.size(); i++) j += (i ? "," : "") + std::to_string(e.Shape[i]);
+        for (size_t i = 0; i < kv.second.size(); i++) j += (i ? "," : "") + std::to_string(kv.second[i]);
         j += "],\"data_offsets\":[" + std::to_string(offset) + "," + std::to_string(end) + "]}";
         header[name] = j;
         offset = end;
@@ -92,40 +93,148 @@ inline std::string write_safetensors(const std::string& path, const EntryMap& en
     h += "}";
     while (h.size() % 8 != 0) h += ' ';
     if (h.size() > kSafeTensorHeaderLimit) return "autograd: invalid safetensors header length";
+    *out = std::move(h);
+    return "";
+}
 
-    std::string dir = ".";
-    size_t slash = path.rfind('/');
-    if (slash != std::string::npos) dir = slash == 0 ? "/" : path.substr(0, slash);
-    std::string tmpl = dir + "/.gograd-checkpoint-XXXXXX";
-    std::vector<char> name(tmpl.begin(), tmpl.end());
-    name.push_back(0);
-    int fd = mkstemp(name.data());
-    if (fd < 0) return "autograd: cannot create a temporary file in " + dir;
-    auto write_all = [&](const void* data, size_t n) {
+// A container written front to back without holding its data: the shapes are known first, the
+// values arrive entry by entry in sorted-name order (an entry may arrive in consecutive pieces).
+// Temporary file in the target directory, fsync, rename: the same discipline and the same bytes
+// as write_safetensors.
+class SafeTensorStream {
+   public:
+    SafeTensorStream() = default;
+    SafeTensorStream(const SafeTensorStream&) = delete;
+    SafeTensorStream& operator=(const SafeTensorStream&) = delete;
+    ~SafeTensorStream() { Abort(); }
+
+    std::string Begin(const std::string& path, const std::map<std::string, std::vector<int>>& shapes,
+                      const Metadata* metadata) {
+        if (fd_ >= 0) return "autograd: the stream is already open";
+        std::string h;
+        std::string e = safetensors_header(shapes, metadata, &h);
+        if (!e.empty()) return e;
+        order_.clear();
+        for (const auto& kv : shapes) {
+            long long count = 0;
+            safe_numel(kv.second, (long long)1 << 40, &count);
+            order_.push_back({kv.first, count});
+        }
+        next_ = 0;
+        done_in_entry_ = 0;
+        skip_empty();
+        path_ = path;
+        std::string dir = ".";
+        size_t slash = path.rfind('/');
+        if (slash != std::string::npos) dir = slash == 0 ? "/" : path.substr(0, slash);
+        std::string tmpl = dir + "/.gograd-checkpoint-XXXXXX";
+        std::vector<char> name(tmpl.begin(), tmpl.end());
+        name.push_back(0);
+        fd_ = mkstemp(name.data());
+        if (fd_ < 0) return "autograd: cannot create a temporary file in " + dir;
+        tmp_ = name.data();
+        unsigned char prefix[8];
+        uint64_t hl = h.size();
+        for (int i = 0; i < 8; i++) prefix[i] = (unsigned char)(hl >> (8 * i));
+        if (!write_all(prefix, 8) || !write_all(h.data(), h.size())) {
+            Abort();
+            return "autograd: writing " + path + " failed";
+        }
+        return "";
+    }
+
+    // The entry the file wants next and how many of its values are still missing; false at the end.
+    bool Next(std::string* name, long long* remaining) const {
+        if (next_ >= order_.size()) return false;
+        *name = order_[next_].first;
+        *remaining = order_[next_].second - done_in_entry_;
+        return true;
+    }
+
+    std::string Append(const std::string& name, const float* values, long long count) {
+        if (fd_ < 0) return "autograd: the stream is not open";
+        if (next_ >= order_.size() || order_[next_].first != name)
+            return "autograd: entry " + name + " is out of order" +
+                   (next_ < order_.size() ? " (the file wants " + order_[next_].first + ")" : " (the file is complete)");
+        if (count < 0 || count > order_[next_].second - done_in_entry_) return "autograd: too many values for " + name;
+        if (count > 0 && !write_all(values, (size_t)count * 4)) {  // host is little-endian: floats are written as they are
+            Abort();
+            return "autograd: writing " + path_ + " failed";
+        }
+        done_in_entry_ += count;
+        if (done_in_entry_ == order_[next_].second) {
+            next_++;
+            done_in_entry_ = 0;
+            skip_empty();
+        }
+        return "";
+    }
+
+    std::string Finish() {
+        if (fd_ < 0) return "autograd: the stream is not open";
+        if (next_ < order_.size()) {
+            std::string missing = order_[next_].first;
+            Abort();
+            return "autograd: entry " + missing + " was not written";
+        }
+        bool ok = fsync(fd_) == 0;
+        ok = (close(fd_) == 0) && ok;
+        fd_ = -1;
+        if (!ok || rename(tmp_.c_str(), path_.c_str()) != 0) {
+            unlink(tmp_.c_str());
+            return "autograd: writing " + path_ + " failed";
+        }
+        return "";
+    }
+
+    void Abort() {
+        if (fd_ >= 0) {
+            close(fd_);
+            unlink(tmp_.c_str());
+            fd_ = -1;
+        }
+    }
+
+   private:
+    int fd_ = -1;
+    std::string path_, tmp_;
+    std::vector<std::pair<std::string, long long>> order_;
+    size_t next_ = 0;
+    long long done_in_entry_ = 0;
+
+    void skip_empty() {
+        while (next_ < order_.size() && order_[next_].second == 0) next_++;
+    }
+    bool write_all(const void* data, size_t n) {
         const char* p = (const char*)data;
         while (n > 0) {
-            ssize_t w = ::write(fd, p, n);
+            ssize_t w = ::write(fd_, p, n);
             if (w <= 0) return false;
             p += w;
             n -= (size_t)w;
         }
         return true;
-    };
-    unsigned char prefix[8];
-    uint64_t hl = h.size();
-    for (int i = 0; i < 8; i++) prefix[i] = (unsigned char)(hl >> (8 * i));
-    bool ok = write_all(prefix, 8) && write_all(h.data(), h.size());
-    for (const auto& kv : entries) {  // host is little-endian: floats are written as they are
-        if (!ok) break;
-        if (!kv.second.Values.empty()) ok = write_all(kv.second.Values.data(), kv.second.Values.size() * 4);
     }
-    ok = ok && fsync(fd) == 0;
-    ok = (close(fd) == 0) && ok;
-    if (!ok || rename(name.data(), path.c_str()) != 0) {
-        unlink(name.data());
-        return "autograd: writing " + path + " failed";
+};
+
+inline std::string write_safetensors(const std::string& path, const EntryMap& entries, const Metadata* metadata) {
+    std::map<std::string, std::vector<int>> shapes;
+    for (const auto& kv : entries) {
+        long long count = 0;
+        if (!safe_numel(kv.second.Shape, (long long)kv.second.Values.size(), &count) ||
+            count != (long long)kv.second.Values.size() || kv.first == "__metadata__")
+            return "autograd: incompatible tensor " + kv.first;
+        shapes[kv.first] = kv.second.Shape;
     }
-    return "";
+    SafeTensorStream stream;
+    std::string e = stream.Begin(path, shapes, metadata);
+    if (!e.empty()) return e;
+    for (const auto& kv : entries) {
+        if (kv.second.Values.empty()) continue;
+        e = stream.Append(kv.first, kv.second.Values.data(), (long long)kv.second.Values.size());
+        if (!e.empty()) return e;
+    }
+    return stream.Finish();
 }
 
 inline std::string read_safetensors(const std::string& path, EntryMap* entries, Metadata* metadata) {

@@ -370,10 +370,62 @@ class Zero1AdamW(Zero1Schedule):
             return [("default", members, scale, decay)]
         return [(f"group{k}", members, scale, decay) for k, ((scale, decay), members) in enumerate(seen.items())]
 
-    def save_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
-        """Gathers the sharded moments and lets rank 0 write them as a "gograd-adamw" state file:
-        entries m.<i> / v.<i> of shape [numel] per parameter plus the configuration metadata, the
-        layout an unsharded AdamW reads back (autograd/optimizer_state.go:142-226)."""
+    def save_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], streaming: bool = True) -> None:
+        """Rank 0 writes the sharded moments as a "gograd-adamw" state file: entries m.<i> / v.<i> of
+        shape [numel] per parameter plus the configuration metadata, the layout an unsharded AdamW
+        reads back (autograd/optimizer_state.go:142-226).
+
+        streaming (default): the file is written front to back in the order it stores its entries;
+        for each entry the owners send their pieces to rank 0, which appends them, so rank 0 never
+        holds more than one piece on the host. streaming=False gathers all of m and v on rank 0
+        first (12 bytes of host memory per parameter of the model) and writes from memory; both
+        produce the same bytes."""
+        if not streaming:
+            return self._save_state_gathered(path, names, shapes)
+        torch, dist = self.torch, self.dist
+        L = self.layout
+        # who holds which part of every tensor: (rank, offset in the rank's shard, length), by rank
+        holders: List[List[Tuple[int, int, int]]] = [[] for _ in L.numels]
+        for r in range(self.world):
+            lo, _ = L.shard_range(r)
+            for pc in L.pieces(r):
+                holders[pc.tensor].append((r, pc.flat_offset - lo, pc.length))
+        groups = self.groups()
+        stream = None
+        if self.rank == 0:
+            from . import autograd as host
+            stream = host.AdamWStateStream(path, list(names), [list(s) for s in shapes], self.step_count, self.lr,
+                                           groups[0][3], self.beta1, self.beta2, self.eps, groups)
+        try:
+            # every rank walks the same order: the file's (sorted entry names)
+            order = sorted([f"{k}.{i}" for k in ("m", "v") for i in range(len(L.numels))])
+            bounce = None
+            for entry in order:
+                key, index = entry.split(".")
+                shard = self.m if key == "m" else self.v
+                for r, a, n in holders[int(index)]:
+                    if self.rank == 0:
+                        if r == 0:
+                            piece = shard[a:a + n]
+                        else:
+                            if bounce is None or bounce.numel() < n:
+                                bounce = torch.empty(max(n, 1 << 20), dtype=torch.float32, device=shard.device)
+                            piece = bounce[:n]
+                            dist.recv(piece, src=r, group=self.pg)
+                        stream.append(entry, piece.cpu().numpy())
+                    elif self.rank == r:
+                        dist.send(shard[a:a + n].contiguous(), dst=0, group=self.pg)
+            if self.rank == 0:
+                assert stream.next() is None
+                stream.finish()
+        except BaseException:
+            if stream is not None:
+                stream.abort()
+            raise
+        if self.world > 1:
+            dist.barrier(group=self.pg)
+
+    def _save_state_gathered(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
         torch, dist = self.torch, self.dist
         gathered = {}
         for key, shard in (("m", self.m), ("v", self.v)):

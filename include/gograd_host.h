@@ -155,6 +155,22 @@ typedef struct gg_adamw_config {
 OE_API int gg_adamw_state_write(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
                                 const int32_t* shape_offsets, const float* const* m, const float* const* v,
                                 const gg_adamw_config* config, const gg_groups* groups);
+/* The same file written front to back without holding the moments: begin with names, shapes,
+ * configuration and groups (the header and its offsets are fixed by them), then hand over the
+ * values entry by entry in the order the file stores them (sorted names: m.0, m.1, m.10, ...;
+ * gg_state_stream_next names the entry the file wants and how many of its values are missing, an
+ * empty name at the end). An entry may arrive in consecutive pieces, so a sharded optimizer passes
+ * each owner's piece as it is gathered. finish checks that everything arrived, fsyncs and renames
+ * the temporary file into place; finish and abort free the handle. Byte for byte the file
+ * gg_adamw_state_write produces. Needs no GPU. */
+typedef struct gg_state_stream gg_state_stream;
+OE_API int gg_adamw_state_stream_begin(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                                       const int32_t* shape_offsets, const gg_adamw_config* config,
+                                       const gg_groups* groups, gg_state_stream** out);
+OE_API int gg_state_stream_next(const gg_state_stream* s, char* name_out, int32_t capacity, int64_t* remaining_out);
+OE_API int gg_state_stream_append(gg_state_stream* s, const char* entry, const float* values, int64_t count);
+OE_API int gg_state_stream_finish(gg_state_stream* s);
+OE_API void gg_state_stream_abort(gg_state_stream* s);
 /* Validates a file with the reference reader's rules and returns a JSON description
  * {"entries":{name:{"shape":[..],"sum":float64 sum of the values}},"metadata":{..}} in out. */
 OE_API int gg_safetensors_describe(const char* path, char* out, int32_t capacity);

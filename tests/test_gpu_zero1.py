@@ -209,6 +209,68 @@ def test_all_real_ranks_of_the_box(comm):
             assert np.array_equal(shadow[o:o + n], own), f"rank {rank} shadow[{i}] ({comm})"
 
 
+def _saving_rank_main(rank, world, port, out_dir, queue):
+    import torch.distributed as dist
+    from gograd_b200.zero1 import Zero1AdamW
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank, comm="peer")
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+    for step in (1, 2):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+        opt.step()
+    names = [f"t{i}" for i in range(len(NUMELS))]
+    shapes = [[n] for n in NUMELS]
+    opt.save_state(os.path.join(out_dir, "streamed.safetensors"), names, shapes)
+    opt.save_state(os.path.join(out_dir, "gathered.safetensors"), names, shapes, streaming=False)
+    torch.cuda.synchronize()
+    queue.put((rank, opt.lo, opt.m.cpu().numpy(), opt.v.cpu().numpy()))
+    opt.close()
+    dist.destroy_process_group()
+
+
+def test_two_real_ranks_stream_their_state_into_one_file(tmp_path):
+    """Two ranks, tensors straddling the shard boundary: the streamed file (owners send their pieces
+    to rank 0 entry by entry) equals the gathered one byte for byte and holds every rank's moments."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from gograd_b200 import autograd as ag
+    from gograd_b200.zero1 import ShardLayout
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_saving_rank_main, args=(r, world, port, str(tmp_path), queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    streamed = open(tmp_path / "streamed.safetensors", "rb").read()
+    assert streamed == open(tmp_path / "gathered.safetensors", "rb").read()
+    L = ShardLayout(NUMELS, world)
+    flat_m, flat_v = np.zeros(L.total, np.float32), np.zeros(L.total, np.float32)
+    for rank, lo, m, v in results:
+        flat_m[lo:lo + m.size], flat_v[lo:lo + v.size] = m, v
+    d = ag.safetensors_describe(str(tmp_path / "streamed.safetensors"))
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert d["entries"][f"m.{i}"]["shape"] == [n]
+        for key, flat in (("m", flat_m), ("v", flat_v)):
+            want = flat[o:o + n].astype(np.float64)
+            assert abs(d["entries"][f"{key}.{i}"]["sum"] - float(want.sum())) <= 1e-9 * float(np.abs(want).sum()) + 1e-30
+
+
 def _leaving_rank_main(rank, world, port, queue):
     """Rank 1 leaves after step 1, between steps: every rank has synchronised its device and met
     the others in the store first, so nothing of the leaving rank is in flight anywhere."""
@@ -318,7 +380,10 @@ def test_sharded_state_file_loads_into_unsharded_adamw_and_back(tmp_path):
         for step in (1, 2):
             sharded_step(z, step)
         path = str(tmp_path / "sharded.safetensors")
-        z.save_state(path, names, shapes)
+        z.save_state(path, names, shapes)                       # streamed, entry by entry
+        gathered = str(tmp_path / "gathered.safetensors")
+        z.save_state(gathered, names, shapes, streaming=False)  # all of m and v in host memory first
+        assert open(path, "rb").read() == open(gathered, "rb").read()
         d = ag.safetensors_describe(path)
         assert d["metadata"]["format"] == "gograd-adamw" and d["metadata"]["step_count"] == "2"
         assert sorted(d["entries"]) == sorted([f"m.{i}" for i in range(len(NUMELS))] + [f"v.{i}" for i in range(len(NUMELS))])

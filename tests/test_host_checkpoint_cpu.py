@@ -2,6 +2,7 @@
 the reference writes (autograd/safetensors.go:30-98) and the rules its reader enforces
 (autograd/safetensors_stream.go:28-96)."""
 import json
+import os
 import struct
 
 import numpy as np
@@ -108,3 +109,62 @@ def test_grad_accumulator_bookkeeping():
     with pytest.raises(ag.HostError, match="invalid gradient accumulator"):
         broken.MicroBatch()
     assert broken.Pending() == 0, "a failed call changes nothing"
+
+
+def _state_case():
+    rng = np.random.default_rng(3)
+    names = [f"layer{i}.w" for i in range(12)]          # twelve entries: "m.10" sorts before "m.2"
+    shapes = [[3, 4], [5], [2, 2, 2], [1], [7], [6], [4, 4], [9], [10], [11], [2, 6], [13]]
+    m = [rng.normal(0, 1, int(np.prod(s))).astype(np.float32) for s in shapes]
+    v = [np.abs(rng.normal(0, 1, int(np.prod(s)))).astype(np.float32) for s in shapes]
+    groups = [("decay", [0, 2, 4, 6, 8, 10], 1.0, 0.1), ("plain", [1, 3, 5, 7, 9, 11], 0.5, 0.0)]
+    config = dict(step_count=17, lr=3e-4, weight_decay=0.1, beta1=0.9, beta2=0.95, eps=1e-8)
+    return names, shapes, m, v, groups, config
+
+
+def test_streamed_state_file_equals_the_one_written_from_memory(tmp_path):
+    """The streaming writer produces the bytes of the in-memory writer; entries arrive in the file's
+    own order (sorted names), whole or in pieces."""
+    names, shapes, m, v, groups, c = _state_case()
+    whole, streamed = str(tmp_path / "whole.safetensors"), str(tmp_path / "streamed.safetensors")
+    ag.adamw_state_write(whole, names, shapes, m, v, c["step_count"], c["lr"], c["weight_decay"], c["beta1"], c["beta2"],
+                         c["eps"], groups)
+    stream = ag.AdamWStateStream(streamed, names, shapes, c["step_count"], c["lr"], c["weight_decay"], c["beta1"],
+                                 c["beta2"], c["eps"], groups)
+    order = []
+    while True:
+        nxt = stream.next()
+        if nxt is None:
+            break
+        entry, remaining = nxt
+        key, index = entry.split(".")
+        values = (m if key == "m" else v)[int(index)]
+        assert remaining == values.size
+        order.append(entry)
+        if values.size > 3:                                  # two pieces, as two owners of a straddling tensor would
+            stream.append(entry, values[:3])
+            assert stream.next() == (entry, values.size - 3)
+            stream.append(entry, values[3:])
+        else:
+            stream.append(entry, values)
+    stream.finish()
+    assert order == sorted(order) and order[:4] == ["m.0", "m.1", "m.10", "m.11"]
+    assert open(whole, "rb").read() == open(streamed, "rb").read()
+
+
+def test_stream_rejects_wrong_order_and_incomplete_files(tmp_path):
+    names, shapes, m, v, groups, c = _state_case()
+    path = str(tmp_path / "broken.safetensors")
+    args = (names, shapes, c["step_count"], c["lr"], c["weight_decay"], c["beta1"], c["beta2"], c["eps"], groups)
+    stream = ag.AdamWStateStream(path, *args)
+    with pytest.raises(ag.HostError, match="out of order"):
+        stream.append("m.1", m[1])
+    stream.append("m.0", m[0][:5])
+    with pytest.raises(ag.HostError, match="too many values"):
+        stream.append("m.0", m[0])
+    with pytest.raises(ag.HostError, match="m.0 was not written"):
+        stream.finish()
+    assert [f for f in os.listdir(tmp_path) if not f.startswith("whole")] == [], "no file and no temporary left behind"
+    stream = ag.AdamWStateStream(path, *args)
+    stream.abort()
+    assert os.listdir(tmp_path) == []
