@@ -653,3 +653,26 @@ def test_device_step_counter_is_advanced_by_the_update_launch_itself(eng, orc):
     assert eng.launch_count() == 3 and eng.launch_count("oe_sgd_fused") == 3
     assert float(x[0]) == np.float32(1.0) - np.float32(0.05) - np.float32(0.05) - np.float32(0.05)
     plan.close()
+
+
+def test_default_work_unit_follows_the_size_of_the_parameter_list(eng):
+    """Left to the library, the work unit is 4096 elements for sets that stream from HBM and is halved
+    (down to 1024) while the list would give fewer than two units per SM; an explicit size is kept."""
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+
+    def unit_for(numels, chunk=0):
+        p = [torch.zeros(n, device="cuda") for n in numels]
+        plan = eng.Plan([eng.TensorDesc(x, x.clone(), x.clone(), x.clone()) for x in p], 0, chunk)
+        unit, units = plan.info(5), plan.info(1)
+        plan.close()
+        return unit, units
+
+    assert unit_for([10])[0] == 1024
+    assert unit_for([784 * 256, 256, 2560, 10]) == (1024, 196 + 1 + 3 + 1)
+    unit, units = unit_for([4096 * 2 * sms])            # exactly two 4096-element units per SM
+    assert unit == 4096 and units == 2 * sms
+    unit, units = unit_for([4096 * 2 * sms - 4096])     # one short: halve once
+    assert unit == 2048 and units >= 2 * sms
+    assert unit_for([10], 8192)[0] == 8192
+    with pytest.raises(eng.engine.EngineError):
+        unit_for([10], 1000)
