@@ -117,6 +117,11 @@ def run(args) -> int:
         k1, k2 = phases.get("reduce_ms"), phases.get("update_ms")
         nvlink_ms = (pull_remote + push_remote) / (NVLINK_PEER_GBS * 1e9) * 1e3
         hbm_ms = ((4.0 * world + 4.0) + 30.0) * shard / (peak * 1e9) * 1e3
+        # The update cannot start before the global norm is known, i.e. before every rank's reduction is
+        # over, so the two phases cannot overlap: the reduction at link rate (or its own HBM traffic, if
+        # that takes longer) followed by the update at HBM rate (or its remote stores at link rate).
+        reduce_floor = max(pull_remote / (NVLINK_PEER_GBS * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) * 1e3
+        update_floor = max(30.0 * shard / (peak * 1e9), push_remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
         roofline = {
             "bound": "nvlink", "kernel": "oe_peer_reduce_sumsq (pull reduce-scatter + norm)" if comm == "peer" else "ncclReduceScatter",
             "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
@@ -128,8 +133,9 @@ def run(args) -> int:
                               "nvlink_achieved": push_remote / (k2 * 1e-3) / 1e9 if k2 else None,
                               "hbm_bytes": 30.0 * shard,
                               "hbm_achieved": 30.0 * shard / (k2 * 1e-3) / 1e9 if k2 else None, "hbm_peak": peak},
-            "step_floor_ms": {"nvlink": nvlink_ms, "hbm": hbm_ms},
+            "step_floor_ms": {"nvlink": nvlink_ms, "hbm": hbm_ms, "reduce_then_update": reduce_floor + update_floor},
             "step_frac_of_floor": max(nvlink_ms, hbm_ms) / ms_per_step,
+            "step_frac_of_serial_floor": (reduce_floor + update_floor) / ms_per_step,
             "phases_ms": phases,
         }
         line = {
