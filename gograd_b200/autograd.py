@@ -109,6 +109,10 @@ class Tensor:
     def has_grad(self) -> bool:
         return bool(lib().gg_tensor_has_grad(self._h))
 
+    @property
+    def grad_known_zero(self) -> bool:
+        return bool(lib().gg_tensor_grad_known_zero(self._h))
+
     def set_grad(self, values) -> None:
         """None makes the gradient absent (a nil gradBuf)."""
         if values is None:
@@ -245,6 +249,10 @@ class _Optimizer:
 
     def SetEngine(self, write_shadow: bool = False, clip_devform: bool = False) -> None:
         _check(lib().gg_opt_set_engine(self._h, int(write_shadow), int(clip_devform)))
+
+    def SetZeroGradInStep(self, on: bool = True) -> None:
+        """AdamW only: Step stores zeros over the gradients it reads; ZeroGrad then has nothing to launch."""
+        _check(lib().gg_opt_set_zero_grad_in_step(self._h, int(on)))
 
     def SetGradScale(self, scale: float) -> None:
         """Step and StepClipped read every gradient element as float32(g * scale) from now on."""

@@ -40,6 +40,11 @@ class Tensor {
     bool RequiresGrad = true;
     uint64_t buf = 0, gradBuf = 0, bf16Buf = 0;
     uint64_t version = 0, bf16Version = 0;
+    // True while the gradient buffer is known to hold zeros: freshly created, zeroed, or zeroed by an
+    // optimizer step that was asked to do so. Anything that writes a gradient clears it (SetGrad here;
+    // a backward pass that is handed the raw address must call MarkGradWritten).
+    bool gradKnownZero = false;
+    void MarkGradWritten() { gradKnownZero = false; }
 
     static std::string New(const std::vector<float>& values, const std::vector<int>& shape, int device,
                            bool requiresGrad, std::shared_ptr<Tensor>* out);
@@ -167,6 +172,10 @@ struct EngineOptions {
     bool WriteShadow = false;
     bool ClipDevForm = false;  // the CUDA kernels' fminf(1, .) rule instead of the host rule
     uint64_t Stream = 0;
+    // Step stores zeros over every gradient it has read (the next group's ZeroGrad then finds nothing to do:
+    // one pass and one launch less per update, autograd/training_loop.go:125-133). AdamW only: SGD's eager
+    // ZeroGrad releases its gradients (autograd/sgd.go:231-246), and a zeroed buffer is not an absent one.
+    bool ZeroGradInStep = false;
     // Step and StepClipped read every gradient element as (float)(g * GradScale): the 1/groups
     // factor of gradient accumulation, applied in the pass that reads the gradients anyway
     // instead of through the seed of every backward.

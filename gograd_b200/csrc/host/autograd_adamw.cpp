@@ -151,7 +151,8 @@ void AdamW::run(float maxNorm, bool captured) {
         hp.bc2 = (float)(1.0 - std::pow((double)Beta2, (double)StepCount));
     }
     hp.max_norm = maxNorm;
-    hp.flags = (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u);
+    hp.flags = (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u) |
+               (Engine.ZeroGradInStep ? OE_ZERO_GRAD : 0u);
     if (maxNorm > 0 && (rc = oe_grad_norm(plan_, 0, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_grad_norm", rc));
     if ((rc = oe_adamw_step(plan_, &hp, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_adamw_step", rc));
     if (!captured) {
@@ -162,6 +163,7 @@ void AdamW::run(float maxNorm, bool captured) {
             // rewritten it: bump the version and stamp the shadow as current.
             t.version++;
             if (Engine.WriteShadow && t.bf16Buf != 0) t.bf16Version = t.version;
+            if (Engine.ZeroGradInStep) t.gradKnownZero = true;  // the update stored zeros over what it read
         }
         if (graphStep_ != 0) {
             std::string e2 = PrepareGraph();
@@ -184,10 +186,16 @@ float AdamW::LastGradNorm() {
 
 void AdamW::ZeroGrad() {
     // AdamW.ZeroGrad keeps the buffers and zeroes them (autograd/nn.go:533-537); one launch
-    // when the plan already describes the current gradients, else per tensor.
+    // when the plan already describes the current gradients, else per tensor; nothing at all when
+    // every present gradient is known to hold zeros already (the last Step zeroed them).
+    bool dirty = false;
+    for (const Parameter& p : Params) dirty = dirty || (p.Value->gradBuf != 0 && !p.Value->gradKnownZero);
+    if (!dirty) return;
     if (plan_ != nullptr && refreshPlan().empty()) {
         int rc = oe_zero_grads(plan_, Engine.Stream);
         if (rc != 0) throw std::runtime_error(engine_error("oe_zero_grads", rc));
+        for (Parameter& p : Params)
+            if (p.Value->gradBuf != 0) p.Value->gradKnownZero = true;
         return;
     }
     for (Parameter& p : Params) {

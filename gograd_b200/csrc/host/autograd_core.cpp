@@ -95,6 +95,7 @@ std::string Tensor::EnsureGrad() {
     if (gradBuf != 0 || Numel() == 0) return "";
     GG_TRY(oe_mem_alloc(Device, (uint64_t)Numel() * 4, &gradBuf), "oe_mem_alloc");
     GG_TRY(oe_memset_u32(Device, gradBuf, 0, (uint64_t)Numel(), 0), "oe_memset_u32");
+    gradKnownZero = true;
     return "";
 }
 
@@ -103,6 +104,7 @@ std::string Tensor::SetGrad(const std::vector<float>& values) {
     std::string e = EnsureGrad();
     if (!e.empty()) return e;
     if (values.empty()) return "";
+    gradKnownZero = false;
     GG_TRY(oe_memcpy_h2d(Device, gradBuf, values.data(), values.size() * 4, 0), "oe_memcpy_h2d");
     GG_TRY(oe_stream_sync(Device, 0), "oe_stream_sync");
     return "";
@@ -111,11 +113,13 @@ std::string Tensor::SetGrad(const std::vector<float>& values) {
 void Tensor::FreeGrad() {
     oe_mem_free(Device, gradBuf);
     gradBuf = 0;
+    gradKnownZero = false;
 }
 
 std::string Tensor::ZeroGrad() {
     if (gradBuf == 0) return "";
     GG_TRY(oe_memset_u32(Device, gradBuf, 0, (uint64_t)Numel(), 0), "oe_memset_u32");
+    gradKnownZero = true;
     return "";
 }
 

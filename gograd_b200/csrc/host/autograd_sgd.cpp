@@ -173,6 +173,8 @@ void SGD::run(float maxNorm) {
     if (!e.empty()) throw std::runtime_error(e);
     if (StepCount >= INT32_MAX) throw std::runtime_error("autograd: SGD step count overflow");
     if (!std::isfinite(Engine.GradScale) || !(Engine.GradScale > 0)) throw std::runtime_error("autograd: invalid gradient scale");
+    if (Engine.ZeroGradInStep)
+        throw std::runtime_error("autograd: SGD.ZeroGrad releases its gradients; zeroing them inside Step would update parameters that are skipped today");
     StepCount++;
     if (!(e = refreshPlan()).empty()) throw std::runtime_error(e);
     int rc = oe_plan_set_grad_scale(plan_, &Engine.GradScale);

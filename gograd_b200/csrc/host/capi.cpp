@@ -157,8 +157,11 @@ int gg_tensor_shadow_current(const gg_tensor* t) { return t && t->t->ShadowCurre
 
 uint64_t gg_tensor_address(const gg_tensor* t, int32_t which) {
     if (!t) return 0;
+    if (which == 1) t->t->MarkGradWritten();  // whoever asks for the raw gradient address may write through it
     return which == 0 ? t->t->buf : which == 1 ? t->t->gradBuf : t->t->bf16Buf;
 }
+
+int gg_tensor_grad_known_zero(const gg_tensor* t) { return t && t->t->gradBuf != 0 && t->t->gradKnownZero ? 1 : 0; }
 
 uint64_t gg_tensor_shadow_lease(gg_tensor* t) { return t ? t->t->AcquireShadowLease() : 0; }
 void gg_tensor_shadow_release(gg_tensor* t, uint64_t address) {
@@ -258,6 +261,14 @@ int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devfor
     EngineOptions& e = o->adamw ? o->adamw->Engine : o->sgd->Engine;
     e.WriteShadow = write_shadow != 0;
     e.ClipDevForm = clip_devform != 0;
+    return 0;
+}
+
+int gg_opt_set_zero_grad_in_step(gg_optimizer* o, int32_t on) {
+    if (!o) return fail("optimizer is NULL");
+    if (on && !o->adamw)
+        return fail("autograd: SGD.ZeroGrad releases its gradients; zeroing them inside Step would update parameters that are skipped today");
+    (o->adamw ? o->adamw->Engine : o->sgd->Engine).ZeroGradInStep = on != 0;
     return 0;
 }
 

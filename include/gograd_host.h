@@ -69,6 +69,7 @@ OE_API int gg_tensor_grad_to_host(const gg_tensor* t, float* out);
 OE_API int gg_tensor_shadow_to_host(const gg_tensor* t, uint16_t* out);
 OE_API int gg_tensor_shadow_current(const gg_tensor* t);           /* 1 when the bf16 shadow matches the value */
 OE_API uint64_t gg_tensor_address(const gg_tensor* t, int32_t which); /* 0 value, 1 gradient, 2 shadow */
+OE_API int gg_tensor_grad_known_zero(const gg_tensor* t);          /* 1 while the gradient is known to hold zeros */
 /* bf16 shadow leases (autograd/cuda_autocast.go:77-94): a reader that keeps the shadow's address across an
  * optimizer step takes a lease; the step then writes a fresh buffer and the leased one stays valid until
  * released. gg_tensor_shadow_lease returns the leased device address (0 when there is no shadow). */
@@ -87,6 +88,10 @@ OE_API int gg_sgd_new(const char* const* names, gg_tensor* const* tensors, int32
 OE_API int gg_sgd_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n,
                              const gg_sgd_options* options, const gg_groups* groups, gg_optimizer** out);
 OE_API int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devform);
+/* AdamW only: Step stores zeros over every gradient it has read, and the next ZeroGrad launches nothing
+ * while no gradient was written since (ZeroGrad at the start of a group, autograd/training_loop.go:125-133).
+ * Refused for SGD, whose eager ZeroGrad makes gradients absent (autograd/sgd.go:231-246). */
+OE_API int gg_opt_set_zero_grad_in_step(gg_optimizer* o, int32_t on);
 /* Step and step_clipped read every gradient element as (float)(g * *scale) from now on (default 1):
  * the 1/groups factor of gradient accumulation folded into the pass that reads the gradients. */
 OE_API int gg_opt_set_grad_scale(gg_optimizer* o, const float* scale);

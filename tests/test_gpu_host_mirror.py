@@ -502,3 +502,50 @@ def test_accumulated_gradients_read_at_the_seed_scale(ag):
             opt.Close()
         for a, b in zip(*runs):
             assert np.array_equal(a, b), kind
+
+
+def test_step_zeroes_the_gradients_it_read_and_zero_grad_finds_nothing_to_do(ag):
+    """The loop around the optimizer calls ZeroGrad at the start of every group
+    (autograd/training_loop.go:125-133) and AdamW.ZeroGrad keeps the buffers and zeroes them
+    (autograd/nn.go:533-537). With zeroing folded into Step the gradients are zero when Step returns,
+    the following ZeroGrad launches nothing, results are unchanged, and a gradient written afterwards
+    is zeroed again the usual way. SGD refuses: its ZeroGrad makes gradients absent."""
+    import gograd_b200 as eng
+    rng = np.random.default_rng(41)
+    sizes = (1000, 7, 4096, 20001)
+    values = [rng.normal(0, .05, n).astype(np.float32) for n in sizes]
+    grads = [[rng.normal(0, .5, n).astype(np.float32) for n in sizes] for _ in range(3)]
+    runs = []
+    for fused in (False, True):
+        params = params_of(ag, [(f"p{i}", v) for i, v in enumerate(values)])
+        opt = ag.NewAdamW(params, 1e-2, 0.1)
+        if fused:
+            opt.SetZeroGradInStep(True)
+        for step in range(3):
+            opt.ZeroGrad()
+            for p, g in zip(params, grads[step]):
+                p.Value.set_grad(g)
+            assert not any(p.Value.grad_known_zero for p in params)
+            opt.StepClipped(1.0)
+            if fused:
+                assert all(p.Value.grad_known_zero for p in params)
+                assert all(float(np.abs(p.Value.grad_to_host()).max()) == 0.0 for p in params)
+                before = eng.launch_count()
+                opt.ZeroGrad()
+                assert eng.launch_count() == before, "nothing to zero: nothing launched"
+            else:
+                assert np.array_equal(params[0].Value.grad_to_host(), grads[step][0])
+        runs.append([p.Value.to_host() for p in params])
+        if fused:
+            params[2].Value.set_grad(grads[0][2])
+            before = eng.launch_count()
+            opt.ZeroGrad()
+            assert eng.launch_count() == before + 1 and float(np.abs(params[2].Value.grad_to_host()).max()) == 0.0
+            assert all(p.Value.grad_known_zero for p in params)
+        opt.Close()
+    for a, b in zip(*runs):
+        assert np.array_equal(a, b)
+    sgd = ag.NewSGD(params_of(ag, [("w", values[0])]), ag.SGDOptions(LR=0.1))
+    with pytest.raises(ag.HostError, match="releases its gradients"):
+        sgd.SetZeroGradInStep(True)
+    sgd.Close()
