@@ -400,6 +400,103 @@ class GradAccumulator:
         lib().gg_accumulator_reset(C.byref(self._a))
 
 
+class _TrainingLoop(C.Structure):
+    NEXT = C.CFUNCTYPE(C.c_int, C.c_void_p)
+    POSITION = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_char), C.c_int32, C.POINTER(C.c_int32))
+    STEP = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_float), C.POINTER(C.c_double))
+    REPORT = C.CFUNCTYPE(None, C.c_void_p, C.c_int32, C.POINTER(C.c_double))
+    SAVE = C.CFUNCTYPE(C.c_int, C.c_void_p, C.POINTER(C.c_char), C.c_int32)
+    _fields_ = [("user", C.c_void_p), ("next", NEXT), ("next_epoch", NEXT), ("position", POSITION), ("step", STEP),
+                ("report", REPORT), ("save", SAVE), ("optimizer", C.c_void_p), ("schedule", C.c_void_p),
+                ("updates", C.c_int32), ("applied", C.c_int32), ("accumulate", C.c_int32), ("log_every", C.c_int32)]
+
+
+class LoopCancelled(Exception):
+    """Raise from a reader or a step to stop the run the way a cancelled context does."""
+
+
+class LoopStopped(HostError):
+    """TrainingLoop.Run ended on a cancellation (after Save has run)."""
+
+
+class TrainingLoop:
+    """autograd.TrainingLoop (autograd/training_loop.go:53-214) over the host library.
+
+    reader: object with next() -> batch (raise StopIteration at the end of an epoch) and next_epoch();
+    sampler: object with marshal() -> bytes, or None; step(batch, seed) -> loss, back-propagating with
+    the seed 1/accumulate; report(update, loss) and save(savepoint: Optional[bytes]) are optional.
+    Exceptions of the callbacks end the run; LoopCancelled is the cancellation."""
+
+    END_OF_EPOCH, CANCELLED, FAILED = 1, 2, 3
+
+    def __init__(self, reader, optimizer, step, sampler=None, schedule: Optional["OneCycle"] = None, updates: int = 0,
+                 applied: int = 0, accumulate: int = 0, log_every: int = 0, report=None, save=None):
+        self.reader, self.optimizer, self.step, self.sampler, self.schedule = reader, optimizer, step, sampler, schedule
+        self.Updates, self.Applied, self.Accumulate, self.LogEvery = updates, applied, accumulate, log_every
+        self.report, self.save = report, save
+        self._batch = None
+
+    def _guard(self, fn, cancelled=2, failed=3):
+        try:
+            return fn() or 0
+        except LoopCancelled as e:
+            lib().gg_loop_set_error((str(e) or "context canceled").encode())
+            return cancelled
+        except Exception as e:  # any other error ends the run and is reported by it
+            lib().gg_loop_set_error(f"{type(e).__name__}: {e}".encode())
+            return failed
+
+    def Run(self) -> None:
+        T = _TrainingLoop
+
+        def do_next(_user):
+            def body():
+                try:
+                    self._batch = self.reader.next()
+                except StopIteration:
+                    return self.END_OF_EPOCH
+            return self._guard(body)
+
+        def do_next_epoch(_user):
+            return self._guard(lambda: self.reader.next_epoch(), failed=1, cancelled=1)
+
+        def do_position(_user, out, capacity, length):
+            def body():
+                payload = bytes(self.sampler.marshal())
+                if len(payload) > capacity:
+                    raise ValueError("sampler position too large")
+                C.memmove(out, payload, len(payload))
+                length[0] = len(payload)
+            return self._guard(body, failed=1, cancelled=1)
+
+        def do_step(_user, seed, loss):
+            def body():
+                loss[0] = float(self.step(self._batch, np.float32(seed[0])))
+            return self._guard(body)
+
+        def do_report(_user, update, loss):
+            self.report(update, loss[0])
+
+        def do_save(_user, savepoint, length):
+            return self._guard(lambda: self.save(C.string_at(savepoint, length) if savepoint else None), failed=1,
+                               cancelled=1)
+
+        keep = [T.NEXT(do_next) if self.reader is not None else T.NEXT(),
+                T.NEXT(do_next_epoch) if self.reader is not None else T.NEXT(),
+                T.POSITION(do_position) if self.sampler is not None else T.POSITION(),
+                T.STEP(do_step) if self.step is not None else T.STEP(),
+                T.REPORT(do_report) if self.report is not None else T.REPORT(),
+                T.SAVE(do_save) if self.save is not None else T.SAVE()]
+        c = T(None, *keep, self.optimizer._h if self.optimizer is not None else None,
+              C.cast(C.pointer(self.schedule._c), C.c_void_p) if self.schedule is not None else None,
+              self.Updates, self.Applied, self.Accumulate, self.LogEvery)
+        rc = lib().gg_training_loop_run(C.byref(c))
+        self.Applied = c.applied
+        if rc == self.CANCELLED:
+            raise LoopStopped(lib().gg_last_error().decode("utf-8", "replace"))
+        _check(rc)
+
+
 class OneCycle:
     def __init__(self, max_lr: float, total: int, pct_start: float):
         self._c = _OneCycle()

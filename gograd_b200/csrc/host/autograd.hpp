@@ -19,6 +19,7 @@
 #define GG_AUTOGRAD_HPP
 
 #include <cstdint>
+#include <functional>
 #include <map>
 #include <memory>
 #include <stdexcept>
@@ -302,6 +303,26 @@ struct OneCycle {
     void Step(CheckpointOptimizer& o);
 };
 std::string validateOneCycle(const OneCycle& c);
+
+// TrainingLoop (autograd/training_loop.go:53-214): the caller of ZeroGrad / Step / Schedule.Step.
+// Reader, sampler, step, report and save are the caller's; they arrive as functions. A reader or a
+// step reports how it ended with a status, the way the Go code tells io.EOF and context
+// cancellation apart from other errors.
+struct TrainingLoop {
+    enum Status { Batch = 0, EndOfEpoch = 1, Cancelled = 2, Failed = 3 };
+    std::function<int(std::string* err)> Next;                               // Reader.Next: a Status
+    std::function<std::string()> NextEpoch;                                  // Reader.NextEpoch
+    std::function<std::string(std::string* payload)> Position;               // Sampler.MarshalBinary; empty = no sampler
+    std::function<int(float seed, double* loss, std::string* err)> Step;     // one micro-batch, backward seeded with seed: 0, Cancelled or Failed
+    std::function<void(int update, double loss)> Report;                     // optional
+    std::function<std::string(const std::string* savepoint)> Save;           // optional; savepoint may be null
+    CheckpointOptimizer* Optimizer = nullptr;
+    OneCycle* Schedule = nullptr;
+    int Updates = 0, Applied = 0, Accumulate = 0, LogEvery = 0;
+    // "" when the planned updates were applied (and saved); otherwise what stopped the run, with
+    // *cancelled telling a cancellation (after which Save has run) from a failure.
+    std::string Run(bool* cancelled);
+};
 
 // Entries / metadata of the checkpoint layout (autograd/optimizer_state.go:142-160,
 // autograd/sgd_state.go:150-194, autograd/optimizer.go:85-120).

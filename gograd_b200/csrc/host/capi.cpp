@@ -453,6 +453,73 @@ static void from_cycle(const OneCycle& o, gg_onecycle* c) {
     c->step_count = o.StepCount;
 }
 
+namespace {
+thread_local std::string t_loop_error;  // what a loop callback left with gg_loop_set_error
+std::string take_loop_error(const char* fallback) {
+    std::string e = t_loop_error.empty() ? fallback : t_loop_error;
+    t_loop_error.clear();
+    return e;
+}
+}  // namespace
+
+void gg_loop_set_error(const char* message) { t_loop_error = message ? message : ""; }
+
+int gg_training_loop_run(gg_training_loop* c) {
+    if (!c) return fail("loop is NULL");
+    TrainingLoop loop;
+    if (c->next)
+        loop.Next = [c](std::string* err) {
+            int status = c->next(c->user);
+            if (status != 0) *err = take_loop_error(status == GG_LOOP_CANCELLED ? "context canceled" : "autograd: the reader failed");
+            return status;
+        };
+    if (c->next_epoch)
+        loop.NextEpoch = [c]() -> std::string { return c->next_epoch(c->user) == 0 ? "" : take_loop_error("autograd: the reader could not start an epoch"); };
+    if (c->position)
+        loop.Position = [c](std::string* payload) -> std::string {
+            std::vector<char> buf(1 << 16);
+            int32_t length = 0;
+            if (c->position(c->user, buf.data(), (int32_t)buf.size(), &length) != 0 || length < 0 || length > (int32_t)buf.size())
+                return take_loop_error("autograd: the sampler could not save its position");
+            payload->assign(buf.data(), (size_t)length);
+            return "";
+        };
+    if (c->step)
+        loop.Step = [c](float seed, double* loss, std::string* err) {
+            int status = c->step(c->user, &seed, loss);
+            if (status != 0) *err = take_loop_error(status == GG_LOOP_CANCELLED ? "context canceled" : "autograd: the step failed");
+            return status;
+        };
+    if (c->report) loop.Report = [c](int update, double loss) { c->report(c->user, update, &loss); };
+    if (c->save)
+        loop.Save = [c](const std::string* savepoint) -> std::string {
+            int rc = savepoint ? c->save(c->user, savepoint->data(), (int32_t)savepoint->size()) : c->save(c->user, nullptr, 0);
+            return rc == 0 ? "" : take_loop_error("autograd: saving failed");
+        };
+    loop.Optimizer = c->optimizer ? c->optimizer->base() : nullptr;
+    OneCycle cycle;
+    if (c->schedule) {
+        cycle = to_cycle(c->schedule);
+        loop.Schedule = &cycle;
+    }
+    loop.Updates = c->updates;
+    loop.Applied = c->applied;
+    loop.Accumulate = c->accumulate;
+    loop.LogEvery = c->log_every;
+    bool cancelled = false;
+    std::string e;
+    try {
+        e = loop.Run(&cancelled);
+    } catch (const std::exception& ex) {
+        e = ex.what();
+    }
+    c->applied = loop.Applied;
+    if (c->schedule) from_cycle(cycle, c->schedule);
+    if (e.empty()) return 0;
+    fail(e);
+    return cancelled ? GG_LOOP_CANCELLED : 1;
+}
+
 int gg_accumulator_new(int32_t groups, gg_accumulator* out) {
     if (!out) return fail("accumulator is NULL");
     GradAccumulator a;

@@ -133,6 +133,36 @@ OE_API int gg_accumulator_new(int32_t groups, gg_accumulator* out);
 OE_API int gg_accumulator_micro_batch(gg_accumulator* a, float* seed_out, int32_t* complete_out);
 OE_API void gg_accumulator_reset(gg_accumulator* a);
 
+/* ---- the loop that calls the optimizer (TrainingLoop.Run, autograd/training_loop.go:53-214) ----
+ * Reader, sampler, step, report and save belong to the caller and arrive as callbacks (user is passed
+ * back to each). Statuses of next and step: 0 = a batch was read / the micro-batch was back-propagated,
+ * GG_LOOP_END_OF_EPOCH (next only, io.EOF), GG_LOOP_CANCELLED (a context error: the run stops, unfinished
+ * gradients are dropped and save receives the starting position of the unfinished group),
+ * GG_LOOP_FAILED (any other error: the run returns it without saving); on a non-zero status the
+ * callback may leave a message with gg_loop_set_error. step back-propagates with the seed it is given
+ * (1/accumulate, GradAccumulator.Backward). position writes the sampler's payload (at most capacity
+ * bytes) and its length; NULL = no sampler. report and save may be NULL; save's savepoint is NULL when
+ * there is nothing to rewind. schedule may be NULL. applied is advanced by the run.
+ * Returns 0 when the planned updates were applied, GG_LOOP_CANCELLED after a cancellation, 1 for any
+ * other error (gg_last_error). */
+#define GG_LOOP_END_OF_EPOCH 1
+#define GG_LOOP_CANCELLED 2
+#define GG_LOOP_FAILED 3
+typedef struct gg_training_loop {
+    void* user;
+    int (*next)(void* user);
+    int (*next_epoch)(void* user);
+    int (*position)(void* user, char* out, int32_t capacity, int32_t* length);
+    int (*step)(void* user, const float* seed, double* loss);
+    void (*report)(void* user, int32_t update, const double* loss);
+    int (*save)(void* user, const char* savepoint, int32_t length);
+    gg_optimizer* optimizer;
+    gg_onecycle* schedule;
+    int32_t updates, applied, accumulate, log_every;
+} gg_training_loop;
+OE_API int gg_training_loop_run(gg_training_loop* loop);
+OE_API void gg_loop_set_error(const char* message);
+
 /* ---- schedule and training checkpoint (autograd/nn.go:539-571, autograd/training_checkpoint.go) ---- */
 OE_API int gg_onecycle_new(const double* max_lr, int32_t total, const double* pct_start, gg_onecycle* out);
 OE_API int gg_onecycle_lr(const gg_onecycle* c, double* out);
