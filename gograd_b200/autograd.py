@@ -316,6 +316,17 @@ class SGD(_Optimizer):
         """(momentum buffer, initialised flag) of one parameter."""
         return self._state(index, 2)
 
+    def PrepareGraph(self) -> None:
+        _check(lib().gg_opt_prepare_graph(self._h))
+
+    def StepCaptured(self) -> None:
+        _check(lib().gg_opt_step_captured(self._h))
+
+    def GraphStepCount(self) -> int:
+        out = C.c_int32()
+        _check(lib().gg_opt_graph_step_count(self._h, C.byref(out)))
+        return out.value
+
 
 def NewAdamW(params: Sequence[Parameter], lr: float, decay: float) -> AdamW:
     names, handles, n = _param_arrays(params)

@@ -243,10 +243,16 @@ class SGD : public CheckpointOptimizer {
     ~SGD() override;
     void Step() override;
     void StepClipped(float maxNorm);
-    void ZeroGrad() override;  // eager: gradients become absent (set-to-none), autograd/sgd.go:231-246
+    // Eager: gradients become absent (set-to-none). Once prepared for graphs the buffers are kept
+    // and zeroed, since a replay needs stable addresses (autograd/sgd.go:228-246).
+    void ZeroGrad() override;
     float LearningRate() const override { return LR; }
     void SetLearningRate(float lr) override;
     void Close() override;
+    std::string PrepareGraph();       // autograd/cuda_sgd.go:99-115
+    std::string GraphStepCount(int* out);
+    std::string SyncGraphStepCount();
+    void StepCaptured();              // the capture branch of Step (autograd/sgd.go:167-172)
     SGDOptions config() const;
     std::string State(SGDState* out);
     std::string LoadState(const SGDState& state);
@@ -261,6 +267,7 @@ class SGD : public CheckpointOptimizer {
    private:
     SGDOptions options_;
     std::vector<uint64_t> bufferGPU_, initializedGPU_;
+    uint64_t graphStep_ = 0;
     std::vector<ParameterGroup> groups_;
     std::vector<int> groupOf_;
     oe_plan* plan_ = nullptr;
@@ -270,7 +277,7 @@ class SGD : public CheckpointOptimizer {
     std::string deviceStorage(std::vector<uint64_t>* buffers, std::vector<uint64_t>* flags);
     void freeStorage(std::vector<uint64_t>& buffers, std::vector<uint64_t>& flags);
     std::string refreshPlan();
-    void run(float maxNorm);
+    void run(float maxNorm, bool captured = false);
 };
 
 // ClipGradNorm for CUDA parameters (autograd/nn.go:310-317 + autograd/cuda_clip.go:114-134): the

@@ -108,6 +108,8 @@ void SGD::Close() {
     oe_plan_destroy(plan_);
     plan_ = nullptr;
     freeStorage(bufferGPU_, initializedGPU_);
+    if (graphStep_ != 0) oe_mem_free(device_, graphStep_);
+    graphStep_ = 0;
     closed_ = true;
 }
 
@@ -168,14 +170,20 @@ std::string SGD::refreshPlan() {
     return rc == 0 ? "" : engine_error("optimizer plan", rc);
 }
 
-void SGD::run(float maxNorm) {
+void SGD::run(float maxNorm, bool captured) {
     std::string e = validateOpen();
     if (!e.empty()) throw std::runtime_error(e);
-    if (StepCount >= INT32_MAX) throw std::runtime_error("autograd: SGD step count overflow");
+    if (captured && graphStep_ == 0) throw std::runtime_error("autograd: call SGD.PrepareGraph before capture");
     if (!std::isfinite(Engine.GradScale) || !(Engine.GradScale > 0)) throw std::runtime_error("autograd: invalid gradient scale");
-    if (Engine.ZeroGradInStep)
+    // Zeroing inside Step equals ZeroGrad only where ZeroGrad zeroes: once prepared for graphs. Eager
+    // ZeroGrad makes gradients absent, and a zeroed buffer is not an absent one.
+    if (Engine.ZeroGradInStep && graphStep_ == 0)
         throw std::runtime_error("autograd: SGD.ZeroGrad releases its gradients; zeroing them inside Step would update parameters that are skipped today");
-    StepCount++;
+    if (!captured) {
+        if (graphStep_ != 0 && !(e = SyncGraphStepCount()).empty()) throw std::runtime_error(e);
+        if (StepCount >= INT32_MAX) throw std::runtime_error("autograd: SGD step count overflow");
+        StepCount++;
+    }
     if (!(e = refreshPlan()).empty()) throw std::runtime_error(e);
     int rc = oe_plan_set_grad_scale(plan_, &Engine.GradScale);
     if (rc != 0) throw std::runtime_error(engine_error("oe_plan_set_grad_scale", rc));
@@ -186,24 +194,66 @@ void SGD::run(float maxNorm) {
     hp.dampening = options_.Dampening;
     hp.max_norm = maxNorm;
     hp.flags = (options_.Nesterov ? OE_NESTEROV : 0u) | (options_.Maximize ? OE_MAXIMIZE : 0u) |
-               (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u);
+               (Engine.WriteShadow ? OE_WRITE_SHADOW : 0u) | (Engine.ClipDevForm ? OE_CLIP_DEVFORM : 0u) |
+               (Engine.ZeroGradInStep ? OE_ZERO_GRAD : 0u);
+    if (captured) hp.step_dev = graphStep_;  // the launch advances the device counter (sgd_step, autograd/cuda_sgd.go:67-70)
     if (maxNorm > 0 && (rc = oe_grad_norm(plan_, 0, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_grad_norm", rc));
     if ((rc = oe_sgd_step(plan_, &hp, Engine.Stream)) != 0) throw std::runtime_error(engine_error("oe_sgd_step", rc));
+    if (captured) return;  // a captured step changes no host state (autograd/cuda_sgd.go:94-96)
     for (Parameter& p : Params) {
         Tensor& t = *p.Value;
         if (t.gradBuf == 0) continue;
         t.version++;  // autograd/cuda_sgd.go:94-96 invalidates here; the engine rewrote the shadow instead
         if (Engine.WriteShadow && t.bf16Buf != 0) t.bf16Version = t.version;
+        if (Engine.ZeroGradInStep) t.gradKnownZero = true;
     }
+    if (graphStep_ != 0 && !(e = PrepareGraph()).empty()) throw std::runtime_error(e);
 }
 
 void SGD::Step() { run(0.0f); }
 void SGD::StepClipped(float maxNorm) { run(maxNorm); }
+void SGD::StepCaptured() { run(0.0f, true); }
 
 void SGD::ZeroGrad() {
     std::string e = validateOpen();
     if (!e.empty()) throw std::runtime_error(e);
-    for (Parameter& p : Params) p.Value->FreeGrad();  // set-to-none (autograd/sgd.go:231-246)
+    if (graphStep_ != 0) {  // prepared for graphs: keep the buffers, zero them (autograd/sgd.go:236-239)
+        for (Parameter& p : Params) {
+            if (p.Value->gradBuf == 0 || p.Value->gradKnownZero) continue;
+            if (!(e = p.Value->ZeroGrad()).empty()) throw std::runtime_error(e);
+        }
+        return;
+    }
+    for (Parameter& p : Params) p.Value->FreeGrad();  // set-to-none (autograd/sgd.go:240-245)
+}
+
+std::string SGD::PrepareGraph() {
+    std::string e = validateOpen();
+    if (!e.empty()) return e;
+    if (Params.empty()) return "cuda: unavailable";
+    int rc;
+    if (graphStep_ == 0 && (rc = oe_mem_alloc(device_, 4, &graphStep_)) != 0) return engine_error("oe_mem_alloc", rc);
+    int32_t step = (int32_t)StepCount;
+    if ((rc = oe_memcpy_h2d(device_, graphStep_, &step, 4, Engine.Stream)) != 0) return engine_error("oe_memcpy_h2d", rc);
+    if ((rc = oe_stream_sync(device_, Engine.Stream)) != 0) return engine_error("oe_stream_sync", rc);
+    return "";
+}
+
+std::string SGD::GraphStepCount(int* out) {
+    if (closed_ || graphStep_ == 0) return "cuda: unavailable";
+    int32_t step = 0;
+    int rc;
+    if ((rc = oe_memcpy_d2h(device_, &step, graphStep_, 4, Engine.Stream)) != 0) return engine_error("oe_memcpy_d2h", rc);
+    if ((rc = oe_stream_sync(device_, Engine.Stream)) != 0) return engine_error("oe_stream_sync", rc);
+    *out = step;
+    return "";
+}
+
+std::string SGD::SyncGraphStepCount() {
+    int step = 0;
+    std::string e = GraphStepCount(&step);
+    if (e.empty()) StepCount = step;
+    return e;
 }
 
 // ---- state (autograd/sgd_state.go) ------------------------------------------------------
@@ -212,6 +262,7 @@ std::string SGD::State(SGDState* out) {
     if (!e.empty()) return e;
     SGDState s;
     s.StepCount = StepCount;
+    if (graphStep_ != 0 && !(e = GraphStepCount(&s.StepCount)).empty()) return e;  // autograd/sgd_state.go:31-37
     s.Options = config();
     s.Initialized.assign(Params.size(), false);
     s.Buffers.resize(Params.size());
@@ -293,6 +344,7 @@ std::string SGD::LoadState(const SGDState& s) {
         for (int index : groups_[g].Indexes) groupOf_[index] = (int)g;
     options_.WeightDecay = groups_[0].WeightDecay;
     StepCount = s.StepCount;
+    if (graphStep_ != 0) return PrepareGraph();  // autograd/sgd_state.go:145-147
     return "";
 }
 

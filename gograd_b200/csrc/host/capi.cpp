@@ -266,8 +266,8 @@ int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devfor
 
 int gg_opt_set_zero_grad_in_step(gg_optimizer* o, int32_t on) {
     if (!o) return fail("optimizer is NULL");
-    if (on && !o->adamw)
-        return fail("autograd: SGD.ZeroGrad releases its gradients; zeroing them inside Step would update parameters that are skipped today");
+    // For SGD the option only holds once the optimizer is prepared for graphs, where ZeroGrad zeroes
+    // instead of releasing; Step checks that.
     (o->adamw ? o->adamw->Engine : o->sgd->Engine).ZeroGradInStep = on != 0;
     return 0;
 }
@@ -372,26 +372,47 @@ int gg_opt_load(gg_optimizer* o, const char* path) {
     return guarded([&]() { return o->adamw ? o->adamw->LoadSafeTensors(path) : o->sgd->LoadSafeTensors(path); });
 }
 
-int gg_adamw_prepare_graph(gg_optimizer* o) {
-    return guarded([&]() -> std::string { return o->adamw ? o->adamw->PrepareGraph() : "not an AdamW optimizer"; });
+int gg_opt_prepare_graph(gg_optimizer* o) {
+    return guarded([&]() -> std::string {
+        if (!o) return "optimizer is NULL";
+        return o->adamw ? o->adamw->PrepareGraph() : o->sgd->PrepareGraph();
+    });
 }
 
-int gg_adamw_step_captured(gg_optimizer* o) {
+int gg_opt_step_captured(gg_optimizer* o) {
     return guarded([&]() -> std::string {
-        if (!o->adamw) return "not an AdamW optimizer";
-        o->adamw->StepCaptured();
+        if (!o) return "optimizer is NULL";
+        if (o->adamw)
+            o->adamw->StepCaptured();
+        else
+            o->sgd->StepCaptured();
         return "";
     });
 }
 
-int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out) {
+int gg_opt_graph_step_count(gg_optimizer* o, int32_t* out) {
     return guarded([&]() -> std::string {
-        if (!o->adamw) return "not an AdamW optimizer";
+        if (!o || !out) return "NULL argument";
         int step = 0;
-        std::string e = o->adamw->GraphStepCount(&step);
+        std::string e = o->adamw ? o->adamw->GraphStepCount(&step) : o->sgd->GraphStepCount(&step);
         *out = step;
         return e;
     });
+}
+
+int gg_adamw_prepare_graph(gg_optimizer* o) {
+    if (!o || !o->adamw) return fail("not an AdamW optimizer");
+    return gg_opt_prepare_graph(o);
+}
+
+int gg_adamw_step_captured(gg_optimizer* o) {
+    if (!o || !o->adamw) return fail("not an AdamW optimizer");
+    return gg_opt_step_captured(o);
+}
+
+int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out) {
+    if (!o || !o->adamw) return fail("not an AdamW optimizer");
+    return gg_opt_graph_step_count(o, out);
 }
 
 int gg_partition_parameters(const char* const* names, gg_tensor* const* tensors, const char* const* labels, int32_t n,

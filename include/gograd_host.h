@@ -88,9 +88,10 @@ OE_API int gg_sgd_new(const char* const* names, gg_tensor* const* tensors, int32
 OE_API int gg_sgd_new_groups(const char* const* names, gg_tensor* const* tensors, int32_t n,
                              const gg_sgd_options* options, const gg_groups* groups, gg_optimizer** out);
 OE_API int gg_opt_set_engine(gg_optimizer* o, int32_t write_shadow, int32_t clip_devform);
-/* AdamW only: Step stores zeros over every gradient it has read, and the next ZeroGrad launches nothing
- * while no gradient was written since (ZeroGrad at the start of a group, autograd/training_loop.go:125-133).
- * Refused for SGD, whose eager ZeroGrad makes gradients absent (autograd/sgd.go:231-246). */
+/* Step stores zeros over every gradient it has read, and the next ZeroGrad launches nothing while no
+ * gradient was written since (ZeroGrad at the start of a group, autograd/training_loop.go:125-133).
+ * An eager SGD refuses to step with it: its ZeroGrad makes gradients absent (autograd/sgd.go:231-246),
+ * and a zeroed buffer is not an absent one; once prepared for graphs SGD zeroes too and accepts it. */
 OE_API int gg_opt_set_zero_grad_in_step(gg_optimizer* o, int32_t on);
 /* Step and step_clipped read every gradient element as (float)(g * *scale) from now on (default 1):
  * the 1/groups factor of gradient accumulation folded into the pass that reads the gradients. */
@@ -110,9 +111,12 @@ OE_API int gg_opt_state(gg_optimizer* o, int32_t index, int32_t which, float* ou
 OE_API int gg_opt_group_scale(const gg_optimizer* o, int32_t index, float* step_size, float* decay); /* groupScale */
 OE_API int gg_opt_save(gg_optimizer* o, const char* path);              /* SaveSafeTensors */
 OE_API int gg_opt_load(gg_optimizer* o, const char* path);              /* LoadSafeTensors */
-OE_API int gg_adamw_prepare_graph(gg_optimizer* o);                     /* PrepareGraph */
-OE_API int gg_adamw_step_captured(gg_optimizer* o);                     /* the capture branch of Step */
-OE_API int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out);    /* GraphStepCount */
+OE_API int gg_opt_prepare_graph(gg_optimizer* o);                       /* AdamW.PrepareGraph / SGD.PrepareGraph */
+OE_API int gg_opt_step_captured(gg_optimizer* o);                       /* the capture branch of Step */
+OE_API int gg_opt_graph_step_count(gg_optimizer* o, int32_t* out);      /* GraphStepCount */
+OE_API int gg_adamw_prepare_graph(gg_optimizer* o);                     /* the three above, AdamW only */
+OE_API int gg_adamw_step_captured(gg_optimizer* o);
+OE_API int gg_adamw_graph_step_count(gg_optimizer* o, int32_t* out);
 
 /* PartitionParameters (autograd/param_groups.go:63-102): labels[i] is what the caller's assign(name)
  * returns for parameter i. Writes the resulting specs, in order of first appearance of each label, as

@@ -545,7 +545,67 @@ def test_step_zeroes_the_gradients_it_read_and_zero_grad_finds_nothing_to_do(ag)
         opt.Close()
     for a, b in zip(*runs):
         assert np.array_equal(a, b)
-    sgd = ag.NewSGD(params_of(ag, [("w", values[0])]), ag.SGDOptions(LR=0.1))
+    sgd_params = params_of(ag, [("w", values[0])])
+    sgd = ag.NewSGD(sgd_params, ag.SGDOptions(LR=0.1))
+    sgd.SetZeroGradInStep(True)
+    sgd_params[0].Value.set_grad(grads[0][0])
     with pytest.raises(ag.HostError, match="releases its gradients"):
-        sgd.SetZeroGradInStep(True)
+        sgd.Step()
+    assert sgd.StepCount == 0 and np.array_equal(sgd_params[0].Value.to_host(), values[0])
     sgd.Close()
+
+
+def test_sgd_captured_steps_match_eager_and_sync_the_counter(ag):
+    """autograd/sgd_test.go:268-333: three captured steps over a stable gradient equal three eager
+    steps (weights and momentum), State reads the device counter, an eager step afterwards syncs the
+    host count and invalidates the bf16 shadow. Prepared for graphs, ZeroGrad keeps the buffers and
+    zeroes them (autograd/sgd.go:228-246), and Step may do that zeroing itself."""
+    import gograd_b200 as eng
+    initial = np.float32([.3, -.7, .2, .4])
+    grad = np.float32([.2, -.3, .1, .4])
+    options = ag.SGDOptions(LR=.03, Momentum=.9, Dampening=.2, WeightDecay=.1)
+    p, q = ag.Parameter("weight", ag.Tensor(initial, [2, 2])), ag.Parameter("weight", ag.Tensor(initial, [2, 2]))
+    o, eager = ag.NewSGD([p], options), ag.NewSGD([q], options)
+    with pytest.raises(ag.HostError, match="call SGD.PrepareGraph before capture"):
+        o.StepCaptured()
+    p.Value.set_grad(grad)
+    o.PrepareGraph()
+    for _ in range(3):
+        o.StepCaptured()
+    for _ in range(3):
+        eager.ZeroGrad()
+        assert not q.Value.has_grad, "eager ZeroGrad makes the gradient absent"
+        q.Value.set_grad(grad)
+        eager.Step()
+    assert o.GraphStepCount() == 3
+    assert o.StepCount == 0, "a captured step changes no host state"
+    assert np.array_equal(p.Value.to_host(), q.Value.to_host())
+    left, right = o.Buffer(0), eager.Buffer(0)
+    assert left[1] and right[1] and np.array_equal(left[0], right[0])
+    # graph mode: ZeroGrad keeps the buffer and zeroes it
+    o.ZeroGrad()
+    assert p.Value.has_grad and float(np.abs(p.Value.grad_to_host()).max()) == 0.0
+    # an eager step after replay syncs the host count and invalidates the shadow
+    o.SetEngine(write_shadow=True)
+    p.Value.set_grad(grad)
+    o.Step()
+    assert o.StepCount == 4 and o.GraphStepCount() == 4 and p.Value.shadow_current
+    o.SetEngine(write_shadow=False)
+    p.Value.set_grad(grad)
+    o.Step()
+    assert o.StepCount == 5 and not p.Value.shadow_current, "a step that does not rewrite the shadow invalidates it"
+    # zeroing folded into Step is accepted once prepared for graphs, refused by an eager SGD
+    o.SetZeroGradInStep(True)
+    p.Value.set_grad(grad)
+    o.Step()
+    assert p.Value.grad_known_zero and float(np.abs(p.Value.grad_to_host()).max()) == 0.0
+    before = eng.launch_count()
+    o.ZeroGrad()
+    assert eng.launch_count() == before and p.Value.has_grad
+    eager.SetZeroGradInStep(True)
+    q.Value.set_grad(grad)
+    with pytest.raises(ag.HostError, match="releases its gradients"):
+        eager.Step()
+    assert eager.StepCount == 3
+    o.Close()
+    eager.Close()
