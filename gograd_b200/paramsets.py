@@ -117,6 +117,16 @@ def gpt() -> ParamSet:
                     notes="tied embedding; 109,630,464 parameters from the listed tensors")
 
 
+def gpt_sgd() -> ParamSet:
+    """The GPT-style tensors under SGD with momentum: a mid-size streaming case of the SGD kernel
+    (larger than L2, small enough to profile), not one of the reference's configurations."""
+    base = gpt()
+    return ParamSet("gpt_sgd", "SGD with momentum over the GPT-style parameter set", "sgd", base.params,
+                    [GroupSpec("decay", 1.0, 5e-4), GroupSpec("no_decay", 1.0, 0.0)],
+                    dict(lr=0.05, momentum=0.9, dampening=0.0, nesterov=0, maximize=0),
+                    grad_std=0.01, grad_seed=5, steps=50)
+
+
 def _llama(key, title, d, layers, kv_dim, ffn, vocab, seed, steps, beta2):
     params = [ParamSpec("embed_tokens.weight", (vocab, d))]
     for l in range(layers):
@@ -144,8 +154,8 @@ def llama8b() -> ParamSet:
                   4096, 32, 1024, 14336, 128256, seed=4, steps=10, beta2=0.95)
 
 
-REGISTRY = {"mlp": mlp, "cnn": cnn, "gpt": gpt, "llama1b": llama1b, "llama8b": llama8b}
-EXPECTED_NUMEL = {"mlp": 203_530, "cnn": 114_186, "gpt": 109_630_464, "llama1b": 1_345_423_360,
+REGISTRY = {"mlp": mlp, "cnn": cnn, "gpt": gpt, "gpt_sgd": gpt_sgd, "llama1b": llama1b, "llama8b": llama8b}
+EXPECTED_NUMEL = {"mlp": 203_530, "cnn": 114_186, "gpt": 109_630_464, "gpt_sgd": 109_630_464, "llama1b": 1_345_423_360,
                   "llama8b": 8_030_261_248}
 
 
