@@ -67,6 +67,7 @@ PROTOTYPES = {
                                      C.POINTER(C.c_float), _u64]),
     "oe_peer_reduce_grads": (_i, [_plan, C.POINTER(_u64), _u32, _u64, _u64, _u64, C.POINTER(C.c_float), _u32, _u64]),
     "oe_adamw_step_peers": (_i, [_plan, C.POINTER(oe_adamw_hparams), C.POINTER(C.c_int64), _u32, _u64]),
+    "oe_sgd_step_peers": (_i, [_plan, C.POINTER(oe_sgd_hparams), C.POINTER(C.c_int64), _u32, _u64]),
     "oe_ipc_export": (_i, [_i, _u64, _vp, C.POINTER(_u64)]),
     "oe_ipc_import": (_i, [_i, _vp, C.POINTER(_u64)]),
     "oe_ipc_close": (_i, [_i, _u64]),

@@ -312,10 +312,10 @@ __device__ __forceinline__ void oe_sgd_one(float& p, float g, float& b, const oe
     p = __fsub_rn(p, __fmul_rn(lr, g));
 }
 
-template <bool SCALED>
+template <bool SCALED, bool PEERS>
 __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ tensors,
                                             const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
-                                            uint32_t chunk_elems, const oe_sgd_args& a) {
+                                            uint32_t chunk_elems, const oe_sgd_args& a, const oe_peer_set& peers) {
     oe_sgd_consts k;
     k.momentum = a.momentum;
     k.one_minus_damp = __fsub_rn(1.0f, a.dampening);
@@ -373,7 +373,7 @@ __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ te
                             uint2 packed;
                             packed.x = oe_bf16_rne(P[u].x) | (oe_bf16_rne(P[u].y) << 16);
                             packed.y = oe_bf16_rne(P[u].z) | (oe_bf16_rne(P[u].w) << 16);
-                            __stcs((uint2*)sh + i, packed);
+                            oe_store_shadow4<PEERS>(sh, i, packed, peers);
                         }
                         if (zero_grad) __stcs(g4 + i, make_float4(0.f, 0.f, 0.f, 0.f));
                     }
@@ -387,10 +387,12 @@ __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ te
             oe_sgd_one(pi, SCALED ? __fmul_rn(g[i], k.gscale) : g[i], bi, k, lr, decay, first);
             p[i] = pi;
             if (has_buf) b[i] = bi;
-            if (sh) sh[i] = (uint16_t)oe_bf16_rne(pi);
+            if (sh) oe_store_shadow1<PEERS>(sh, i, (uint16_t)oe_bf16_rne(pi), peers);
             if (zero_grad) g[i] = 0.0f;
         }
     }
+    // Peer stores must be performed before the kernel is reported complete to other devices.
+    if (PEERS) __threadfence_system();
     if (k.momentum > 0.0f) {
         // Every tensor that took part now has an initialised momentum buffer (the reference's
         // sgd_mark, one launch per tensor, autograd/cuda_sgd.go:14-16). Every CTA read the flags
@@ -418,10 +420,23 @@ oe_sgd_fused(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __re
     // Capture mode: the launch advances the device step counter (the reference's sgd_step,
     // autograd/cuda_sgd.go:18); nothing in the update reads it.
     if (a.step_dev != 0 && blockIdx.x == 0 && threadIdx.x == 0) *(int32_t*)a.step_dev += 1;
+    oe_peer_set none;
+    none.n = 0;
     if (a.grad_scale == 1.0f)
-        oe_sgd_body<false>(tensors, chunks, n_chunks, chunk_elems, a);
+        oe_sgd_body<false, false>(tensors, chunks, n_chunks, chunk_elems, a, none);
     else
-        oe_sgd_body<true>(tensors, chunks, n_chunks, chunk_elems, a);
+        oe_sgd_body<true, false>(tensors, chunks, n_chunks, chunk_elems, a, none);
+}
+
+// Sharded step: same update, shadow stored into every rank's shadow buffer.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
+oe_sgd_fused_peers(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
+                   uint32_t chunk_elems, oe_sgd_args a, const __grid_constant__ oe_peer_set peers) {
+    if (a.step_dev != 0 && blockIdx.x == 0 && threadIdx.x == 0) *(int32_t*)a.step_dev += 1;
+    if (a.grad_scale == 1.0f)
+        oe_sgd_body<false, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
+    else
+        oe_sgd_body<true, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
 }
 
 // ---------------------------------------------------------------------------------

@@ -51,7 +51,7 @@ int fail_cu(const oe_driver* d, CUresult r, const char* op) {
 
 struct KernelSet {
     CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
-    CUfunction adamw_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
+    CUfunction adamw_peers = nullptr, sgd_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
     CUfunction step_increment = nullptr, sgd = nullptr, sumsq = nullptr, norm_finalize = nullptr,
                scale = nullptr, zero = nullptr, cast = nullptr;
 };
@@ -67,7 +67,7 @@ struct DeviceCtx {
     int sm_count = 0;
     KernelSet k;
     int occ_adamw[4] = {0, 0, 0, 0};
-    int occ_adamw_peers = 0, occ_peer_reduce[3] = {0, 0, 0};
+    int occ_adamw_peers = 0, occ_sgd_peers = 0, occ_peer_reduce[3] = {0, 0, 0};
     int occ_sgd = 0, occ_sumsq = 0, occ_scale = 0, occ_zero = 0, occ_cast = 0;
 };
 
@@ -358,6 +358,7 @@ extern "C" int oe_init(int device) {
         {&dc->k.peer_reduce[1], "oe_peer_reduce_sumsq_n4", &dc->occ_peer_reduce[1]},
         {&dc->k.peer_reduce[2], "oe_peer_reduce_sumsq_n8", &dc->occ_peer_reduce[2]},
         {&dc->k.step_increment, "oe_step_increment", nullptr}, {&dc->k.sgd, "oe_sgd_fused", &dc->occ_sgd},
+        {&dc->k.sgd_peers, "oe_sgd_fused_peers", &dc->occ_sgd_peers},
         {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
         {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
         {&dc->k.zero, "oe_zero_grads", &dc->occ_zero},         {&dc->k.cast, "oe_cast_bf16", &dc->occ_cast},
@@ -675,7 +676,8 @@ extern "C" int oe_adamw_step_chunks(oe_plan* plan, const oe_adamw_hparams* hp, u
     return launch_adamw(d, plan, hp, (CUstream)stream, nullptr, first_chunk, n_chunks);
 }
 
-extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream) {
+namespace {
+int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_peer_set* peers) {
     if (!plan || !hp) return fail(OE_ERR_INVALID, "plan or hyper-parameters are NULL");
     // SGDOptions.validate (autograd/sgd.go:21-31)
     for (float v : {hp->lr, hp->momentum, hp->dampening})
@@ -716,8 +718,41 @@ extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t str
     a.ticket = (uint64_t)plan->d_norm + offsetof(oe_dev_norm, step_ticket);
     a.n_tensors = plan->n_active;
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
+    if (peers) {
+        oe_peer_set ps = *peers;
+        void* peer_args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a, &ps};
+        return launch(d, plan->dc->k.sgd_peers, "oe_sgd_fused_peers", grid_for(plan, plan->dc->occ_sgd_peers), kThreads,
+                      (CUstream)stream, peer_args);
+    }
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
     return launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
+}
+
+int peer_set_from(const int64_t* shadow_deltas, uint32_t n_ranks, const char* who, oe_peer_set* ps) {
+    if (!shadow_deltas) return fail(OE_ERR_INVALID, std::string(who) + ": NULL argument");
+    if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, std::string(who) + ": 1 to 8 ranks are supported");
+    memset(ps, 0, sizeof(*ps));
+    ps->n = n_ranks;
+    for (uint32_t k = 0; k < n_ranks; k++) {
+        if (shadow_deltas[k] & 1) return fail(OE_ERR_INVALID, std::string(who) + ": odd byte distance to a bf16 buffer");
+        // an 8-byte store needs every target as aligned as the local one
+        if (shadow_deltas[k] & 7) return fail(OE_ERR_INVALID, std::string(who) + ": shadow buffers must be mutually 8-byte aligned");
+        ps->delta[k] = shadow_deltas[k];
+    }
+    return 0;
+}
+}  // namespace
+
+extern "C" int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream) {
+    return sgd_step(plan, hp, stream, nullptr);
+}
+
+extern "C" int oe_sgd_step_peers(oe_plan* plan, const oe_sgd_hparams* hp, const int64_t* shadow_deltas, uint32_t n_ranks,
+                                 uint64_t stream) {
+    oe_peer_set ps;
+    int rc = peer_set_from(shadow_deltas, n_ranks, "oe_sgd_step_peers", &ps);
+    if (rc) return rc;
+    return sgd_step(plan, hp, stream, &ps);
 }
 
 extern "C" int oe_zero_grads(oe_plan* plan, uint64_t stream) {
@@ -959,21 +994,13 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
 
 extern "C" int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
                                    uint32_t n_ranks, uint64_t stream) {
-    if (!plan || !shadow_deltas) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: NULL argument");
-    if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_adamw_step_peers: 1 to 8 ranks are supported");
-    int rc = 0;
+    if (!plan) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: NULL argument");
+    oe_peer_set ps;
+    int rc = peer_set_from(shadow_deltas, n_ranks, "oe_adamw_step_peers", &ps);
+    if (rc) return rc;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
     if ((rc = validate_adamw(plan, hp)) != 0) return rc;
-    oe_peer_set ps;
-    memset(&ps, 0, sizeof(ps));
-    ps.n = n_ranks;
-    for (uint32_t k = 0; k < n_ranks; k++) {
-        if (shadow_deltas[k] & 1) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: odd byte distance to a bf16 buffer");
-        // an 8-byte store needs every target as aligned as the local one
-        if (shadow_deltas[k] & 7) return fail(OE_ERR_INVALID, "oe_adamw_step_peers: shadow buffers must be mutually 8-byte aligned");
-        ps.delta[k] = shadow_deltas[k];
-    }
     CtxGuard guard(d, plan->dc->ctx);
     return launch_adamw(d, plan, hp, (CUstream)stream, &ps);
 }

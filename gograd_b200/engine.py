@@ -174,6 +174,12 @@ class Plan:
         deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
         check(lib().oe_adamw_step_peers(self._h, C.byref(c), deltas, len(shadow_deltas), _stream(stream)))
 
+    def sgd_step_peers(self, hp: SGDHParams, shadow_deltas: Sequence[int], stream=None) -> None:
+        """SGD step whose shadow stores go to every rank's shadow buffer (oe_sgd_step_peers)."""
+        c = hp.to_c()
+        deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
+        check(lib().oe_sgd_step_peers(self._h, C.byref(c), deltas, len(shadow_deltas), _stream(stream)))
+
     def zero_grads(self, stream=None) -> None:
         check(lib().oe_zero_grads(self._h, _stream(stream)))
 

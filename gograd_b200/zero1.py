@@ -257,8 +257,7 @@ class Zero1AdamW(Zero1Schedule):
         self.grad_flat = torch.zeros(L.total, dtype=torch.float32, device=dev)
         self.shadow_flat = torch.zeros(L.total, dtype=torch.bfloat16, device=dev)
         self.master = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
-        self.m = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
-        self.v = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
+        self._allocate_state(dev)
         self.grads = [self.grad_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
         self.shadows = [self.shadow_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
         self.plan = engine.Plan(self._descs(), device, chunk_elems)
@@ -269,6 +268,11 @@ class Zero1AdamW(Zero1Schedule):
         self.shadow_deltas: Optional[List[int]] = None
         if comm == "peer":
             self._map_peers()
+
+    def _allocate_state(self, dev) -> None:
+        torch = self.torch
+        self.m = torch.zeros(self.layout.shard_len, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(self.layout.shard_len, dtype=torch.float32, device=dev)
 
     def _descs(self):
         """One descriptor per piece of a tensor inside this rank's shard."""
@@ -500,6 +504,55 @@ class Zero1AdamW(Zero1Schedule):
         self.torch.cuda.synchronize()
         self.dist.barrier(group=self.pg)
         self.plan.close()
+
+
+class Zero1SGD(Zero1AdamW):
+    """The sharded form of SGD.Step (autograd/sgd.go:192-225): same flat layout, reduction, norm and
+    shadow exchange as `Zero1AdamW`; the owner of a shard keeps the momentum buffer of its pieces and
+    one init flag per piece (the reference keeps one per tensor: a tensor that straddles two shards
+    has a piece, and a flag, on each owner). State files are not written by this class."""
+
+    def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, momentum: float,
+                 dampening: float, nesterov: bool, maximize: bool, max_norm: float, device: int, comm: str = "peer",
+                 process_group=None, chunk_elems: int = 0):
+        if nesterov and (not momentum > 0 or dampening != 0):
+            raise ValueError("autograd: Nesterov momentum requires a positive momentum and zero dampening")
+        self.momentum, self.dampening, self.nesterov, self.maximize = momentum, dampening, nesterov, maximize
+        # the base class fingerprints (lr, beta1, beta2, eps, max_norm): momentum and dampening take
+        # the places of the betas, the two switches the place of eps
+        super().__init__(numels, group_of, lr, momentum, dampening, float(2 * int(nesterov) + int(maximize)), max_norm,
+                         device, comm, process_group, chunk_elems)
+
+    def _allocate_state(self, dev) -> None:
+        torch = self.torch
+        self.buffer = torch.zeros(self.layout.shard_len, dtype=torch.float32, device=dev)
+        self.flags = torch.zeros(max(len(self.my_pieces), 1), dtype=torch.float32, device=dev)
+
+    def _descs(self):
+        lo, descs = self.lo, []
+        for k, pc in enumerate(self.my_pieces):
+            a, b = pc.flat_offset, pc.flat_offset + pc.length
+            scale, decay = self.group_of[pc.tensor]
+            has_state = self.momentum > 0
+            descs.append(self.engine.TensorDesc(self.master[a - lo:b - lo], self.grad_flat[a:b],
+                                                self.buffer[a - lo:b - lo] if has_state else None,
+                                                self.flags[k:k + 1] if has_state else None, self.shadow_flat[a:b], scale, decay))
+        return descs
+
+    def update(self) -> None:
+        from .engine import OE_MAXIMIZE, OE_NESTEROV, OE_WRITE_SHADOW
+        flags = OE_WRITE_SHADOW | (OE_NESTEROV if self.nesterov else 0) | (OE_MAXIMIZE if self.maximize else 0)
+        hp = self.engine.SGDHParams(self.lr, self.momentum, self.dampening, self.max_norm, flags)
+        if self.comm == "peer":
+            self.plan.sgd_step_peers(hp, self.shadow_deltas)
+        else:
+            self.plan.sgd_step(hp)
+
+    def save_state(self, *args, **kwargs) -> None:
+        raise NotImplementedError("the sharded SGD does not write state files")
+
+    def load_state(self, *args, **kwargs) -> None:
+        raise NotImplementedError("the sharded SGD does not read state files")
         for base in self._imported:
             self.engine.ipc_close(base, self.device)
         self._imported = []

@@ -266,6 +266,11 @@ OE_API int oe_adamw_step_chunks(oe_plan* plan, const oe_adamw_hparams* hp, uint6
 OE_API int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
                                uint32_t n_ranks, uint64_t stream);
 
+/* The same for oe_sgd_step: the sharded form of SGD.Step, momentum buffers and init flags per piece of a
+ * tensor inside the rank's shard. */
+OE_API int oe_sgd_step_peers(oe_plan* plan, const oe_sgd_hparams* hp, const int64_t* shadow_deltas, uint32_t n_ranks,
+                             uint64_t stream);
+
 /* CUDA IPC plumbing: export the allocation that contains `address` (64-byte handle + offset of
  * the address inside it), map a peer's allocation on this device, unmap it. */
 OE_API int oe_ipc_export(int device, uint64_t address, void* handle_out, uint64_t* offset_out);

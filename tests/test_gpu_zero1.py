@@ -209,6 +209,153 @@ def test_all_real_ranks_of_the_box(comm):
             assert np.array_equal(shadow[o:o + n], own), f"rank {rank} shadow[{i}] ({comm})"
 
 
+SGD_HP = dict(lr=0.05, momentum=0.9, dampening=0.0, nesterov=True, maximize=False, max_norm=0.01)
+
+
+def _oracle_sgd_run(world, steps):
+    """Unsharded oracle SGD on the fixed-order mean, clipped in place first."""
+    from oracle import oracle
+    groups = [oracle.Group(f"g{i}", [i], s, d) for i, (s, d) in enumerate(GROUPS)]
+    ref = oracle.OracleSGD([w.copy() for w in _weights()], lr=SGD_HP["lr"], momentum=SGD_HP["momentum"],
+                           dampening=SGD_HP["dampening"], nesterov=SGD_HP["nesterov"], maximize=SGD_HP["maximize"],
+                           groups=groups)
+    for step in range(1, steps + 1):
+        per_rank = [_grads(r, step) for r in range(world)]
+        mean = []
+        for i in range(len(NUMELS)):
+            acc = per_rank[0][i].copy()
+            for r in range(1, world):
+                acc = (acc + per_rank[r][i]).astype(np.float32)
+            mean.append((acc * np.float32(1.0 / world)).astype(np.float32))
+        oracle.clip_grad_norm(mean, SGD_HP["max_norm"])
+        ref.step(mean)
+    return ref
+
+
+def test_sgd_peer_kernel_with_emulated_ranks():
+    """oe_sgd_step_peers on one GPU: two "ranks" as separate buffers, each updating its shard of the flat
+    layout and storing bf16 into both shadow buffers; p, momentum buffers and shadows equal the
+    unsharded oracle, every piece's init flag is set after the first step."""
+    import gograd_b200 as eng
+    from gograd_b200.engine import OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW
+    from gograd_b200.zero1 import ShardLayout, _RawCuda
+    from oracle import oracle
+
+    eng.init(0)
+    world, steps = 2, 3
+    L = ShardLayout(NUMELS, world)
+    G = [torch.zeros(L.total, device="cuda") for _ in range(world)]
+    S = [torch.full((L.total,), -1, dtype=torch.int16, device="cuda") for _ in range(world)]
+    weights = np.zeros(L.total, np.float32)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = w
+    P, B, F, plans, records = [], [], [], [], []
+    for r in range(world):
+        lo, hi = L.shard_range(r)
+        pieces = L.pieces(r)
+        P.append(torch.from_numpy(weights[lo:hi].copy()).cuda())
+        B.append(torch.zeros(L.shard_len, device="cuda"))
+        F.append(torch.zeros(len(pieces), device="cuda"))
+        descs = []
+        for k, pc in enumerate(pieces):
+            a, b = pc.flat_offset, pc.flat_offset + pc.length
+            descs.append(eng.TensorDesc(P[r][a - lo:b - lo], G[r][a:b], B[r][a - lo:b - lo], F[r][k:k + 1], S[r][a:b],
+                                        *GROUPS[pc.tensor]))
+        plans.append(eng.Plan(descs))
+        records.append(torch.as_tensor(_RawCuda(plans[r].norm_address(), (1,), "<f8"), device="cuda"))
+    ref = _oracle_sgd_run(world, steps)
+    for step in range(1, steps + 1):
+        for r in range(world):
+            G[r].zero_()
+            for o, g in zip(L.offsets, _grads(r, step)):
+                G[r][o:o + g.size] = torch.from_numpy(g).cuda()
+        bases = [g.data_ptr() for g in G]
+        for r in range(world):
+            lo, hi = L.shard_range(r)
+            plans[r].peer_reduce_grads(bases, lo, L.shard_len, G[r][lo:hi].data_ptr(), 1.0 / world, OE_PARTIAL_ONLY)
+        total = sum(float(rec.item()) for rec in records)
+        for r in range(world):
+            records[r].fill_(total)
+            plans[r].norm_finalize()
+            hp = eng.SGDHParams(SGD_HP["lr"], SGD_HP["momentum"], SGD_HP["dampening"], SGD_HP["max_norm"],
+                                OE_WRITE_SHADOW | OE_NESTEROV)
+            plans[r].sgd_step_peers(hp, [S[k].data_ptr() - S[r].data_ptr() for k in range(world)])
+        if step == 1:
+            assert all(bool((f == 1).all()) for f in F)
+    torch.cuda.synchronize()
+    flat_p, flat_b = np.zeros(L.total, np.float32), np.zeros(L.total, np.float32)
+    for r in range(world):
+        lo, hi = L.shard_range(r)
+        flat_p[lo:hi], flat_b[lo:hi] = P[r].cpu().numpy(), B[r].cpu().numpy()
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat_p[o:o + n], ref.params[i]), f"p[{i}]"
+        assert np.array_equal(flat_b[o:o + n], ref.buffers[i]), f"buffer[{i}]"
+        want = oracle.f32_to_bf16(ref.params[i]).view(np.int16)
+        for r in range(world):
+            assert np.array_equal(S[r][o:o + n].cpu().numpy(), want), f"shadow[{i}] on rank {r}"
+    for p in plans:
+        p.close()
+
+
+def _sgd_rank_main(rank, world, port, comm, queue):
+    import torch.distributed as dist
+    from gograd_b200.zero1 import Zero1SGD
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    opt = Zero1SGD(NUMELS, GROUPS, SGD_HP["lr"], SGD_HP["momentum"], SGD_HP["dampening"], SGD_HP["nesterov"],
+                   SGD_HP["maximize"], SGD_HP["max_norm"], rank, comm=comm)
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+    for step in (1, 2, 3):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+        opt.step()
+    torch.cuda.synchronize()
+    queue.put((rank, opt.lo, opt.master.cpu().numpy(), opt.buffer.cpu().numpy(),
+               opt.shadow_flat.view(torch.int16).cpu().numpy()))
+    opt.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("comm", ["peer", "nccl"])
+def test_two_real_ranks_sgd(comm):
+    """The sharded SGD over two real ranks, both data paths, bit-identical to the unsharded oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from gograd_b200.zero1 import ShardLayout
+    from oracle import oracle
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_sgd_rank_main, args=(r, world, port, comm, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    ref = _oracle_sgd_run(world, 3)
+    L = ShardLayout(NUMELS, world)
+    flat_p, flat_b = np.zeros(L.total, np.float32), np.zeros(L.total, np.float32)
+    for rank, lo, master, buffer, shadow in results:
+        flat_p[lo:lo + master.size], flat_b[lo:lo + buffer.size] = master, buffer
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat_p[o:o + n], ref.params[i]), f"p[{i}] ({comm})"
+        assert np.array_equal(flat_b[o:o + n], ref.buffers[i]), f"buffer[{i}] ({comm})"
+        want = oracle.f32_to_bf16(ref.params[i]).view(np.int16)
+        for rank, lo, master, buffer, shadow in results:
+            assert np.array_equal(shadow[o:o + n], want), f"rank {rank} shadow[{i}] ({comm})"
+
+
 def _saving_rank_main(rank, world, port, out_dir, queue):
     import torch.distributed as dist
     from gograd_b200.zero1 import Zero1AdamW
