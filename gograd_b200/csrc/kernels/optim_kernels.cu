@@ -611,12 +611,24 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
         const uint64_t nvec = n >> 2;
         const float4* s4 = (const float4*)src;
         uint2* d2 = (uint2*)dst;
-        for (uint64_t i = tid; i < nvec; i += stride) {
-            float4 x = __ldcs(s4 + i);
-            uint2 packed;
-            packed.x = oe_bf16_rne(x.x) | (oe_bf16_rne(x.y) << 16);
-            packed.y = oe_bf16_rne(x.z) | (oe_bf16_rne(x.w) << 16);
-            __stcs(d2 + i, packed);
+        // four 128-bit loads in flight per thread before the first use, like the update kernels
+        for (uint64_t i0 = tid; i0 < nvec; i0 += stride * OE_UNROLL) {
+            float4 x[OE_UNROLL];
+#pragma unroll
+            for (int u = 0; u < OE_UNROLL; u++) {
+                uint64_t i = i0 + (uint64_t)u * stride;
+                if (i < nvec) x[u] = __ldcs(s4 + i);
+            }
+#pragma unroll
+            for (int u = 0; u < OE_UNROLL; u++) {
+                uint64_t i = i0 + (uint64_t)u * stride;
+                if (i < nvec) {
+                    uint2 packed;
+                    packed.x = oe_bf16_rne(x[u].x) | (oe_bf16_rne(x[u].y) << 16);
+                    packed.y = oe_bf16_rne(x[u].z) | (oe_bf16_rne(x[u].w) << 16);
+                    __stcs(d2 + i, packed);
+                }
+            }
         }
         done = nvec << 2;
     }
