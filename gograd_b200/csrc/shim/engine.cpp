@@ -765,8 +765,10 @@ extern "C" int oe_zero_grads(oe_plan* plan, uint64_t stream) {
     CtxGuard guard(d, plan->dc->ctx);
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems};
-    return launch(d, plan->dc->k.zero, "oe_zero_grads", grid_for(plan, plan->dc->occ_zero), kThreads, (CUstream)stream,
-                  args);
+    // One CTA per work unit, dispatched in table order: for a write-only stream a compact window that
+    // sweeps the addresses in order measured 7.5 TB/s on B200 against 6.1 TB/s for a persistent grid
+    // whose CTAs drift apart (the read-modify-write kernels measured the same either way).
+    return launch(d, plan->dc->k.zero, "oe_zero_grads", n_chunks, kThreads, (CUstream)stream, args);
 }
 
 extern "C" int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t numel, uint64_t stream) {
