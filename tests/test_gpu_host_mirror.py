@@ -609,3 +609,45 @@ def test_sgd_captured_steps_match_eager_and_sync_the_counter(ag):
     assert eager.StepCount == 3
     o.Close()
     eager.Close()
+
+
+def test_a_bf16_gemm_consumes_the_shadow_the_step_wrote(ag):
+    """The consumer on the far side of the path: the next forward's matrix multiply takes a lease on the
+    weight's bf16 shadow (autograd/cuda_blas.go:97-99,197-203) instead of casting the fp32 master again.
+    A library bf16 GEMM over the leased buffer gives the bits of the same GEMM over a fresh cast of the
+    master, before and after further steps, and the leased operand stays what the GEMM node captured."""
+    class Borrowed:
+        def __init__(self, address, shape):
+            self.__cuda_array_interface__ = {"shape": shape, "typestr": "<i2", "data": (address, False), "version": 2}
+
+    rng = np.random.default_rng(61)
+    rows, cols = 96, 128
+    w = ag.Tensor(rng.normal(0, .05, rows * cols).astype(np.float32), [rows, cols])
+    opt = ag.NewAdamW([ag.Parameter("w", w)], 1e-2, 0.1)
+    opt.SetEngine(write_shadow=True)
+    x = torch.from_numpy(rng.normal(0, 1, (32, rows)).astype(np.float32)).cuda().to(torch.bfloat16)
+
+    def forward_with_lease():
+        lease = w.shadow_lease()
+        weight = torch.as_tensor(Borrowed(lease, (rows, cols)), device="cuda").view(torch.bfloat16)
+        return lease, weight, x @ weight
+
+    def forward_with_fresh_cast():
+        master = torch.from_numpy(w.to_host()).cuda().view(rows, cols)
+        return x @ master.to(torch.bfloat16)
+
+    w.set_grad(rng.normal(0, .1, rows * cols).astype(np.float32))
+    opt.StepClipped(1.0)
+    lease1, weight1, y1 = forward_with_lease()
+    assert torch.equal(y1, forward_with_fresh_cast())
+    captured = weight1.clone()
+    w.set_grad(rng.normal(0, .1, rows * cols).astype(np.float32))
+    opt.StepClipped(1.0)                      # the first forward's node still holds its lease
+    assert torch.equal(weight1, captured), "the operand a graph node kept must not change under it"
+    lease2, weight2, y2 = forward_with_lease()
+    assert lease2 != lease1 and torch.equal(y2, forward_with_fresh_cast()) and not torch.equal(y2, y1)
+    w.shadow_release(lease1)
+    w.shadow_release(lease2)
+    assert w.leased_shadows == 0
+    torch.cuda.synchronize()
+    opt.Close()
