@@ -20,7 +20,7 @@ def _slice_with_offset(values, offset):
     return view
 
 
-@pytest.mark.parametrize("seed", range(24))
+@pytest.mark.parametrize("seed", range(64))
 def test_random_configuration(seed):
     import gograd_b200 as eng
     from gograd_b200.engine import (OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_WRITE_SHADOW, OE_ZERO_GRAD)
