@@ -24,6 +24,14 @@
  * Threading. A plan may be used from any thread, by one thread and one stream at a
  * time. The library never changes the caller's current context: it pushes the
  * device's primary context for the duration of a call and pops it again.
+ *
+ * Stream capture. oe_grad_norm, oe_norm_finalize, oe_adamw_step, oe_sgd_step, oe_zero_grads and
+ * oe_cast_bf16 only enqueue launches: they allocate nothing and never synchronise, and the
+ * counters the kernels use re-arm themselves, so the calls may be recorded in a stream capture
+ * and replayed. A recorded launch carries the plan's table addresses, its number of work units,
+ * its gradient scale and the hyper-parameter block as they were when it was recorded (step_dev
+ * and lr_dev are the two values a replay reads afresh): create or update the plan before
+ * capturing, and capture again after oe_plan_update changed the tensors.
  */
 #ifndef OPTENGINE_H
 #define OPTENGINE_H
