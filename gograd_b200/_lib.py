@@ -74,6 +74,8 @@ PROTOTYPES = {
     "oe_grad_norm_static": (_i, [_i, _u64, _u64, _u64, _u64]),
     "oe_launch_count": (C.c_int64, [C.c_char_p]),
     "oe_launch_count_reset": (None, []),
+    "oe_profile_enable": (None, [_i]),
+    "oe_profile_get": (_i, [C.c_char_p, C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
     "oe_mem_alloc": (_i, [_i, _u64, C.POINTER(_u64)]),
     "oe_mem_free": (_i, [_i, _u64]),
     "oe_mem_info": (_i, [_i, C.POINTER(_u64), C.POINTER(_u64)]),

@@ -7,6 +7,7 @@
 #include <stdint.h>
 #include <string.h>
 
+#include <atomic>
 #include <map>
 #include <mutex>
 #include <new>
@@ -114,10 +115,35 @@ void count_launch(const char* name) {
     g_launches[name] += 1;
 }
 
+// Optional per-launch timing (the reference's EnableGPUProfile / timedGPU, autograd/cuda_kernels.go:24-82):
+// two events around the launch and a wait for the second one, summed per kernel name. Like the
+// reference's it serialises every launch, so it is a diagnostic and must stay off under stream capture.
+std::atomic<bool> g_profiling{false};
+std::map<std::string, double> g_profile_ms;  // guarded by g_mu
+
 int launch(const oe_driver* d, CUfunction f, const char* name, uint32_t grid, uint32_t block, CUstream stream,
            void** args) {
-    OE_CU(d->cuLaunchKernel_(f, grid, 1, 1, block, 1, 1, 0, stream, args, nullptr), name);
-    count_launch(name);
+    if (!g_profiling.load(std::memory_order_relaxed)) {
+        OE_CU(d->cuLaunchKernel_(f, grid, 1, 1, block, 1, 1, 0, stream, args, nullptr), name);
+        count_launch(name);
+        return 0;
+    }
+    CUevent start = nullptr, end = nullptr;
+    OE_CU(d->cuEventCreate_(&start, CU_EVENT_DEFAULT), "cuEventCreate(profile)");
+    CUresult r = d->cuEventCreate_(&end, CU_EVENT_DEFAULT);
+    if (r == CUDA_SUCCESS) r = d->cuEventRecord_(start, stream);
+    if (r == CUDA_SUCCESS) r = d->cuLaunchKernel_(f, grid, 1, 1, block, 1, 1, 0, stream, args, nullptr);
+    bool launched = r == CUDA_SUCCESS;
+    if (r == CUDA_SUCCESS) r = d->cuEventRecord_(end, stream);
+    if (r == CUDA_SUCCESS) r = d->cuEventSynchronize_(end);
+    float ms = 0.0f;
+    if (r == CUDA_SUCCESS) r = d->cuEventElapsedTime_(&ms, start, end);
+    d->cuEventDestroy_(start);
+    if (end) d->cuEventDestroy_(end);
+    if (launched) count_launch(name);
+    if (r != CUDA_SUCCESS) return fail_cu(d, r, name);
+    std::lock_guard<std::mutex> lock(g_mu);
+    g_profile_ms[name] += (double)ms;
     return 0;
 }
 
@@ -828,6 +854,28 @@ extern "C" int64_t oe_launch_count(const char* kernel_name) {
 extern "C" void oe_launch_count_reset(void) {
     std::lock_guard<std::mutex> lock(g_mu);
     g_launches.clear();
+}
+
+extern "C" void oe_profile_enable(int enabled) {
+    if (enabled) {  // enabling starts a fresh profile, as EnableGPUProfile(true) does
+        std::lock_guard<std::mutex> lock(g_mu);
+        g_profile_ms.clear();
+        g_launches.clear();
+    }
+    g_profiling.store(enabled != 0);
+}
+
+extern "C" int oe_profile_get(const char* kernel_name, int64_t* count_out, double* ms_out) {
+    std::lock_guard<std::mutex> lock(g_mu);
+    int64_t count = 0;
+    double ms = 0.0;
+    for (const auto& kv : g_launches)
+        if (!kernel_name || kv.first == kernel_name) count += kv.second;
+    for (const auto& kv : g_profile_ms)
+        if (!kernel_name || kv.first == kernel_name) ms += kv.second;
+    if (count_out) *count_out = count;
+    if (ms_out) *ms_out = ms;
+    return 0;
 }
 
 // -------------------------------------------------------------------------------------

@@ -252,3 +252,15 @@ def launch_count_reset() -> None:
 __all__ = ["AdamWHParams", "SGDHParams", "TensorDesc", "Plan", "cast_bf16", "init", "launch_count",
            "launch_count_reset", "EngineError", "OE_CLIP_DEVFORM", "OE_WRITE_SHADOW", "OE_ZERO_GRAD", "OE_NESTEROV",
            "OE_MAXIMIZE", "OE_PARTIAL_ONLY", "OE_ACCUMULATE"]
+
+
+def profile_enable(enabled: bool = True) -> None:
+    """Per-launch timing like the reference's EnableGPUProfile: serialises every launch while on."""
+    lib().oe_profile_enable(int(enabled))
+
+
+def profile(name: Optional[str] = None):
+    """(launch count, device milliseconds) of one kernel, or of all kernels."""
+    count, ms = C.c_int64(), C.c_double()
+    check(lib().oe_profile_get(None if name is None else name.encode(), C.byref(count), C.byref(ms)))
+    return int(count.value), float(ms.value)

@@ -315,6 +315,14 @@ OE_API int oe_grad_norm_static(int device, uint64_t grad, uint64_t numel, uint64
 OE_API int64_t oe_launch_count(const char* kernel_name);
 OE_API void oe_launch_count_reset(void);
 
+/* Optional timing of every launch (EnableGPUProfile / GPUProfile, autograd/cuda_kernels.go:24-82): while
+ * enabled each launch is bracketed by two events and waited for, and its device time is added to the
+ * total of its kernel name. Enabling clears counts and times. A diagnostic: it serialises the stream
+ * and must stay off inside a stream capture. oe_profile_get reads count and milliseconds of one
+ * kernel (name NULL = all kernels); either output may be NULL. */
+OE_API void oe_profile_enable(int enabled);
+OE_API int oe_profile_get(const char* kernel_name, int64_t* count_out, double* ms_out);
+
 /* ---- device plumbing for a host without a CUDA binding ------------------------------------------ */
 /* The reference's cuda package only exists for Windows (cuda/cuda_stub.go:1-25); these
  * are the few calls its optimizer path needs on Linux (cuda.Alloc / Buffer.Free /

@@ -676,3 +676,31 @@ def test_default_work_unit_follows_the_size_of_the_parameter_list(eng):
     assert unit_for([10], 8192)[0] == 8192
     with pytest.raises(eng.engine.EngineError):
         unit_for([10], 1000)
+
+
+def test_launch_profile_counts_and_times_kernels(eng):
+    """The reference's tests assert that a kernel ran through its profile (EnableGPUProfile / GPUProfile,
+    autograd/cuda_kernels.go:24-82, autograd/sgd_test.go:119-121): while enabled every launch is timed
+    and summed under its kernel name; enabling starts afresh; disabled, only the counts go on."""
+    from gograd_b200 import engine
+    n = 1 << 22
+    p, g = torch.zeros(n, device="cuda"), torch.full((n,), 1e-3, device="cuda")
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    plan = eng.Plan([eng.TensorDesc(p, g, m, v, None, 1.0, 0.1)])
+    hp = eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, 0.1, 0.001, max_norm=1.0)
+    engine.profile_enable(True)
+    for _ in range(3):
+        plan.grad_norm()
+        plan.adamw_step(hp)
+    count, ms = engine.profile("oe_adamw_fused")
+    assert count == 3 and 0.0 < ms < 50.0
+    assert engine.profile("oe_grad_sumsq")[0] == 3 and engine.profile("oe_sgd_fused") == (0, 0.0)
+    total_count, total_ms = engine.profile()
+    assert total_count == 6 and total_ms >= ms
+    engine.profile_enable(False)
+    plan.adamw_step(hp)
+    assert engine.profile("oe_adamw_fused") == (4, ms), "counts go on, times stop"
+    engine.profile_enable(True)
+    assert engine.profile() == (0, 0.0)
+    engine.profile_enable(False)
+    plan.close()
