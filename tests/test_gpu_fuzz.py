@@ -12,6 +12,16 @@ torch = pytest.importorskip("torch")
 SIZES = [1, 2, 3, 4, 5, 7, 8, 63, 64, 65, 1000, 4095, 4096, 4097, 8191, 8193, 12288, 20011]
 
 
+def _guards_untouched(view):
+    """The elements of the allocation around a view still hold what they were created with (zeros)."""
+    base = view._base
+    if base is None:
+        return True
+    start = view.storage_offset()
+    flat = base.reshape(-1)
+    return bool((flat[:start] == 0).all()) and bool((flat[start + view.numel():] == 0).all())
+
+
 def _slice_with_offset(values, offset):
     """A device tensor whose first element sits `offset` floats past an allocation boundary."""
     backing = torch.zeros(values.size + offset + 4, dtype=torch.float32, device="cuda")
@@ -125,4 +135,8 @@ def test_random_configuration(seed):
             if present[i]:
                 want_g = np.zeros(sizes[i], np.float32) if zero_grad else grads[i]
                 assert np.array_equal(g[i].cpu().numpy(), want_g), f"{what}: gradient after the step"
+    # canaries: nothing was written outside any tensor, whatever its offset, tail or work-unit size
+    for group in (p, g, s1, sh, s2 if use_adamw else []):
+        for t in group:
+            assert _guards_untouched(t), f"seed {seed}: a kernel wrote outside a tensor"
     plan.close()
