@@ -704,3 +704,64 @@ def test_launch_profile_counts_and_times_kernels(eng):
     assert engine.profile() == (0, 0.0)
     engine.profile_enable(False)
     plan.close()
+
+
+def test_against_the_library_optimizers_as_a_second_opinion(eng):
+    """The oracle restates the reference; the fixtures it is pinned to came from PyTorch. As a second
+    opinion the engine is compared with torch.optim.AdamW / SGD and clip_grad_norm_ directly (the same
+    library family, other operation order, fused multiply-adds allowed): within 2e-6 relative plus a
+    floor tied to each tensor's scale after five clipped steps — a tolerance, not the bit-for-bit
+    equality the oracle tests require."""
+    rng = np.random.default_rng(77)
+    sizes = [5000, 33, 4096, 12001]
+    w0 = [rng.normal(0, .05, n).astype(np.float32) for n in sizes]
+    grads = [[rng.normal(0, .02, n).astype(np.float32) for n in sizes] for _ in range(5)]
+
+    def close(name, got, want):
+        got, want = got.astype(np.float64), want.astype(np.float64)
+        floor = 2e-6 * float(np.max(np.abs(want)))
+        assert np.all(np.abs(got - want) <= 2e-6 * np.abs(want) + floor), name
+
+    # AdamW, decoupled decay, clip 0.5
+    tp = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in w0]
+    topt = torch.optim.AdamW(tp, lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    p = [dev(x) for x in w0]
+    g = [torch.zeros_like(x) for x in p]
+    m = [torch.zeros_like(x) for x in p]
+    v = [torch.zeros_like(x) for x in p]
+    plan = eng.Plan([eng.TensorDesc(p[i], g[i], m[i], v[i], None, 1.0, 0.1) for i in range(len(p))])
+    for t, gs in enumerate(grads, start=1):
+        for i, x in enumerate(gs):
+            tp[i].grad = torch.from_numpy(x.copy()).cuda()
+            g[i].copy_(torch.from_numpy(x))
+        want_norm = float(torch.nn.utils.clip_grad_norm_(tp, 0.5))
+        topt.step()
+        b1, b2 = bc(0.9, 0.95, t)
+        plan.grad_norm()
+        plan.adamw_step(eng.AdamWHParams(1e-3, 0.9, 0.95, 1e-8, b1, b2, max_norm=0.5))
+        norm, _ = plan.read_norm()
+        assert abs(norm - want_norm) <= 1e-6 * want_norm
+    for i in range(len(p)):
+        close(f"adamw p[{i}]", host(p[i]), tp[i].detach().cpu().numpy())
+        close(f"adamw m[{i}]", host(m[i]), topt.state[tp[i]]["exp_avg"].cpu().numpy())
+        close(f"adamw v[{i}]", host(v[i]), topt.state[tp[i]]["exp_avg_sq"].cpu().numpy())
+    plan.close()
+
+    # SGD, coupled decay, momentum, Nesterov
+    tp = [torch.nn.Parameter(torch.from_numpy(x.copy()).cuda()) for x in w0]
+    topt = torch.optim.SGD(tp, lr=0.05, momentum=0.9, nesterov=True, weight_decay=0.01)
+    p = [dev(x) for x in w0]
+    g = [torch.zeros_like(x) for x in p]
+    buf = [torch.zeros_like(x) for x in p]
+    flag = [torch.zeros(1, device="cuda") for _ in p]
+    plan = eng.Plan([eng.TensorDesc(p[i], g[i], buf[i], flag[i], None, 1.0, 0.01) for i in range(len(p))])
+    for gs in grads:
+        for i, x in enumerate(gs):
+            tp[i].grad = torch.from_numpy(x.copy()).cuda()
+            g[i].copy_(torch.from_numpy(x))
+        topt.step()
+        plan.sgd_step(eng.SGDHParams(0.05, 0.9, 0.0, 0.0, eng.engine.OE_NESTEROV))
+    for i in range(len(p)):
+        close(f"sgd p[{i}]", host(p[i]), tp[i].detach().cpu().numpy())
+        close(f"sgd buffer[{i}]", host(buf[i]), topt.state[tp[i]]["momentum_buffer"].cpu().numpy())
+    plan.close()
