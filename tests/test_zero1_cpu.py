@@ -278,13 +278,25 @@ def test_roll_call_passes_when_everyone_is_there():
     import torch.distributed as dist
     from gograd_b200.zero1 import PeerLiveness
     server = dist.TCPStore("127.0.0.1", 0, is_master=True, wait_for_workers=False, timeout=timedelta(seconds=30))
-    a, b = PeerLiveness(server, 0, 2, 1.0), PeerLiveness(server, 1, 2, 1.0)
+    # every participant talks to the store over a connection of its own, as ranks do: one client
+    # object shared by two threads would interleave their requests on one socket
+    client = dist.TCPStore("127.0.0.1", server.port, is_master=False, timeout=timedelta(seconds=30))
+    a, b = PeerLiveness(server, 0, 2, 20.0), PeerLiveness(client, 1, 2, 20.0)
     import threading
+    failures = []
+
+    def other(step):
+        try:
+            b.arrive(step)
+        except Exception as e:   # reported by the test's own assertion, not as a stray thread warning
+            failures.append(e)
+
     for step in range(1, 6):
-        t = threading.Thread(target=b.arrive, args=(step,))
+        t = threading.Thread(target=other, args=(step,))
         t.start()
         a.arrive(step)
         t.join()
+    assert failures == []
     assert not server.check(["oe/alive/1/0"]) and server.check(["oe/alive/5/0"])
     with pytest.raises(ValueError):
         PeerLiveness(server, 0, 2, 0.0)
