@@ -437,8 +437,17 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--variant", default="")
     ap.add_argument("--chunk", type=int, default=0)
-    ap.add_argument("--comm", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: fused peer-memory kernels, or NCCL reduce-scatter / all-gather around the kernels")
+    ap.add_argument("--comm", default="peer", choices=["peer", "abi", "nccl"],
+                    help="N > 1: fused peer-memory kernels ordered by tiny NCCL all-reduces (peer) or by the library's own "
+                         "bounded exchanges, one C call per step (abi); or NCCL reduce-scatter / all-gather around the "
+                         "single-GPU kernels (nccl)")
+    ap.add_argument("--multicast", action="store_true", help="N > 1: shadow stores through the NVLink multicast mapping")
+    ap.add_argument("--push-order", default="ascending", choices=["ascending", "rotated"])
+    ap.add_argument("--reduce-first", default="rank0", choices=["rank0", "rotated"])
+    ap.add_argument("--reduce-grid", type=int, default=0)
+    ap.add_argument("--update-grid", type=int, default=0)
+    ap.add_argument("--push-warp-rotate", action="store_true")
+    ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")
     ap.add_argument("--secondary", action="store_true", help="time the other kernels of the path instead of the step")
     ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")
     ap.add_argument("--graph-steps", type=int, default=1,
@@ -454,8 +463,8 @@ def main():
         return run_secondary(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.gpus > 1 or world > 1:
-        from gograd_b200 import zero1_bench
-        return zero1_bench.run(args)
+        import bench_zero1
+        return bench_zero1.run(args)
     return run_single(args)
 
 

@@ -28,6 +28,17 @@ class oe_sgd_hparams(C.Structure):
                 ("flags", C.c_uint32), ("reserved", C.c_uint32), ("step_dev", C.c_uint64), ("lr_dev", C.c_uint64)]
 
 
+class oe_zero1_desc(C.Structure):
+    _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("first_elem", C.c_uint64), ("numel", C.c_uint64),
+                ("grad_bases", C.c_uint64 * 8), ("shadow_deltas", C.c_int64 * 8), ("shadow_mc_delta", C.c_int64),
+                ("sync_blocks", C.c_uint64 * 8), ("timeout_ms", C.c_uint32), ("flags", C.c_uint32)]
+
+
+OE_ZERO1_SYNC_BYTES = 512
+OE_ZERO1_NO_ENTRY_EXCHANGE = 1
+OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_PUSH_WARP_ROTATE = 1, 2, 3, 4
+
+
 class EngineError(RuntimeError):
     """A C-ABI call returned non-zero; carries the code and oe_last_error()."""
 
@@ -68,6 +79,17 @@ PROTOTYPES = {
     "oe_peer_reduce_grads": (_i, [_plan, C.POINTER(_u64), _u32, _u64, _u64, _u64, C.POINTER(C.c_float), _u32, _u64]),
     "oe_adamw_step_peers": (_i, [_plan, C.POINTER(oe_adamw_hparams), C.POINTER(C.c_int64), _u32, _u64]),
     "oe_sgd_step_peers": (_i, [_plan, C.POINTER(oe_sgd_hparams), C.POINTER(C.c_int64), _u32, _u64]),
+    "oe_adamw_step_multicast": (_i, [_plan, C.POINTER(oe_adamw_hparams), C.POINTER(C.c_int64), _u32,
+                                     C.POINTER(C.c_int64), _u64]),
+    "oe_sgd_step_multicast": (_i, [_plan, C.POINTER(oe_sgd_hparams), C.POINTER(C.c_int64), _u32,
+                                   C.POINTER(C.c_int64), _u64]),
+    "oe_plan_set_tuning": (_i, [_plan, _i, _u64]),
+    "oe_zero1_create": (_i, [_plan, C.POINTER(oe_zero1_desc), C.POINTER(_vp)]),
+    "oe_zero1_destroy": (_i, [_vp]),
+    "oe_zero1_adamw_step": (_i, [_vp, C.POINTER(oe_adamw_hparams), _u64]),
+    "oe_zero1_sgd_step": (_i, [_vp, C.POINTER(oe_sgd_hparams), _u64]),
+    "oe_zero1_exchange": (_i, [_vp, _u32, _u64]),
+    "oe_zero1_status": (_i, [_vp, C.POINTER(_u32), _u64]),
     "oe_ipc_export": (_i, [_i, _u64, _vp, C.POINTER(_u64)]),
     "oe_ipc_import": (_i, [_i, _vp, C.POINTER(_u64)]),
     "oe_ipc_close": (_i, [_i, _u64]),

@@ -620,18 +620,14 @@ def adamw_state_write(path: str, names: Sequence[str], shapes: Sequence[Sequence
     _check(lib().gg_adamw_state_write(path.encode(), n, c_names, c_shapes, c_off, c_m, c_v, C.byref(cfg), C.byref(gs)))
 
 
-class AdamWStateStream:
-    """The same "gograd-adamw" file written front to back without holding the moments: the file's
-    layout is fixed by names, shapes, configuration and groups; the values then arrive entry by
-    entry in the order the file stores them, an entry possibly in consecutive pieces."""
+class _SGDConfig(C.Structure):
+    _fields_ = [("step_count", C.c_int32), ("lr", C.c_float), ("momentum", C.c_float), ("dampening", C.c_float),
+                ("weight_decay", C.c_float), ("nesterov", C.c_int32), ("maximize", C.c_int32)]
 
-    def __init__(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], step_count: int, lr: float,
-                 weight_decay: float, beta1: float, beta2: float, eps: float, groups: Sequence[tuple]):
-        n, c_names, c_shapes, c_off, cfg, gs, _keep = _state_c_args(names, shapes, step_count, lr, weight_decay, beta1,
-                                                                    beta2, eps, groups)
-        self._h = C.c_void_p()
-        _check(lib().gg_adamw_state_stream_begin(path.encode(), n, c_names, c_shapes, c_off, C.byref(cfg), C.byref(gs),
-                                                 C.byref(self._h)))
+
+class _StateStream:
+    """Common part of the streamed state writers: values arrive entry by entry in file order."""
+    _h = None
 
     def next(self):
         """(entry name, values still missing) of the entry the file wants next; None at the end."""
@@ -659,3 +655,34 @@ class AdamWStateStream:
             self.abort()
         except Exception:
             pass
+
+
+class SGDStateStream(_StateStream):
+    """A "gograd-sgd" state file (autograd/sgd_state.go:150-194) written front to back: one entry
+    buffer.<i> per parameter whose momentum buffer is initialised; flags, options and groups in the
+    metadata. groups: (name, member indexes, lr_scale, weight_decay) per group."""
+
+    def __init__(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], step_count: int, lr: float,
+                 momentum: float, dampening: float, weight_decay: float, nesterov: bool, maximize: bool,
+                 initialized: Sequence[bool], groups: Sequence[tuple]):
+        n, c_names, c_shapes, c_off, _cfg, gs, _keep = _state_c_args(names, shapes, step_count, lr, weight_decay, 0.0,
+                                                                     0.0, 0.0, groups)
+        cfg = _SGDConfig(step_count, lr, momentum, dampening, weight_decay, int(nesterov), int(maximize))
+        flags = (C.c_uint8 * max(n, 1))(*[1 if b else 0 for b in initialized])
+        self._h = C.c_void_p()
+        _check(lib().gg_sgd_state_stream_begin(path.encode(), n, c_names, c_shapes, c_off, C.byref(cfg), flags,
+                                               C.byref(gs), C.byref(self._h)))
+
+
+class AdamWStateStream(_StateStream):
+    """The same "gograd-adamw" file written front to back without holding the moments: the file's
+    layout is fixed by names, shapes, configuration and groups; the values then arrive entry by
+    entry in the order the file stores them, an entry possibly in consecutive pieces."""
+
+    def __init__(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]], step_count: int, lr: float,
+                 weight_decay: float, beta1: float, beta2: float, eps: float, groups: Sequence[tuple]):
+        n, c_names, c_shapes, c_off, cfg, gs, _keep = _state_c_args(names, shapes, step_count, lr, weight_decay, beta1,
+                                                                    beta2, eps, groups)
+        self._h = C.c_void_p()
+        _check(lib().gg_adamw_state_stream_begin(path.encode(), n, c_names, c_shapes, c_off, C.byref(cfg), C.byref(gs),
+                                                 C.byref(self._h)))

@@ -336,6 +336,7 @@ struct TrainingLoop {
 std::string optimizerEntries(OptimizerState state, EntryMap* entries, Metadata* metadata);
 void optimizerMetadata(const OptimizerState& state, Metadata* metadata);
 std::string optimizerStateFromEntries(const EntryMap& entries, const Metadata& metadata, int count, OptimizerState* out);
+void sgdMetadata(const SGDState& state, Metadata* metadata);
 std::string sgdEntries(SGDState state, EntryMap* entries, Metadata* metadata);
 std::string sgdStateFromEntries(const EntryMap& entries, const Metadata& metadata, SGDState* out);
 std::string snapshotEntries(const OptimizerSnapshot& s, EntryMap* entries, Metadata* metadata);

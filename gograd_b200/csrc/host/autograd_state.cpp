@@ -193,15 +193,9 @@ std::string optimizerStateFromEntries(const EntryMap& entries, const Metadata& m
 }
 
 // ---- SGD --------------------------------------------------------------------------------
-std::string sgdEntries(SGDState s, EntryMap* entries, Metadata* metadata) {
-    entries->clear();
-    for (size_t i = 0; i < s.Initialized.size(); i++) {
-        if (!s.Initialized[i]) continue;  // only initialised parameters have a buffer entry
-        SafeTensorEntry b;
-        b.Values = std::move(s.Buffers[i]);
-        b.Shape = {(int)b.Values.size()};
-        (*entries)["buffer." + std::to_string(i)] = std::move(b);
-    }
+// Metadata of a "gograd-sgd" file: it depends on names, shapes, options, flags and groups, never
+// on the buffer values, so a streamed writer can lay the file out before any value arrives.
+void sgdMetadata(const SGDState& s, Metadata* metadata) {
     std::string init = s.Initialized.empty() ? "[]" : "[";
     for (size_t i = 0; i < s.Initialized.size(); i++) init += std::string(i ? "," : "") + (s.Initialized[i] ? "true" : "false");
     if (!s.Initialized.empty()) init += "]";
@@ -212,6 +206,18 @@ std::string sgdEntries(SGDState s, EntryMap* entries, Metadata* metadata) {
                          ",\"Nesterov\":" + (o.Nesterov ? "true" : "false") + ",\"Maximize\":" + (o.Maximize ? "true" : "false") +
                          "},\"Initialized\":" + init + ",\"Buffers\":null,\"Groups\":" + groups_json(s.Groups) + "}";
     *metadata = {{"format", "gograd-sgd"}, {"version", "1"}, {"step_count", std::to_string(s.StepCount)}, {"optimizer", config}};
+}
+
+std::string sgdEntries(SGDState s, EntryMap* entries, Metadata* metadata) {
+    entries->clear();
+    sgdMetadata(s, metadata);
+    for (size_t i = 0; i < s.Initialized.size(); i++) {
+        if (!s.Initialized[i]) continue;  // only initialised parameters have a buffer entry
+        SafeTensorEntry b;
+        b.Values = std::move(s.Buffers[i]);
+        b.Shape = {(int)b.Values.size()};
+        (*entries)["buffer." + std::to_string(i)] = std::move(b);
+    }
     return "";
 }
 

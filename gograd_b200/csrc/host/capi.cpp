@@ -734,6 +734,47 @@ int gg_adamw_state_stream_begin(const char* path, int32_t n, const char* const* 
     });
 }
 
+int gg_sgd_state_stream_begin(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                              const int32_t* shape_offsets, const gg_sgd_config* config, const uint8_t* initialized,
+                              const gg_groups* groups, gg_state_stream** out) {
+    return guarded([&]() -> std::string {
+        if (!path || !out || !config || (n > 0 && !initialized)) return "NULL argument";
+        // names, shapes and groups arrive in the flat form the AdamW writer takes
+        gg_adamw_config unused = {config->step_count, config->lr, config->weight_decay, 0.0f, 0.0f, 0.0f};
+        OptimizerState base;
+        std::string e = state_from_c(n, names, shapes, shape_offsets, &unused, groups, &base);
+        if (!e.empty()) return e;
+        SGDState s;
+        s.StepCount = config->step_count;
+        s.Names = base.Names;
+        s.Shapes = base.Shapes;
+        s.Groups = base.Groups;
+        s.Options.LR = config->lr;
+        s.Options.Momentum = config->momentum;
+        s.Options.Dampening = config->dampening;
+        s.Options.WeightDecay = config->weight_decay;
+        s.Options.Nesterov = config->nesterov != 0;
+        s.Options.Maximize = config->maximize != 0;
+        if (!(e = s.Options.validate()).empty()) return e;
+        std::map<std::string, std::vector<int>> entry_shapes;
+        for (int32_t i = 0; i < n; i++) {
+            s.Initialized.push_back(initialized[i] != 0);
+            if (!initialized[i]) continue;  // only initialised parameters have a buffer entry (autograd/sgd_state.go:150-164)
+            if (!(s.Options.Momentum > 0) || s.StepCount == 0) return "autograd: invalid SGD momentum buffer " + std::to_string(i);
+            long long count = 0;
+            if (!safe_numel(s.Shapes[(size_t)i], INT32_MAX, &count)) return "autograd: invalid shape of " + s.Names[(size_t)i];
+            entry_shapes["buffer." + std::to_string(i)] = {(int)count};
+        }
+        Metadata metadata;
+        sgdMetadata(s, &metadata);
+        std::unique_ptr<gg_state_stream> h(new gg_state_stream());
+        e = h->stream.Begin(path, entry_shapes, &metadata);
+        if (!e.empty()) return e;
+        *out = h.release();
+        return "";
+    });
+}
+
 int gg_state_stream_next(const gg_state_stream* s, char* name_out, int32_t capacity, int64_t* remaining_out) {
     if (!s || !name_out || !remaining_out || capacity < 1) return fail("NULL argument");
     std::string name;

@@ -100,11 +100,29 @@ __device__ __forceinline__ void oe_adamw_one(float& p, float g, float& m, float&
 // owns a shard stores its bf16 values into all of them (its own included) — the
 // all-gather of the shadows is these stores, overlapped with the update's HBM traffic.
 // Peer buffers are plain peer-mapped device memory reached with ordinary stores.
+// Peer modes. Plain: one ordinary store per target, in the order of peers.delta (the caller
+// chooses the order; with OE_PEER_WARP_ROTATE warp w of the CTA starts its round at target
+// w mod n, so the warps of a CTA do not all address the same GPU at the same moment).
+// Multicast: peers.mc_delta leads to a multicast mapping of the buffer (every rank's copy bound
+// to one NVLink multicast object); one multimem.st leaves this GPU once and the switch
+// delivers it to every rank, the storing one included. The instruction has no 16-bit form,
+// so the few single elements (tails of tensors whose length is no multiple of 4) keep the
+// plain stores.
 template <bool PEERS>
 __device__ __forceinline__ void oe_store_shadow4(uint16_t* sh, uint32_t vec_index, uint2 packed, const oe_peer_set& peers) {
     if (PEERS) {
-        for (uint32_t k = 0; k < peers.n; k++)
+        if (peers.mode & OE_PEER_MULTICAST) {
+            uint2* dst = (uint2*)((char*)sh + peers.mc_delta) + vec_index;
+            asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(dst), "f"(__uint_as_float(packed.x)),
+                         "f"(__uint_as_float(packed.y))
+                         : "memory");
+            return;
+        }
+        uint32_t k = (peers.mode & OE_PEER_WARP_ROTATE) ? (threadIdx.x >> 5) % peers.n : 0u;
+        for (uint32_t j = 0; j < peers.n; j++) {
             __stcs((uint2*)((char*)sh + peers.delta[k]) + vec_index, packed);
+            if (++k == peers.n) k = 0;
+        }
     } else {
         __stcs((uint2*)sh + vec_index, packed);
     }
@@ -137,6 +155,9 @@ template <int UNROLL, bool PEERS, bool SCALED>
 __device__ __forceinline__ void oe_adamw_body(const oe_dev_tensor* __restrict__ tensors,
                                               const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
                                               uint32_t chunk_elems, const oe_adamw_args& a, const oe_peer_set& peers) {
+    // Sharded step: an exchange between the ranks that gave up leaves a non-zero status word;
+    // every later launch of that step then does nothing (the word is uniform over the grid).
+    if (a.status != 0 && *(const volatile uint32_t*)a.status != 0u) return;
     oe_adamw_consts k;
     k.b1 = a.beta1;
     k.b2 = a.beta2;
@@ -316,6 +337,7 @@ template <bool SCALED, bool PEERS>
 __device__ __forceinline__ void oe_sgd_body(const oe_dev_tensor* __restrict__ tensors,
                                             const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks,
                                             uint32_t chunk_elems, const oe_sgd_args& a, const oe_peer_set& peers) {
+    if (a.status != 0 && *(const volatile uint32_t*)a.status != 0u) return;
     oe_sgd_consts k;
     k.momentum = a.momentum;
     k.one_minus_damp = __fsub_rn(1.0f, a.dampening);
@@ -649,11 +671,12 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
 // writes before it writes it, and no other rank reads that range of this buffer.
 // No flag or barrier is waited on here; ordering against the other ranks is the host's
 // job (stream-ordered collectives before and after).
-template <int NP, int U>
+template <int NP, int U, int ROT>
 __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
                                                     float* __restrict__ out, oe_dev_norm* rec, double* partials) {
     __shared__ double warp_sums[OE_THREADS / 32];
     __shared__ uint32_t is_last;
+    if (pg.status != 0 && *(const volatile uint32_t*)pg.status != 0u) return;  // a failed exchange: skip
     const uint32_t n = pg.n;
     const float scale = pg.scale;
     double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
@@ -676,9 +699,14 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const uint64_t i = i0 + (uint64_t)u * stride;
+                // Issue order: rank ROT first, then upwards and around (the host passes its own
+                // rank + 1, so the ranks of a step do not all address the same source first).
+                // The slot of a value is its rank, whatever the order of issue.
 #pragma unroll
-                for (int k = 0; k < NP; k++)
+                for (int kk = 0; kk < NP; kk++) {
+                    const int k = (kk + ROT) % NP;
                     if (k < (int)n && i < nvec) v[u][k] = __ldcg((const float4*)((const float*)pg.base[k] + first) + i);
+                }
             }
 #pragma unroll
             for (int u = 0; u < U; u++) {
@@ -739,11 +767,90 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
     }
 }
 
+// One body per first-issued rank; pg.rot is uniform over the grid, so the switch costs nothing.
+template <int NP, int U>
+__device__ __forceinline__ void oe_peer_reduce_dispatch(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
+                                                        float* __restrict__ out, oe_dev_norm* rec, double* partials) {
+    switch (pg.rot % NP) {
+        case 1: oe_peer_reduce_body<NP, U, 1 % NP>(pg, first, numel, out, rec, partials); break;
+        case 2: oe_peer_reduce_body<NP, U, 2 % NP>(pg, first, numel, out, rec, partials); break;
+        case 3: oe_peer_reduce_body<NP, U, 3 % NP>(pg, first, numel, out, rec, partials); break;
+        case 4: oe_peer_reduce_body<NP, U, 4 % NP>(pg, first, numel, out, rec, partials); break;
+        case 5: oe_peer_reduce_body<NP, U, 5 % NP>(pg, first, numel, out, rec, partials); break;
+        case 6: oe_peer_reduce_body<NP, U, 6 % NP>(pg, first, numel, out, rec, partials); break;
+        case 7: oe_peer_reduce_body<NP, U, 7 % NP>(pg, first, numel, out, rec, partials); break;
+        default: oe_peer_reduce_body<NP, U, 0>(pg, first, numel, out, rec, partials); break;
+    }
+}
+
 #define OE_PEER_REDUCE_VARIANT(name, np, unroll)                                                               \
     extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)                                       \
     name(const __grid_constant__ oe_peer_grads pg, uint64_t first, uint64_t numel, float* out, oe_dev_norm* rec, double* partials) { \
-        oe_peer_reduce_body<np, unroll>(pg, first, numel, out, rec, partials);                             \
+        oe_peer_reduce_dispatch<np, unroll>(pg, first, numel, out, rec, partials);                         \
     }
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2, 8)
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4, 4)
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n8, 8, 2)
+
+// ---------------------------------------------------------------------------------
+// sharded step: exchange between the ranks without a collective library
+// ---------------------------------------------------------------------------------
+// One warp. Lane k speaks to rank k: it publishes this rank's arrival (and, at the middle
+// exchange, its float64 partial sum of squares) in rank k's area with plain peer stores, then
+// waits until rank k's arrival shows in this rank's own area. The wait is bounded twice, by the
+// device clock and by a poll count: when either runs out the lane records which rank was
+// missing in the sticky status word and the kernel returns; nothing spins for ever. After the
+// middle exchange lane 0 adds the partial sums in rank order, so every rank computes the same
+// total and the same norm, bit for bit.
+__device__ __forceinline__ uint32_t oe_ld_acquire_sys(const uint32_t* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void oe_st_release_sys(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint64_t oe_globaltimer() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+extern "C" __global__ void __launch_bounds__(32, 1) oe_rank_exchange(const __grid_constant__ oe_sync_args a) {
+    const uint32_t lane = threadIdx.x;
+    oe_sync_block* own = (oe_sync_block*)a.block[a.rank];
+    oe_dev_norm* rec = (oe_dev_norm*)a.norm_rec;
+    if (*(volatile uint32_t*)&own->status != 0u) return;  // an earlier exchange already gave up
+    const uint32_t parity = a.epoch & 1u;
+    bool failed = false;
+    if (lane < a.world) {
+        oe_sync_block* theirs = (oe_sync_block*)a.block[lane];
+        if (rec != nullptr) theirs->partial[parity][a.rank] = *(volatile double*)&rec->sumsq;
+        // the stores of the kernels before this one on the stream, and the partial above, come first
+        __threadfence_system();
+        oe_st_release_sys(&theirs->arrive[a.phase][a.rank], a.epoch);
+        const uint32_t* flag = &own->arrive[a.phase][lane];
+        const uint64_t t0 = oe_globaltimer();
+        uint32_t polls = 0;
+        while ((int32_t)(oe_ld_acquire_sys(flag) - a.epoch) < 0) {
+            if (++polls >= a.max_polls || oe_globaltimer() - t0 > a.timeout_ns) {
+                failed = true;
+                break;
+            }
+            __nanosleep(polls < 64 ? 100 : 1000);
+        }
+        if (failed) atomicCAS(&own->status, 0u, OE_SYNC_TIMEOUT | (a.phase << 8) | (lane << 16));
+    }
+    const bool any_failed = __any_sync(0xffffffffu, failed);
+    __syncwarp();  // what the other lanes acquired is ordered before lane 0's reads below
+    if (lane == 0 && rec != nullptr) {
+        if (any_failed) {
+            rec->error = OE_SYNC_TIMEOUT;
+        } else {
+            double total = 0.0;
+            for (uint32_t r = 0; r < a.world; r++) total += *(volatile double*)&own->partial[parity][r];
+            rec->sumsq = total;
+            rec->norm = (float)sqrt(total);
+        }
+    }
+}

@@ -54,7 +54,7 @@ struct KernelSet {
     CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
     CUfunction adamw_peers = nullptr, sgd_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
     CUfunction step_increment = nullptr, sgd = nullptr, sumsq = nullptr, norm_finalize = nullptr,
-               scale = nullptr, zero = nullptr, cast = nullptr;
+               scale = nullptr, zero = nullptr, cast = nullptr, rank_exchange = nullptr;
 };
 const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2", "oe_adamw_fused_u8"};
 const char* const kVariantKeys[4] = {"", "u1", "u2", "u8"};
@@ -74,6 +74,7 @@ struct DeviceCtx {
 
 std::mutex g_mu;
 DeviceCtx g_dev[kMaxDevices];
+std::atomic<int> g_live_plans{0};  // plans hold their device's context and kernel handles
 std::map<std::string, int64_t> g_launches;
 
 // Pushes the device's primary context for the lifetime of the guard and pops it
@@ -103,7 +104,12 @@ DeviceCtx* device_or_fail(int device, int* rc) {
         return nullptr;
     }
     DeviceCtx* dc = &g_dev[device];
-    if (!dc->ready) {
+    bool ready;
+    {
+        std::lock_guard<std::mutex> lock(g_mu);
+        ready = dc->ready;
+    }
+    if (!ready) {
         *rc = fail(OE_ERR_NOT_INIT, "oe_init was not called for device " + std::to_string(device));
         return nullptr;
     }
@@ -174,6 +180,10 @@ struct oe_plan {
     CUevent staged = nullptr;
     bool staged_pending = false;
     int64_t uploads = 0;
+    bool tables_valid = false;  // the device tables describe `descs`; false after a failed update
+    // tuning knobs of the peer kernels (0 = the library's choice); none changes a result
+    uint32_t tune_reduce_grid = 0, tune_update_grid = 0, tune_reduce_first = 0, tune_push_warp_rotate = 0;
+    uint64_t status_word = 0;   // device address of a sharded step's status word, 0 = none
 };
 
 namespace {
@@ -242,19 +252,24 @@ void count_active(oe_plan* p) {
 // Makes room for the current tables on the device and in the staging buffer. Only
 // called outside stream capture paths that must not allocate: capacities never shrink.
 int ensure_capacity(const oe_driver* d, oe_plan* p) {
+    // A table that has to grow is allocated before the old one is released, and the plan's
+    // fields change only once the new allocation exists: a failed allocation leaves the plan
+    // exactly as it was (capacities, addresses and all).
     size_t need_t = p->n_active ? p->n_active : 1, need_c = p->n_chunks ? p->n_chunks : 1;
     if (need_t > p->cap_tensors) {
-        if (p->d_tensors) OE_CU(d->cuMemFree_(p->d_tensors), "cuMemFree(tensor table)");
-        p->d_tensors = 0;
         size_t cap = need_t + need_t / 4 + 8;
-        OE_CU(d->cuMemAlloc_(&p->d_tensors, cap * sizeof(oe_dev_tensor)), "cuMemAlloc(tensor table)");
+        CUdeviceptr fresh = 0;
+        OE_CU(d->cuMemAlloc_(&fresh, cap * sizeof(oe_dev_tensor)), "cuMemAlloc(tensor table)");
+        if (p->d_tensors) d->cuMemFree_(p->d_tensors);
+        p->d_tensors = fresh;
         p->cap_tensors = cap;
     }
     if (need_c > p->cap_chunks) {
-        if (p->d_chunks) OE_CU(d->cuMemFree_(p->d_chunks), "cuMemFree(chunk table)");
-        p->d_chunks = 0;
         size_t cap = need_c + need_c / 4 + 64;
-        OE_CU(d->cuMemAlloc_(&p->d_chunks, cap * sizeof(oe_dev_chunk)), "cuMemAlloc(chunk table)");
+        CUdeviceptr fresh = 0;
+        OE_CU(d->cuMemAlloc_(&fresh, cap * sizeof(oe_dev_chunk)), "cuMemAlloc(chunk table)");
+        if (p->d_chunks) d->cuMemFree_(p->d_chunks);
+        p->d_chunks = fresh;
         p->cap_chunks = cap;
     }
     size_t bytes = p->cap_tensors * sizeof(oe_dev_tensor) + p->cap_chunks * sizeof(oe_dev_chunk);
@@ -263,15 +278,19 @@ int ensure_capacity(const oe_driver* d, oe_plan* p) {
             OE_CU(d->cuEventSynchronize_(p->staged), "cuEventSynchronize(table upload)");
             p->staged_pending = false;
         }
-        if (p->h_stage) OE_CU(d->cuMemFreeHost_(p->h_stage), "cuMemFreeHost(staging)");
-        p->h_stage = nullptr;
-        OE_CU(d->cuMemAllocHost_(&p->h_stage, bytes), "cuMemAllocHost(staging)");
+        void* fresh = nullptr;
+        OE_CU(d->cuMemAllocHost_(&fresh, bytes), "cuMemAllocHost(staging)");
+        if (p->h_stage) d->cuMemFreeHost_(p->h_stage);
+        p->h_stage = fresh;
         p->h_stage_bytes = bytes;
     }
     return 0;
 }
 
 int upload_tables(const oe_driver* d, oe_plan* p, CUstream stream) {
+    // From here until the copies are enqueued the device tables may describe neither the old nor
+    // the new descriptors: every launch path refuses a plan whose tables are not valid.
+    p->tables_valid = false;
     int rc = ensure_capacity(d, p);
     if (rc) return rc;
     if (p->staged_pending) {
@@ -291,7 +310,17 @@ int upload_tables(const oe_driver* d, oe_plan* p, CUstream stream) {
         p->staged_pending = true;
     }
     p->uploads++;
+    p->tables_valid = true;
     return 0;
+}
+
+uint32_t grid_for(const oe_plan* p, int occupancy);
+
+// Grid of an update launch that also stores into the peers' buffers: the tuned size when one is set.
+uint32_t peer_update_grid(const oe_plan* p, int occupancy) {
+    uint32_t g = grid_for(p, occupancy);
+    if (p->tune_update_grid && p->tune_update_grid < g) g = p->tune_update_grid;
+    return g;
 }
 
 uint32_t grid_for(const oe_plan* p, int occupancy) {
@@ -311,6 +340,7 @@ void destroy_plan(const oe_driver* d, oe_plan* p) {
     if (p->d_norm) d->cuMemFree_(p->d_norm);
     if (p->d_partials) d->cuMemFree_(p->d_partials);
     delete p;
+    g_live_plans.fetch_sub(1);
 }
 
 // Work-unit size when the caller leaves it to the library. Sets that stream from HBM use
@@ -388,6 +418,7 @@ extern "C" int oe_init(int device) {
         {&dc->k.sumsq, "oe_grad_sumsq", &dc->occ_sumsq},
         {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
         {&dc->k.zero, "oe_zero_grads", &dc->occ_zero},         {&dc->k.cast, "oe_cast_bf16", &dc->occ_cast},
+        {&dc->k.rank_exchange, "oe_rank_exchange", nullptr},
     };
     for (auto& e : table) {
         r = d->cuModuleGetFunction_(e.f, dc->module, e.name);
@@ -409,6 +440,8 @@ extern "C" int oe_shutdown(void) {
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
+    if (g_live_plans.load() > 0)
+        return fail(OE_ERR_INVALID, "oe_shutdown: " + std::to_string(g_live_plans.load()) + " plan(s) still alive; destroy them first");
     std::lock_guard<std::mutex> lock(g_mu);
     for (DeviceCtx& dc : g_dev) {
         if (!dc.ready) continue;
@@ -446,6 +479,7 @@ extern "C" int oe_plan_create(int device, const oe_tensor_desc* tensors, uint32_
     if ((rc = validate_descs(tensors, n_tensors, chunk_elems)) != 0) return rc;
     oe_plan* p = new (std::nothrow) oe_plan();
     if (!p) return fail(OE_ERR_INVALID, "out of host memory");
+    g_live_plans.fetch_add(1);
     p->dc = dc;
     p->chunk_elems = chunk_elems;
     p->descs.assign(tensors, tensors + n_tensors);
@@ -485,12 +519,21 @@ extern "C" int oe_plan_update(oe_plan* plan, const oe_tensor_desc* tensors, uint
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
-    if (same_descs(plan->descs, tensors, n_tensors)) return 0;
+    if (plan->tables_valid && same_descs(plan->descs, tensors, n_tensors)) return 0;
     if ((rc = validate_descs(tensors, n_tensors, plan->chunk_elems)) != 0) return rc;
+    // The new descriptors are adopted only together with their uploaded tables. When a driver call
+    // fails on the way, the plan keeps no descriptors at all: the next update (with any list, the
+    // same one included) uploads again, and until one succeeds every launch is refused.
     plan->descs.assign(tensors, tensors + n_tensors);
     count_active(plan);
     CtxGuard guard(d, plan->dc->ctx);
-    return upload_tables(d, plan, (CUstream)stream);
+    rc = upload_tables(d, plan, (CUstream)stream);
+    if (rc) {
+        plan->descs.clear();
+        count_active(plan);
+        plan->tables_valid = false;
+    }
+    return rc;
 }
 
 extern "C" int oe_plan_destroy(oe_plan* plan) {
@@ -537,6 +580,18 @@ extern "C" int oe_plan_set_grad_scale(oe_plan* plan, const float* scale) {
     return 0;
 }
 
+extern "C" int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value) {
+    if (!plan) return fail(OE_ERR_INVALID, "plan is NULL");
+    if (value > 0x7fffffffull) return fail(OE_ERR_INVALID, "oe_plan_set_tuning: value out of range");
+    switch (what) {
+        case OE_TUNE_PEER_REDUCE_GRID: plan->tune_reduce_grid = (uint32_t)value; return 0;
+        case OE_TUNE_PEER_UPDATE_GRID: plan->tune_update_grid = (uint32_t)value; return 0;
+        case OE_TUNE_PEER_REDUCE_FIRST: plan->tune_reduce_first = (uint32_t)value % OE_MAX_PEERS; return 0;
+        case OE_TUNE_PEER_PUSH_WARP_ROTATE: plan->tune_push_warp_rotate = value ? 1u : 0u; return 0;
+        default: return fail(OE_ERR_INVALID, "oe_plan_set_tuning: unknown knob");
+    }
+}
+
 // -------------------------------------------------------------------------------------
 // norm and clip
 // -------------------------------------------------------------------------------------
@@ -551,8 +606,12 @@ int launch_sumsq(const oe_driver* d, oe_plan* p, uint32_t flags, CUstream stream
     return launch(d, p->dc->k.sumsq, "oe_grad_sumsq", grid, kThreads, stream, args);
 }
 
+// Every launch path passes through here: a plan whose last table upload failed has no usable
+// tables, and a grid dimension (oe_zero_grads launches one CTA per work unit) ends at 2^31-1.
 int check_chunk_count(const oe_plan* p) {
-    if (p->n_chunks > 0xffffffffull) return fail(OE_ERR_LIMIT, "plan has more than 2^32-1 chunks; use a larger chunk_elems");
+    if (!p->tables_valid)
+        return fail(OE_ERR_INVALID, "the plan's device tables are stale (the last oe_plan_update failed); update the plan again");
+    if (p->n_chunks > 0x7fffffffull) return fail(OE_ERR_LIMIT, "plan has more than 2^31-1 work units; use a larger chunk_elems");
     return 0;
 }
 }  // namespace
@@ -658,6 +717,7 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     a.lr_dev = hp->lr_dev;
     a.grad_scale = p->grad_scale;
     a.ticket = (uint64_t)p->d_norm + offsetof(oe_dev_norm, step_ticket);
+    a.status = peers ? p->status_word : 0;
     uint32_t n_chunks = (uint32_t)p->n_chunks, chunk_elems = p->chunk_elems;
     CUdeviceptr chunk_table = p->d_chunks;
     if (range_chunks != UINT64_MAX) {  // a contiguous range of the chunk table
@@ -667,9 +727,10 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     }
     if (peers) {
         oe_peer_set ps = *peers;
+        if (p->tune_push_warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
         void* peer_args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a, &ps};
-        return launch(d, p->dc->k.adamw_peers, "oe_adamw_fused_peers", grid_for(p, p->dc->occ_adamw_peers), kThreads,
-                      stream, peer_args);
+        return launch(d, p->dc->k.adamw_peers, "oe_adamw_fused_peers", peer_update_grid(p, p->dc->occ_adamw_peers),
+                      kThreads, stream, peer_args);
     }
     uint32_t grid = grid_for(p, p->dc->occ_adamw[p->variant]);
     if (grid > n_chunks) grid = n_chunks;
@@ -703,7 +764,7 @@ extern "C" int oe_adamw_step_chunks(oe_plan* plan, const oe_adamw_hparams* hp, u
 }
 
 namespace {
-int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_peer_set* peers) {
+int validate_sgd(const oe_plan* plan, const oe_sgd_hparams* hp) {
     if (!plan || !hp) return fail(OE_ERR_INVALID, "plan or hyper-parameters are NULL");
     // SGDOptions.validate (autograd/sgd.go:21-31)
     for (float v : {hp->lr, hp->momentum, hp->dampening})
@@ -718,11 +779,15 @@ int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_
             if (x.grad != 0 && (x.state1 == 0 || x.state2 == 0))
                 return fail(OE_ERR_INVALID, "incomplete SGD device storage: momentum needs a buffer and a flag per parameter");
     }
-    int rc = 0;
+    if ((hp->step_dev | hp->lr_dev) & 3u) return fail(OE_ERR_INVALID, "step_dev / lr_dev not 4-byte aligned");
+    return check_chunk_count(plan);
+}
+
+int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_peer_set* peers) {
+    int rc = validate_sgd(plan, hp);
+    if (rc) return rc;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
-    if ((rc = check_chunk_count(plan)) != 0) return rc;
-    if ((hp->step_dev | hp->lr_dev) & 3u) return fail(OE_ERR_INVALID, "step_dev / lr_dev not 4-byte aligned");
     CtxGuard guard(d, plan->dc->ctx);
     if (plan->n_chunks == 0) {
         if (!hp->step_dev) return 0;
@@ -743,18 +808,21 @@ int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_
     a.step_dev = hp->step_dev;
     a.ticket = (uint64_t)plan->d_norm + offsetof(oe_dev_norm, step_ticket);
     a.n_tensors = plan->n_active;
+    a.status = peers ? plan->status_word : 0;
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     if (peers) {
         oe_peer_set ps = *peers;
+        if (plan->tune_push_warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
         void* peer_args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a, &ps};
-        return launch(d, plan->dc->k.sgd_peers, "oe_sgd_fused_peers", grid_for(plan, plan->dc->occ_sgd_peers), kThreads,
-                      (CUstream)stream, peer_args);
+        return launch(d, plan->dc->k.sgd_peers, "oe_sgd_fused_peers", peer_update_grid(plan, plan->dc->occ_sgd_peers),
+                      kThreads, (CUstream)stream, peer_args);
     }
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
     return launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
 }
 
-int peer_set_from(const int64_t* shadow_deltas, uint32_t n_ranks, const char* who, oe_peer_set* ps) {
+int peer_set_from(const int64_t* shadow_deltas, uint32_t n_ranks, const char* who, oe_peer_set* ps,
+                  const int64_t* mc_delta = nullptr) {
     if (!shadow_deltas) return fail(OE_ERR_INVALID, std::string(who) + ": NULL argument");
     if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, std::string(who) + ": 1 to 8 ranks are supported");
     memset(ps, 0, sizeof(*ps));
@@ -764,6 +832,11 @@ int peer_set_from(const int64_t* shadow_deltas, uint32_t n_ranks, const char* wh
         // an 8-byte store needs every target as aligned as the local one
         if (shadow_deltas[k] & 7) return fail(OE_ERR_INVALID, std::string(who) + ": shadow buffers must be mutually 8-byte aligned");
         ps->delta[k] = shadow_deltas[k];
+    }
+    if (mc_delta) {
+        if (*mc_delta == 0 || (*mc_delta & 7)) return fail(OE_ERR_INVALID, std::string(who) + ": bad distance to the multicast mapping");
+        ps->mode |= OE_PEER_MULTICAST;
+        ps->mc_delta = *mc_delta;
     }
     return 0;
 }
@@ -1020,6 +1093,8 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     pg.n = n_ranks;
     pg.flags = flags;
     pg.scale = *scale;
+    pg.rot = plan->tune_reduce_first;
+    pg.status = plan->status_word;
     for (uint32_t k = 0; k < n_ranks; k++) {
         if (rank_bases[k] == 0 || (rank_bases[k] & 3u)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad gradient base of rank " + std::to_string(k));
         pg.base[k] = rank_bases[k];
@@ -1037,6 +1112,7 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_peer_reduce[which] > 0 ? dc->occ_peer_reduce[which] : 1);
     uint64_t grid = blocks < persistent ? blocks : persistent;
     if (grid > plan->max_grid) grid = plan->max_grid;
+    if (plan->tune_reduce_grid && plan->tune_reduce_grid < grid) grid = plan->tune_reduce_grid;
     if (grid == 0) grid = 1;
     void* args[] = {&pg, &first_elem, &numel, &out, &plan->d_norm, &plan->d_partials};
     return launch(d, dc->k.peer_reduce[which], names[which], (uint32_t)grid, kThreads, (CUstream)stream, args);
@@ -1053,6 +1129,161 @@ extern "C" int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, co
     if ((rc = validate_adamw(plan, hp)) != 0) return rc;
     CtxGuard guard(d, plan->dc->ctx);
     return launch_adamw(d, plan, hp, (CUstream)stream, &ps);
+}
+
+extern "C" int oe_adamw_step_multicast(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
+                                       uint32_t n_ranks, const int64_t* mc_delta, uint64_t stream) {
+    if (!plan || !mc_delta) return fail(OE_ERR_INVALID, "oe_adamw_step_multicast: NULL argument");
+    oe_peer_set ps;
+    int rc = peer_set_from(shadow_deltas, n_ranks, "oe_adamw_step_multicast", &ps, mc_delta);
+    if (rc) return rc;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if ((rc = validate_adamw(plan, hp)) != 0) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_adamw(d, plan, hp, (CUstream)stream, &ps);
+}
+
+extern "C" int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const int64_t* shadow_deltas,
+                                     uint32_t n_ranks, const int64_t* mc_delta, uint64_t stream) {
+    if (!mc_delta) return fail(OE_ERR_INVALID, "oe_sgd_step_multicast: NULL argument");
+    oe_peer_set ps;
+    int rc = peer_set_from(shadow_deltas, n_ranks, "oe_sgd_step_multicast", &ps, mc_delta);
+    if (rc) return rc;
+    return sgd_step(plan, hp, stream, &ps);
+}
+
+// -------------------------------------------------------------------------------------
+// sharded step driven by the library alone: the exchanges between the ranks are kernels too
+// -------------------------------------------------------------------------------------
+struct oe_zero1 {
+    oe_plan* plan = nullptr;
+    oe_zero1_desc desc;
+    uint32_t epoch = 0;
+    float mean_scale = 1.0f;
+};
+
+namespace {
+int launch_exchange(const oe_driver* d, oe_zero1* z, uint32_t phase, bool with_norm, CUstream stream) {
+    oe_sync_args a;
+    memset(&a, 0, sizeof(a));
+    a.rank = z->desc.rank;
+    a.world = z->desc.world;
+    a.phase = phase;
+    a.epoch = z->epoch;
+    for (uint32_t k = 0; k < OE_MAX_PEERS; k++) a.block[k] = z->desc.sync_blocks[k < z->desc.world ? k : z->desc.rank];
+    a.norm_rec = with_norm ? (uint64_t)z->plan->d_norm : 0;
+    uint64_t ms = z->desc.timeout_ms ? z->desc.timeout_ms : 10000u;
+    a.timeout_ns = ms * 1000000ull;
+    uint64_t polls = ms * 4000ull;  // a poll takes a microsecond or so once the wait backs off
+    a.max_polls = polls > 0x7fffffffull ? 0x7fffffffu : (uint32_t)polls;
+    void* args[] = {&a};
+    return launch(d, z->plan->dc->k.rank_exchange, "oe_rank_exchange", 1, 32, stream, args);
+}
+
+int zero1_step(oe_zero1* z, const oe_adamw_hparams* ahp, const oe_sgd_hparams* shp, uint64_t stream) {
+    if (!z || (!ahp && !shp)) return fail(OE_ERR_INVALID, "oe_zero1 step: NULL argument");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    oe_plan* plan = z->plan;
+    // everything that can be refused is checked before the first launch of the step
+    if (ahp && (rc = validate_adamw(plan, ahp)) != 0) return rc;
+    if (shp && (rc = validate_sgd(plan, shp)) != 0) return rc;
+    const oe_zero1_desc& D = z->desc;
+    CUstream s = (CUstream)stream;
+    z->epoch += 1;
+    {
+        CtxGuard guard(d, plan->dc->ctx);
+        if (!(D.flags & OE_ZERO1_NO_ENTRY_EXCHANGE) && (rc = launch_exchange(d, z, OE_SYNC_GRADS_READY, false, s)) != 0) return rc;
+    }
+    uint64_t out = D.grad_bases[D.rank] + 4ull * D.first_elem;
+    if ((rc = oe_peer_reduce_grads(plan, D.grad_bases, D.world, D.first_elem, D.numel, out, &z->mean_scale, OE_PARTIAL_ONLY,
+                                   stream)) != 0)
+        return rc;
+    {
+        CtxGuard guard(d, plan->dc->ctx);
+        if ((rc = launch_exchange(d, z, OE_SYNC_REDUCED, true, s)) != 0) return rc;
+    }
+    const int64_t* mc = D.shadow_mc_delta ? &D.shadow_mc_delta : nullptr;
+    if (ahp)
+        rc = mc ? oe_adamw_step_multicast(plan, ahp, D.shadow_deltas, D.world, mc, stream)
+                : oe_adamw_step_peers(plan, ahp, D.shadow_deltas, D.world, stream);
+    else
+        rc = mc ? oe_sgd_step_multicast(plan, shp, D.shadow_deltas, D.world, mc, stream)
+                : oe_sgd_step_peers(plan, shp, D.shadow_deltas, D.world, stream);
+    if (rc) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    return launch_exchange(d, z, OE_SYNC_PUSHED, false, s);
+}
+}  // namespace
+
+extern "C" int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero1** out) {
+    if (!out) return fail(OE_ERR_INVALID, "out is NULL");
+    *out = nullptr;
+    if (!plan || !desc) return fail(OE_ERR_INVALID, "oe_zero1_create: NULL argument");
+    if (desc->world < 1 || desc->world > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_zero1_create: 1 to 8 ranks are supported");
+    if (desc->rank >= desc->world) return fail(OE_ERR_INVALID, "oe_zero1_create: rank out of range");
+    if (desc->flags & ~OE_ZERO1_NO_ENTRY_EXCHANGE) return fail(OE_ERR_INVALID, "oe_zero1_create: unknown flag");
+    for (uint32_t k = 0; k < desc->world; k++) {
+        if (desc->grad_bases[k] == 0 || (desc->grad_bases[k] & 3u))
+            return fail(OE_ERR_INVALID, "oe_zero1_create: bad gradient base of rank " + std::to_string(k));
+        if (desc->sync_blocks[k] == 0 || (desc->sync_blocks[k] & 255u))
+            return fail(OE_ERR_INVALID, "oe_zero1_create: exchange area of rank " + std::to_string(k) + " missing or not 256-byte aligned");
+        if (desc->shadow_deltas[k] & 7) return fail(OE_ERR_INVALID, "oe_zero1_create: shadow buffers must be mutually 8-byte aligned");
+    }
+    if (desc->shadow_deltas[desc->rank] != 0) return fail(OE_ERR_INVALID, "oe_zero1_create: the rank's own shadow distance must be 0");
+    if (plan->status_word != 0) return fail(OE_ERR_INVALID, "oe_zero1_create: the plan already drives a sharded step");
+    oe_zero1* z = new (std::nothrow) oe_zero1();
+    if (!z) return fail(OE_ERR_INVALID, "out of host memory");
+    z->plan = plan;
+    z->desc = *desc;
+    z->mean_scale = (float)(1.0 / (double)desc->world);
+    plan->status_word = desc->sync_blocks[desc->rank] + offsetof(oe_sync_block, status);
+    *out = z;
+    return 0;
+}
+
+extern "C" int oe_zero1_destroy(oe_zero1* z) {
+    if (!z) return 0;
+    if (z->plan) z->plan->status_word = 0;
+    delete z;
+    return 0;
+}
+
+extern "C" int oe_zero1_adamw_step(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream) {
+    return zero1_step(z, hp, nullptr, stream);
+}
+
+extern "C" int oe_zero1_sgd_step(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream) {
+    return zero1_step(z, nullptr, hp, stream);
+}
+
+extern "C" int oe_zero1_exchange(oe_zero1* z, uint32_t phase, uint64_t stream) {
+    if (!z) return fail(OE_ERR_INVALID, "oe_zero1_exchange: NULL argument");
+    if (phase >= OE_SYNC_PHASES) return fail(OE_ERR_INVALID, "oe_zero1_exchange: unknown phase");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    if (phase == OE_SYNC_GRADS_READY) z->epoch += 1;  // a step begins with this exchange
+    CtxGuard guard(d, z->plan->dc->ctx);
+    return launch_exchange(d, z, phase, phase == OE_SYNC_REDUCED, (CUstream)stream);
+}
+
+extern "C" int oe_zero1_status(oe_zero1* z, uint32_t* status_out, uint64_t stream) {
+    if (!z || !status_out) return fail(OE_ERR_INVALID, "oe_zero1_status: NULL argument");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    CtxGuard guard(d, z->plan->dc->ctx);
+    uint32_t word = 0;
+    OE_CU(d->cuMemcpyDtoHAsync_(&word, (CUdeviceptr)z->plan->status_word, sizeof(word), (CUstream)stream), "cuMemcpyDtoHAsync(status)");
+    OE_CU(d->cuStreamSynchronize_((CUstream)stream), "cuStreamSynchronize");
+    *status_out = word;
+    if (word != 0)
+        return fail(OE_ERR_DEVICE, "sharded step: rank " + std::to_string((word >> 16) & 0xff) + " did not arrive at exchange " +
+                                       std::to_string((word >> 8) & 0xff) + " within the limit; the step's later launches did nothing");
+    return 0;
 }
 
 extern "C" int oe_ipc_export(int device, uint64_t address, void* handle_out, uint64_t* offset_out) {

@@ -52,6 +52,7 @@ typedef struct oe_adamw_args {
     float grad_scale; /* every gradient element is read as (float)(g * grad_scale) */
     uint32_t pad;
     uint64_t ticket;  /* uint32_t* arrival counter used to advance *step_dev (capture mode) */
+    uint64_t status;  /* const uint32_t* or 0: a non-zero word (a failed exchange between ranks) skips the launch */
 } oe_adamw_args;
 
 typedef struct oe_sgd_args {
@@ -65,6 +66,7 @@ typedef struct oe_sgd_args {
     uint64_t ticket;  /* uint32_t* arrival counter: the last CTA marks the momentum buffers initialised */
     uint32_t n_tensors; /* rows of the tensor table */
     uint32_t pad;
+    uint64_t status;  /* as in oe_adamw_args */
 } oe_sgd_args;
 
 /* Ranks of a sharded step: byte distance from this rank's buffer to rank k's buffer of the
@@ -72,18 +74,49 @@ typedef struct oe_sgd_args {
 #define OE_MAX_PEERS 8
 typedef struct oe_peer_set {
     uint32_t n;
-    uint32_t pad;
+    uint32_t mode;    /* OE_PEER_* bits */
     int64_t delta[OE_MAX_PEERS];
+    int64_t mc_delta; /* OE_PEER_MULTICAST: byte distance to a multicast mapping of the buffer */
 } oe_peer_set;
+#define OE_PEER_MULTICAST 0x1u /* 8-byte vectors go out as one multimem.st through mc_delta, replicated to
+                                  every rank by the switch; single elements still take the plain stores */
+#define OE_PEER_WARP_ROTATE 0x2u /* warp w of a CTA starts its round of stores at target w mod n       */
 
 /* Arguments of the pull-reduce kernel: rank k's gradient buffer base, as seen from this GPU. */
 typedef struct oe_peer_grads {
     uint32_t n;
     uint32_t flags;
     float scale;      /* multiplies the fixed-order sum (1/n for a mean, 1 for a sum) */
-    uint32_t pad;
+    uint32_t rot;     /* the loads of one element are issued starting at rank `rot`; the adds keep rank order */
     uint64_t base[OE_MAX_PEERS];
+    uint64_t status;  /* const uint32_t* or 0: a non-zero word skips the launch */
 } oe_peer_grads;
+
+/* Exchange area of one rank of a sharded step: 512 bytes of device memory, zero before the first
+ * step, mapped by every other rank. Rank r announces that it reached point `phase` of step `epoch`
+ * by storing the epoch into arrive[phase][r] of EVERY rank's area (its own included) and then waits,
+ * with a limit, until its own area shows that epoch in every column. The middle exchange also
+ * carries each rank's float64 partial sum of squares. */
+#define OE_SYNC_PHASES 4
+#define OE_SYNC_GRADS_READY 0  /* this rank's gradients are complete: the others may pull them      */
+#define OE_SYNC_REDUCED     1  /* this rank's pull is over and its partial sum is published          */
+#define OE_SYNC_PUSHED      2  /* this rank's shadow stores are performed on every GPU               */
+typedef struct oe_sync_block {
+    uint32_t arrive[OE_SYNC_PHASES][OE_MAX_PEERS]; /* 128 B */
+    double partial[2][OE_MAX_PEERS];               /* 128 B, indexed by epoch parity */
+    uint32_t status;   /* sticky: OE_SYNC_TIMEOUT | phase << 8 | first missing rank << 16; 0 = fine */
+    uint32_t pad[63];
+} oe_sync_block;
+#define OE_SYNC_TIMEOUT 0x1u
+
+typedef struct oe_sync_args {
+    uint32_t rank, world, phase, epoch;
+    uint64_t block[OE_MAX_PEERS]; /* every rank's oe_sync_block as mapped on this GPU */
+    uint64_t norm_rec;            /* oe_dev_norm* for OE_SYNC_REDUCED (partial in, total and norm out), else 0 */
+    uint64_t timeout_ns;          /* the wait gives up after this long ...                     */
+    uint32_t max_polls;           /* ... or after this many polls, whichever comes first      */
+    uint32_t pad;
+} oe_sync_args;
 
 /* flag bits shared with include/optengine.h */
 #define OE_F_CLIP_DEVFORM 0x1u  /* coefficient = fminf(1, max/(norm+1e-6)) instead of the host rule */

@@ -6,6 +6,8 @@ from dataclasses import dataclass
 from typing import Optional, Sequence
 
 from . import _lib
+from ._lib import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_REDUCE_GRID,
+                   OE_TUNE_PEER_UPDATE_GRID, OE_ZERO1_NO_ENTRY_EXCHANGE, OE_ZERO1_SYNC_BYTES)
 from ._lib import (OE_ACCUMULATE, OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,
                    EngineError, check, lib)
 
@@ -180,6 +182,23 @@ class Plan:
         deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
         check(lib().oe_sgd_step_peers(self._h, C.byref(c), deltas, len(shadow_deltas), _stream(stream)))
 
+    def adamw_step_multicast(self, hp: AdamWHParams, shadow_deltas: Sequence[int], mc_delta: int, stream=None) -> None:
+        """oe_adamw_step_peers with the 8-byte shadow vectors sent once through a multicast mapping."""
+        c = hp.to_c()
+        deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
+        check(lib().oe_adamw_step_multicast(self._h, C.byref(c), deltas, len(shadow_deltas),
+                                            C.byref(C.c_int64(mc_delta)), _stream(stream)))
+
+    def sgd_step_multicast(self, hp: SGDHParams, shadow_deltas: Sequence[int], mc_delta: int, stream=None) -> None:
+        c = hp.to_c()
+        deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
+        check(lib().oe_sgd_step_multicast(self._h, C.byref(c), deltas, len(shadow_deltas),
+                                          C.byref(C.c_int64(mc_delta)), _stream(stream)))
+
+    def set_tuning(self, what: int, value: int) -> None:
+        """A launch-shape knob of the peer kernels (oe_plan_set_tuning); results never change."""
+        check(lib().oe_plan_set_tuning(self._h, what, value))
+
     def zero_grads(self, stream=None) -> None:
         check(lib().oe_zero_grads(self._h, _stream(stream)))
 
@@ -239,6 +258,52 @@ def ipc_import(handle: bytes, device: int = 0) -> int:
 
 def ipc_close(base: int, device: int = 0) -> None:
     check(lib().oe_ipc_close(device, base))
+
+
+class Zero1Context:
+    """oe_zero1: a sharded step whose exchanges between the ranks are the library's own kernels."""
+
+    def __init__(self, plan: Plan, rank: int, world: int, first_elem: int, numel: int, grad_bases: Sequence[int],
+                 shadow_deltas: Sequence[int], sync_blocks: Sequence[int], mc_delta: int = 0, timeout_ms: int = 0,
+                 flags: int = 0):
+        d = _lib.oe_zero1_desc()
+        d.rank, d.world, d.first_elem, d.numel = rank, world, first_elem, numel
+        for k in range(world):
+            d.grad_bases[k], d.shadow_deltas[k], d.sync_blocks[k] = grad_bases[k], shadow_deltas[k], sync_blocks[k]
+        d.shadow_mc_delta, d.timeout_ms, d.flags = mc_delta, timeout_ms, flags
+        self._plan = plan  # the context borrows the plan
+        self._h = C.c_void_p()
+        check(lib().oe_zero1_create(plan._h, C.byref(d), C.byref(self._h)))
+
+    def adamw_step(self, hp: AdamWHParams, stream=None) -> None:
+        c = hp.to_c()
+        check(lib().oe_zero1_adamw_step(self._h, C.byref(c), _stream(stream)))
+
+    def sgd_step(self, hp: SGDHParams, stream=None) -> None:
+        c = hp.to_c()
+        check(lib().oe_zero1_sgd_step(self._h, C.byref(c), _stream(stream)))
+
+    def exchange(self, phase: int, stream=None) -> None:
+        check(lib().oe_zero1_exchange(self._h, phase, _stream(stream)))
+
+    def status(self, stream=None) -> int:
+        """Waits for the stream; 0 when every exchange completed, else raises EngineError (OE_ERR_DEVICE)."""
+        word = C.c_uint32()
+        check(lib().oe_zero1_status(self._h, C.byref(word), _stream(stream)))
+        return int(word.value)
+
+    def status_word(self, stream=None) -> int:
+        """The raw status word, without raising."""
+        word = C.c_uint32()
+        code = lib().oe_zero1_status(self._h, C.byref(word), _stream(stream))
+        if code not in (0, _lib.OE_ERR_DEVICE):
+            check(code)
+        return int(word.value)
+
+    def close(self) -> None:
+        if self._h:
+            check(lib().oe_zero1_destroy(self._h))
+            self._h = C.c_void_p()
 
 
 def launch_count(name: Optional[str] = None) -> int:

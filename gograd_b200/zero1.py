@@ -10,7 +10,7 @@ v exist only on the rank that owns their shard. One step:
     3. fused AdamW on the shard with the clip coefficient folded in
     4. all-gather of the bf16 shadows
 
-Two data paths do this:
+Three ways to run it (`comm`):
 
   "peer"  hand-written kernels over peer-mapped memory (CUDA IPC, plain loads/stores):
           step 1+2 are ONE kernel (each rank pulls its shard from every rank, adds in
@@ -18,8 +18,16 @@ Two data paths do this:
           ONE kernel (the update stores each bf16 value into every rank's shadow buffer).
           The only library collective is the 8-byte all-reduce, which also orders the
           ranks: nothing in the kernels waits on another GPU.
+  "abi"   the same two kernels, but the three points where the ranks meet are the library's own
+          exchange kernels too (oe_zero1_*: peer stores into an exchange area of every rank and a
+          bounded wait): one C call per step and no torch.distributed call inside it — what a host
+          without a collective library uses.
   "nccl"  ncclReduceScatter(avg) + the single-GPU kernels + ncclAllGather: the baseline
           the fused path is measured against.
+
+`multicast=True` (peer and abi) allocates the shadow buffer as torch symmetric memory and lets the
+update kernel send every 8-byte shadow vector once through the NVLink multicast mapping instead of
+once per rank; values and layout are unchanged.
 
 The flat layout and the partition live in `ShardLayout` (pure Python, tested on CPU with
 gloo ranks); `Zero1AdamW` drives either path through torch.distributed.
@@ -196,6 +204,7 @@ class Zero1Schedule:
         self.lo, self.hi = self.layout.shard_range(rank)
         self.my_pieces = self.layout.pieces(rank)
         self.liveness: Optional[PeerLiveness] = None   # set one to have every step begin with a roll call
+        self._lost = False
 
     def bias_corrections(self) -> Tuple[float, float]:
         from .workload import bias_corrections
@@ -203,7 +212,11 @@ class Zero1Schedule:
 
     def step(self) -> None:
         if self.liveness is not None:
-            self.liveness.arrive(self.step_count + 1)   # raises RankLost before anything is launched
+            try:
+                self.liveness.arrive(self.step_count + 1)   # raises RankLost before anything is launched
+            except RankLost:
+                self._lost = True
+                raise
         self.step_count += 1          # one shared counter, as AdamW.Step keeps (autograd/nn.go:492)
         self.reduce_grads()           # mean over ranks of this rank's shard + its sum of squares
         self.combine_sumsq()          # sum over ranks -> global norm
@@ -233,19 +246,26 @@ class Zero1AdamW(Zero1Schedule):
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
                  beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
-                 chunk_elems: int = 0):
+                 chunk_elems: int = 0, multicast: bool = False, exchange_timeout_ms: int = 0,
+                 push_order: str = "ascending"):
         import torch
         import torch.distributed as dist
 
         from . import engine
-        if comm not in ("peer", "nccl"):
-            raise ValueError("comm must be 'peer' or 'nccl'")
+        if comm not in ("peer", "nccl", "abi"):
+            raise ValueError("comm must be 'peer', 'abi' or 'nccl'")
+        if multicast and comm == "nccl":
+            raise ValueError("multicast shadow stores belong to the peer and abi paths")
+        if push_order not in ("ascending", "rotated"):
+            raise ValueError("push_order must be 'ascending' or 'rotated'")
         self.torch, self.dist, self.engine = torch, dist, engine
         self.pg = process_group
         super().__init__(numels, group_of, lr, beta1, beta2, eps, max_norm, dist.get_rank(process_group),
                          dist.get_world_size(process_group))
         self.device = device
         self.comm = comm
+        self.multicast = multicast
+        self.push_order = push_order
         verify_same_layout(dist, layout_fingerprint(self.layout, group_of, (lr, beta1, beta2, eps, max_norm)),
                            process_group)
         # The peer path reads other ranks' gradient buffers directly: by default a tiny
@@ -255,7 +275,17 @@ class Zero1AdamW(Zero1Schedule):
         L = self.layout
         dev = torch.device("cuda", device)
         self.grad_flat = torch.zeros(L.total, dtype=torch.float32, device=dev)
-        self.shadow_flat = torch.zeros(L.total, dtype=torch.bfloat16, device=dev)
+        self._symm = None
+        if multicast:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.shadow_flat = symm_mem.empty(L.total, dtype=torch.bfloat16, device=dev)
+            self.shadow_flat.zero_()
+            group = process_group if process_group is not None else dist.group.WORLD
+            self._symm = symm_mem.rendezvous(self.shadow_flat, group)
+            if not self._symm.multicast_ptr:
+                raise RuntimeError("sharded optimizer: this system offers no NVLink multicast mapping")
+        else:
+            self.shadow_flat = torch.zeros(L.total, dtype=torch.bfloat16, device=dev)
         self.master = torch.zeros(L.shard_len, dtype=torch.float32, device=dev)
         self._allocate_state(dev)
         self.grads = [self.grad_flat[o:o + n] for o, n in zip(L.offsets, L.numels)]
@@ -266,8 +296,17 @@ class Zero1AdamW(Zero1Schedule):
         self._imported: List[int] = []
         self.grad_bases: Optional[List[int]] = None
         self.shadow_deltas: Optional[List[int]] = None
-        if comm == "peer":
+        self.mc_delta = 0
+        self.ctx = None
+        self._closed = False
+        self._lost = False   # a roll call found a rank missing: nothing collective may follow
+        if comm in ("peer", "abi"):
+            # the exchange area of the abi path: zeroed, exported like the other buffers
+            self._sync = torch.zeros(engine.OE_ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device=dev)
             self._map_peers()
+        if comm == "abi":
+            self.ctx = engine.Zero1Context(self.plan, self.rank, self.world, self.lo, L.shard_len, self.grad_bases,
+                                           self.shadow_deltas, self.sync_bases, self.mc_delta, exchange_timeout_ms)
 
     def _allocate_state(self, dev) -> None:
         torch = self.torch
@@ -288,26 +327,39 @@ class Zero1AdamW(Zero1Schedule):
     def _map_peers(self) -> None:
         eng, dist = self.engine, self.dist
         mine = {"grad": eng.ipc_export(self.grad_flat.data_ptr(), self.device),
-                "shadow": eng.ipc_export(self.shadow_flat.data_ptr(), self.device)}
+                "sync": eng.ipc_export(self._sync.data_ptr(), self.device)}
+        if self._symm is None:
+            mine["shadow"] = eng.ipc_export(self.shadow_flat.data_ptr(), self.device)
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=self.pg)
         opened = {}
-        self.grad_bases, self.shadow_deltas = [], []
+        own = {"grad": self.grad_flat.data_ptr(), "sync": self._sync.data_ptr(), "shadow": self.shadow_flat.data_ptr()}
+        seen = {key: [] for key in own}
         for r, info in enumerate(everyone):
-            if r == self.rank:
-                self.grad_bases.append(self.grad_flat.data_ptr())
-                self.shadow_deltas.append(0)
-                continue
-            addr = {}
-            for key in ("grad", "shadow"):
-                handle, offset = info[key]
-                if handle not in opened:  # both buffers may live in one allocation
-                    opened[handle] = eng.ipc_import(handle, self.device)
-                    self._imported.append(opened[handle])
-                addr[key] = opened[handle] + offset
-            self.grad_bases.append(addr["grad"])
-            self.shadow_deltas.append(addr["shadow"] - self.shadow_flat.data_ptr())
+            for key in own:
+                if r == self.rank:
+                    seen[key].append(own[key])
+                elif key not in info:       # symmetric memory: the rendezvous already mapped every rank's buffer
+                    seen[key].append(int(self._symm.buffer_ptrs[r]))
+                else:
+                    handle, offset = info[key]
+                    if handle not in opened:  # several buffers may live in one allocation
+                        opened[handle] = eng.ipc_import(handle, self.device)
+                        self._imported.append(opened[handle])
+                    seen[key].append(opened[handle] + offset)
+        self.grad_bases, self.sync_bases = seen["grad"], seen["sync"]
+        self.shadow_deltas = [a - own["shadow"] for a in seen["shadow"]]
+        if self._symm is not None:
+            self.mc_delta = int(self._symm.multicast_ptr) - own["shadow"]
         dist.barrier(group=self.pg)
+
+    def _push_deltas(self) -> List[int]:
+        """The order in which the update kernel issues its plain shadow stores: ascending rank, or
+        starting after this rank and ending with it, so that the ranks do not all store to the same
+        GPU first."""
+        if self.push_order == "ascending":
+            return self.shadow_deltas
+        return [self.shadow_deltas[(self.rank + 1 + j) % self.world] for j in range(self.world)]
 
     # ---- helpers --------------------------------------------------------------------------
     def zero_padding(self) -> None:
@@ -322,22 +374,51 @@ class Zero1AdamW(Zero1Schedule):
         b1, b2 = self.bias_corrections()
         return self.engine.AdamWHParams(self.lr, self.beta1, self.beta2, self.eps, b1, b2, self.max_norm, flags)
 
+    def step(self) -> None:
+        if self.comm != "abi":
+            return super().step()
+        # one C call enqueues the five launches of the step; no collective library is involved
+        if self.liveness is not None:
+            self._roll_call()
+        self.step_count += 1
+        self._abi_step()
+
+    def _roll_call(self) -> None:
+        try:
+            self.liveness.arrive(self.step_count + 1)
+        except RankLost:
+            self._lost = True
+            raise
+
+    def _abi_step(self) -> None:
+        from .engine import OE_WRITE_SHADOW
+        self.ctx.adamw_step(self._hparams(OE_WRITE_SHADOW))
+
+    def exchange_status(self) -> int:
+        """abi path: waits for the stream and raises EngineError if a rank missed an exchange."""
+        return self.ctx.status() if self.ctx is not None else 0
+
     # ---- the four phases; all work is enqueued on the current torch stream, no host sync ----
     def reduce_grads(self) -> None:
         from .engine import OE_PARTIAL_ONLY
         dist = self.dist
         own = self.grad_flat[self.lo:self.hi]
-        if self.comm == "peer":
-            if self.sync_before_pull:
-                # every rank's gradients must be complete before anyone pulls them
-                dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
-            self.plan.peer_reduce_grads(self.grad_bases, self.lo, self.layout.shard_len, own.data_ptr(),
-                                        1.0 / self.world, OE_PARTIAL_ONLY)
-        else:
+        if self.comm == "nccl":
             dist.reduce_scatter_tensor(own, self.grad_flat, op=dist.ReduceOp.AVG, group=self.pg)
             self.plan.grad_norm(OE_PARTIAL_ONLY)
+            return
+        if self.comm == "abi":
+            self.ctx.exchange(0)
+        elif self.sync_before_pull:
+            # every rank's gradients must be complete before anyone pulls them
+            dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
+        self.plan.peer_reduce_grads(self.grad_bases, self.lo, self.layout.shard_len, own.data_ptr(),
+                                    1.0 / self.world, OE_PARTIAL_ONLY)
 
     def combine_sumsq(self) -> None:
+        if self.comm == "abi":
+            self.ctx.exchange(1)   # partial sums exchanged and added in rank order, norm finalised
+            return
         # 8 bytes; on the peer path this is also the point after which every rank's pull is over
         self.dist.all_reduce(self.sumsq, op=self.dist.ReduceOp.SUM, group=self.pg)
         self.plan.norm_finalize()
@@ -345,14 +426,18 @@ class Zero1AdamW(Zero1Schedule):
     def update(self) -> None:
         from .engine import OE_WRITE_SHADOW
         hp = self._hparams(OE_WRITE_SHADOW)
-        if self.comm == "peer":
-            self.plan.adamw_step_peers(hp, self.shadow_deltas)
-        else:
+        if self.comm == "nccl":
             self.plan.adamw_step(hp)
+        elif self.multicast:
+            self.plan.adamw_step_multicast(hp, self.shadow_deltas, self.mc_delta)
+        else:
+            self.plan.adamw_step_peers(hp, self._push_deltas())
 
     def gather_shadows(self) -> None:
         dist = self.dist
-        if self.comm == "peer":
+        if self.comm == "abi":
+            self.ctx.exchange(2)
+        elif self.comm == "peer":
             # the update kernel already stored into every rank's buffer; once this tiny reduction
             # returns, every rank's stores are complete on every GPU
             dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
@@ -386,6 +471,20 @@ class Zero1AdamW(Zero1Schedule):
         produce the same bytes."""
         if not streaming:
             return self._save_state_gathered(path, names, shapes)
+        groups = self.groups()
+        stream = None
+        if self.rank == 0:
+            from . import autograd as host
+            stream = host.AdamWStateStream(path, list(names), [list(s) for s in shapes], self.step_count, self.lr,
+                                           groups[0][3], self.beta1, self.beta2, self.eps, groups)
+        # every rank walks the same order: the file's (sorted entry names)
+        order = sorted([f"{k}.{i}" for k in ("m", "v") for i in range(len(self.layout.numels))])
+        self._stream_entries(stream, order, lambda key: self.m if key == "m" else self.v)
+
+    def _stream_entries(self, stream, order: Sequence[str], shard_of) -> None:
+        """Sends the entries `order` ("<key>.<tensor index>", in file order) to the writer on rank 0:
+        for each entry the owners pass their pieces of `shard_of(key)` to rank 0, which appends them, so
+        rank 0 holds one piece on the host at a time. `stream` is the writer on rank 0, None elsewhere."""
         torch, dist = self.torch, self.dist
         L = self.layout
         # who holds which part of every tensor: (rank, offset in the rank's shard, length), by rank
@@ -394,19 +493,11 @@ class Zero1AdamW(Zero1Schedule):
             lo, _ = L.shard_range(r)
             for pc in L.pieces(r):
                 holders[pc.tensor].append((r, pc.flat_offset - lo, pc.length))
-        groups = self.groups()
-        stream = None
-        if self.rank == 0:
-            from . import autograd as host
-            stream = host.AdamWStateStream(path, list(names), [list(s) for s in shapes], self.step_count, self.lr,
-                                           groups[0][3], self.beta1, self.beta2, self.eps, groups)
         try:
-            # every rank walks the same order: the file's (sorted entry names)
-            order = sorted([f"{k}.{i}" for k in ("m", "v") for i in range(len(L.numels))])
             bounce = None
             for entry in order:
                 key, index = entry.split(".")
-                shard = self.m if key == "m" else self.v
+                shard = shard_of(key)
                 for r, a, n in holders[int(index)]:
                     if self.rank == 0:
                         if r == 0:
@@ -501,27 +592,40 @@ class Zero1AdamW(Zero1Schedule):
         self.lr, self.beta1, self.beta2, self.eps = (float(np.float32(cfg[k])) for k in ("LR", "Beta1", "Beta2", "Eps"))
 
     def close(self) -> None:
+        """Releases the plan and unmaps the peers' buffers. Local and idempotent: no collective is
+        enqueued, so a rank that survives a `RankLost` can call it. Nothing of another rank can still
+        be touching this rank's buffers once its own stream has drained: a step ends with an exchange
+        that every rank's stores precede, and a peer cannot begin the next pull without this rank.
+        The buffers themselves are torch tensors; they go back to torch's allocator, not to the driver."""
+        if self._closed:
+            return
+        self._closed = True
         self.torch.cuda.synchronize()
-        self.dist.barrier(group=self.pg)
+        if self.ctx is not None:
+            self.ctx.close()
+            self.ctx = None
         self.plan.close()
+        for base in self._imported:
+            self.engine.ipc_close(base, self.device)
+        self._imported = []
 
 
 class Zero1SGD(Zero1AdamW):
     """The sharded form of SGD.Step (autograd/sgd.go:192-225): same flat layout, reduction, norm and
     shadow exchange as `Zero1AdamW`; the owner of a shard keeps the momentum buffer of its pieces and
     one init flag per piece (the reference keeps one per tensor: a tensor that straddles two shards
-    has a piece, and a flag, on each owner). State files are not written by this class."""
+    has a piece, and a flag, on each owner; state files carry the reference's one flag per tensor)."""
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, momentum: float,
                  dampening: float, nesterov: bool, maximize: bool, max_norm: float, device: int, comm: str = "peer",
-                 process_group=None, chunk_elems: int = 0):
+                 process_group=None, chunk_elems: int = 0, **options):
         if nesterov and (not momentum > 0 or dampening != 0):
             raise ValueError("autograd: Nesterov momentum requires a positive momentum and zero dampening")
         self.momentum, self.dampening, self.nesterov, self.maximize = momentum, dampening, nesterov, maximize
         # the base class fingerprints (lr, beta1, beta2, eps, max_norm): momentum and dampening take
         # the places of the betas, the two switches the place of eps
         super().__init__(numels, group_of, lr, momentum, dampening, float(2 * int(nesterov) + int(maximize)), max_norm,
-                         device, comm, process_group, chunk_elems)
+                         device, comm, process_group, chunk_elems, **options)
 
     def _allocate_state(self, dev) -> None:
         torch = self.torch
@@ -539,20 +643,130 @@ class Zero1SGD(Zero1AdamW):
                                                 self.flags[k:k + 1] if has_state else None, self.shadow_flat[a:b], scale, decay))
         return descs
 
-    def update(self) -> None:
+    def _sgd_hparams(self):
         from .engine import OE_MAXIMIZE, OE_NESTEROV, OE_WRITE_SHADOW
         flags = OE_WRITE_SHADOW | (OE_NESTEROV if self.nesterov else 0) | (OE_MAXIMIZE if self.maximize else 0)
-        hp = self.engine.SGDHParams(self.lr, self.momentum, self.dampening, self.max_norm, flags)
-        if self.comm == "peer":
-            self.plan.sgd_step_peers(hp, self.shadow_deltas)
-        else:
+        return self.engine.SGDHParams(self.lr, self.momentum, self.dampening, self.max_norm, flags)
+
+    def update(self) -> None:
+        hp = self._sgd_hparams()
+        if self.comm == "nccl":
             self.plan.sgd_step(hp)
+        elif self.multicast:
+            self.plan.sgd_step_multicast(hp, self.shadow_deltas, self.mc_delta)
+        else:
+            self.plan.sgd_step_peers(hp, self._push_deltas())
 
-    def save_state(self, *args, **kwargs) -> None:
-        raise NotImplementedError("the sharded SGD does not write state files")
+    def _abi_step(self) -> None:
+        self.ctx.sgd_step(self._sgd_hparams())
 
-    def load_state(self, *args, **kwargs) -> None:
-        raise NotImplementedError("the sharded SGD does not read state files")
-        for base in self._imported:
-            self.engine.ipc_close(base, self.device)
-        self._imported = []
+    def _device_sync(self) -> None:
+        self.torch.cuda.synchronize()
+
+    def _state_loaded(self) -> None:
+        self.plan.update(self._descs())   # the groups' scale and decay live in the device table
+
+    # ---- state files in the reference's "gograd-sgd" layout (autograd/sgd_state.go:27-194) --------
+    def tensor_flags(self) -> List[bool]:
+        """The reference keeps one "buffer initialised" flag per tensor; this class keeps one per piece.
+        Every rank learns every piece's flag; a tensor is initialised when all of its pieces are. A
+        tensor whose pieces disagree has no counterpart in the reference's state and is refused."""
+        self._device_sync()
+        mine = [bool(x) for x in self.flags[:len(self.my_pieces)].cpu().tolist()] if self.momentum > 0 else \
+               [False] * len(self.my_pieces)
+        everyone = [None] * self.world
+        self.dist.all_gather_object(everyone, mine, group=self.pg)
+        votes: List[List[bool]] = [[] for _ in self.layout.numels]
+        for r, flags in enumerate(everyone):
+            for pc, flag in zip(self.layout.pieces(r), flags):
+                votes[pc.tensor].append(flag)
+        for i, v in enumerate(votes):
+            if any(v) != all(v):
+                raise ValueError(f"autograd: SGD momentum buffer {i} is initialised on some ranks only")
+        return [all(v) for v in votes]
+
+    def save_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
+        """Rank 0 writes the sharded momentum buffers as a "gograd-sgd" state file: one entry buffer.<i>
+        of shape [numel] per initialised parameter, the flags, options and groups in the metadata — the
+        file an unsharded SGD reads back (autograd/sgd_state.go:150-194). Streamed like the sharded
+        AdamW state: the owners send their pieces in file order, rank 0 appends them."""
+        initialized = self.tensor_flags()
+        groups = self.groups()
+        stream = None
+        if self.rank == 0:
+            from . import autograd as host
+            stream = host.SGDStateStream(path, list(names), [list(s) for s in shapes], self.step_count, self.lr,
+                                         self.momentum, self.dampening, groups[0][3], self.nesterov, self.maximize,
+                                         initialized, groups)
+        order = sorted(f"buffer.{i}" for i, flag in enumerate(initialized) if flag)
+        self._stream_entries(stream, order, lambda key: self.buffer)
+
+    def load_state(self, path: str, names: Sequence[str], shapes: Sequence[Sequence[int]]) -> None:
+        """Every rank reads the file and takes its pieces of the momentum buffers and their flags. The
+        whole file is checked first (format, names, shapes, options, flags against entries, finite
+        values, group layout: autograd/sgd_state.go:68-100,166-194); nothing changes when a check fails."""
+        import json
+        import math
+        import struct
+
+        import numpy as np
+        n = len(self.layout.numels)
+        with open(path, "rb") as f:
+            (hlen,) = struct.unpack("<Q", f.read(8))
+            header = json.loads(f.read(hlen))
+            base = 8 + hlen
+            meta = header.pop("__metadata__", {})
+            if meta.get("format") != "gograd-sgd" or meta.get("version") != "1":
+                raise ValueError("autograd: unsupported SGD state format")
+            cfg = json.loads(meta["optimizer"])
+            opt = cfg["Options"]
+            flags = list(cfg.get("Initialized") or [])
+            if cfg["StepCount"] != int(meta["step_count"]) or cfg["StepCount"] < 0 or len(flags) != len(cfg["Names"] or []):
+                raise ValueError("autograd: invalid SGD state metadata")
+            for key in ("LR", "Momentum", "Dampening", "WeightDecay"):
+                if not (math.isfinite(opt[key]) and opt[key] >= 0):
+                    raise ValueError("autograd: invalid SGD configuration")
+            if opt["Nesterov"] and (not opt["Momentum"] > 0 or opt["Dampening"] != 0):
+                raise ValueError("autograd: Nesterov momentum requires a positive momentum and zero dampening")
+            if len(flags) != n or list(cfg["Names"] or []) != list(names) or \
+                    [list(s) for s in (cfg["Shapes"] or [])] != [list(s) for s in shapes]:
+                raise ValueError("autograd: invalid SGD state count")
+            if len(header) != sum(1 for b in flags if b):
+                raise ValueError("autograd: unexpected SGD state entries")
+            for i, flag in enumerate(flags):
+                entry = header.get(f"buffer.{i}")
+                if flag:
+                    if not opt["Momentum"] > 0 or cfg["StepCount"] == 0 or entry is None or entry["dtype"] != "F32" \
+                            or entry["shape"] != [self.layout.numels[i]]:
+                        raise ValueError(f"autograd: invalid SGD momentum buffer {i}")
+            if bool(opt["Momentum"] > 0) != bool(self.momentum > 0):
+                raise ValueError("autograd: the saved state and the live optimizer disagree on momentum")
+            saved_groups = cfg.get("Groups") or []
+            live = self.groups()
+            if len(saved_groups) != len(live) or any(
+                    [names[i] for i in g[1]] != sg["Names"] for g, sg in zip(live, saved_groups)):
+                raise ValueError("autograd: saved parameter groups do not match the live optimizer")
+            staged = np.zeros(self.layout.shard_len, np.float32)
+            piece_flags = np.zeros(max(len(self.my_pieces), 1), np.float32)
+            for k, pc in enumerate(self.my_pieces):
+                if not flags[pc.tensor]:
+                    continue
+                entry = header[f"buffer.{pc.tensor}"]
+                f.seek(base + entry["data_offsets"][0] + 4 * pc.tensor_offset)
+                values = np.frombuffer(f.read(4 * pc.length), dtype="<f4")
+                if values.size != pc.length or not np.all(np.isfinite(values)):
+                    raise ValueError("autograd: non-finite SGD momentum")
+                a = pc.flat_offset - self.lo
+                staged[a:a + pc.length] = values
+                piece_flags[k] = 1.0
+        if self.momentum > 0:
+            self.buffer.copy_(self.torch.from_numpy(staged))
+            self.flags.copy_(self.torch.from_numpy(piece_flags))
+        for g, sg in zip(live, saved_groups):
+            scale = float(np.float32(sg["LRScale"])) or 1.0
+            for i in g[1]:
+                self.group_of[i] = (scale, float(np.float32(sg["WeightDecay"])))
+        self._state_loaded()
+        self.step_count = int(cfg["StepCount"])
+        self.lr, self.momentum, self.dampening = (float(np.float32(opt[k])) for k in ("LR", "Momentum", "Dampening"))
+        self.nesterov, self.maximize = bool(opt["Nesterov"]), bool(opt["Maximize"])

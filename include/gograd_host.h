@@ -206,6 +206,18 @@ typedef struct gg_state_stream gg_state_stream;
 OE_API int gg_adamw_state_stream_begin(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
                                        const int32_t* shape_offsets, const gg_adamw_config* config,
                                        const gg_groups* groups, gg_state_stream** out);
+/* The same for an SGD state file ("gograd-sgd": one entry buffer.<i> of shape [numel] per parameter whose
+ * momentum buffer is initialised, the flags, options and groups in the metadata,
+ * autograd/sgd_state.go:27-67,150-194). initialized[i] != 0 marks the parameters that have a buffer; the
+ * values follow through gg_state_stream_next / append / finish as above. */
+typedef struct gg_sgd_config {
+    int32_t step_count;
+    float lr, momentum, dampening, weight_decay;
+    int32_t nesterov, maximize;
+} gg_sgd_config;
+OE_API int gg_sgd_state_stream_begin(const char* path, int32_t n, const char* const* names, const int32_t* shapes,
+                                     const int32_t* shape_offsets, const gg_sgd_config* config,
+                                     const uint8_t* initialized, const gg_groups* groups, gg_state_stream** out);
 OE_API int gg_state_stream_next(const gg_state_stream* s, char* name_out, int32_t capacity, int64_t* remaining_out);
 OE_API int gg_state_stream_append(gg_state_stream* s, const char* entry, const float* values, int64_t count);
 OE_API int gg_state_stream_finish(gg_state_stream* s);

@@ -222,8 +222,8 @@ OE_API int oe_read_norm(oe_plan* plan, float* norm_out, double* sumsq_out, uint6
 OE_API int oe_adamw_step(oe_plan* plan, const oe_adamw_hparams* hp, uint64_t stream);
 
 /* One fused SGD step (autograd/sgd.go:192-225 semantics; replaces sgd_update + sgd_mark
- * per tensor, autograd/cuda_sgd.go:66-98): one update launch plus one launch that sets
- * the per-tensor "initialised" flags. */
+ * per tensor, autograd/cuda_sgd.go:66-98) in ONE launch: the CTA that finishes last sets the
+ * per-tensor "initialised" flags, which the reference does with one sgd_mark launch per tensor. */
 OE_API int oe_sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream);
 
 /* Zero every present gradient in one launch (AdamW.ZeroGrad, autograd/nn.go:533-537). */
@@ -248,8 +248,9 @@ OE_API int oe_adamw_step_from_host(oe_plan* plan, const oe_adamw_hparams* hp, co
  * have no counterpart there. Every rank (one process per GPU) keeps a full flat fp32 gradient
  * buffer and a full flat bf16 shadow buffer of one common layout, and owns one contiguous shard of
  * master weights, m and v. Buffers of other ranks are reached through CUDA IPC mappings (plain peer
- * loads and stores only). None of these kernels waits on another rank: the caller
- * orders them with stream-ordered collectives (see gograd_b200/zero1.py). */
+ * loads and stores only). None of the kernels in this group waits on another rank: the caller orders them
+ * with stream-ordered collectives of its own, or uses the oe_zero1_* group below, which brings its own
+ * (bounded) exchanges. */
 
 /* Pull reduce-scatter fused with the norm pass. rank_bases[k] is the address, valid on this GPU, of
  * rank k's gradient buffer; the kernel reads elements [first_elem, first_elem+numel) of each, adds
@@ -279,6 +280,84 @@ OE_API int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const 
 OE_API int oe_sgd_step_peers(oe_plan* plan, const oe_sgd_hparams* hp, const int64_t* shadow_deltas, uint32_t n_ranks,
                              uint64_t stream);
 
+/* The same two steps with the shadow stores sent through an NVLink multicast mapping: *mc_delta is the byte
+ * distance from this rank's shadow buffer to a multicast address that is bound to every rank's shadow
+ * buffer (cuMulticastCreate / cuMulticastBindMem, or torch's symmetric memory). Each 8-byte vector
+ * leaves this GPU once (multimem.st) and the switch delivers it to every rank, this one included; the
+ * few single elements at the end of a tensor whose length is no multiple of 4 take the plain stores
+ * through shadow_deltas. Results are those of oe_adamw_step_peers / oe_sgd_step_peers. */
+OE_API int oe_adamw_step_multicast(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,
+                                   uint32_t n_ranks, const int64_t* mc_delta, uint64_t stream);
+OE_API int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const int64_t* shadow_deltas,
+                                 uint32_t n_ranks, const int64_t* mc_delta, uint64_t stream);
+
+/* Tuning knobs of the peer kernels; none changes a result. value 0 restores the library's choice.
+ *   OE_TUNE_PEER_REDUCE_GRID       CTAs of the pull-reduce launch (at most the persistent grid)
+ *   OE_TUNE_PEER_UPDATE_GRID       CTAs of the update launches that store into peers' buffers
+ *   OE_TUNE_PEER_REDUCE_FIRST      rank whose gradient is loaded first for every element (the adds keep
+ *                                  ascending rank order); ranks that pass their own rank + 1 do not all
+ *                                  address the same source first
+ *   OE_TUNE_PEER_PUSH_WARP_ROTATE  non-zero: warp w of a CTA starts its round of shadow stores at target
+ *                                  w mod n instead of target 0
+ * The update kernels issue their plain shadow stores in the order of shadow_deltas, which the caller may
+ * rotate by rank for the same reason. */
+#define OE_TUNE_PEER_REDUCE_GRID      1
+#define OE_TUNE_PEER_UPDATE_GRID      2
+#define OE_TUNE_PEER_REDUCE_FIRST     3
+#define OE_TUNE_PEER_PUSH_WARP_ROTATE 4
+OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);
+
+/* ---- sharded step driven through this interface alone -------------------------------------------- */
+/* For a host with no collective library (the reference has none: one OS thread per device,
+ * autograd/cuda_context.go:29-54). The three points at which the ranks of a step must meet are small
+ * kernels of the library: every rank announces its arrival with plain stores into an exchange area in
+ * each rank's memory, then waits for the others' announcements in its own area. The wait is bounded:
+ * after timeout_ms (or an equivalent number of polls) the kernel records the missing rank in the area's
+ * status word and returns; every later launch of the sharded step (pull-reduce, update, exchanges) sees
+ * the word and does nothing, so a rank that never arrives costs a time-out, never a hung GPU. The host
+ * reads the word with oe_zero1_status.
+ *
+ * Set-up: every rank allocates OE_ZERO1_SYNC_BYTES of zeroed device memory (256-byte aligned), exports it
+ * with oe_ipc_export like its gradient and shadow buffers, and maps the others' (oe_ipc_import). All
+ * ranks must call the step the same number of times. A rank's kernels wait on kernels of OTHER GPUs
+ * only: never run two ranks of one step on the same GPU. */
+#define OE_ZERO1_SYNC_BYTES 512
+#define OE_ZERO1_NO_ENTRY_EXCHANGE 0x1u /* the caller already knows that every rank's gradients are complete */
+
+typedef struct oe_zero1_desc {
+    uint32_t rank, world;          /* world <= 8, one node                                             */
+    uint64_t first_elem, numel;    /* this rank's shard of the flat layout                             */
+    uint64_t grad_bases[8];        /* rank k's flat gradient buffer as mapped on this GPU              */
+    int64_t shadow_deltas[8];      /* byte distance from this rank's shadow buffer to rank k's (own: 0) */
+    int64_t shadow_mc_delta;       /* distance to a multicast mapping of the shadow buffer, 0 = none   */
+    uint64_t sync_blocks[8];       /* rank k's exchange area as mapped on this GPU                     */
+    uint32_t timeout_ms;           /* limit of every wait, 0 = 10000                                   */
+    uint32_t flags;                /* OE_ZERO1_NO_ENTRY_EXCHANGE                                       */
+} oe_zero1_desc;
+
+typedef struct oe_zero1 oe_zero1;
+
+/* Binds a plan (whose tensors are the pieces of this rank's shard) to the ranks' buffers. Allocates
+ * nothing on the device. */
+OE_API int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero1** out);
+OE_API int oe_zero1_destroy(oe_zero1* z);
+
+/* One sharded step, enqueued on `stream` without a host wait: exchange "gradients ready" -> pull-reduce
+ * of this rank's shard (mean in ascending rank order) with its sum of squares -> exchange of the partial
+ * sums, added in rank order into the global norm -> fused update with the clip folded in, shadow stored
+ * to every rank -> exchange "stores performed". hp as for oe_adamw_step / oe_sgd_step. */
+OE_API int oe_zero1_adamw_step(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream);
+OE_API int oe_zero1_sgd_step(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream);
+
+/* One exchange on its own (phase 0 gradients ready — it also begins a new step —, 1 reduced, 2 stored):
+ * for a caller that enqueues the phases itself. */
+OE_API int oe_zero1_exchange(oe_zero1* z, uint32_t phase, uint64_t stream);
+
+/* Waits for `stream` and reads the status word: 0 and *status_out = 0 when every exchange so far
+ * completed; otherwise OE_ERR_DEVICE, *status_out = 1 | phase << 8 | missing rank << 16, and the message
+ * names the rank. The word is sticky: rebuild the ranks' state before stepping again. */
+OE_API int oe_zero1_status(oe_zero1* z, uint32_t* status_out, uint64_t stream);
+
 /* CUDA IPC plumbing: export the allocation that contains `address` (64-byte handle + offset of
  * the address inside it), map a peer's allocation on this device, unmap it. */
 OE_API int oe_ipc_export(int device, uint64_t address, void* handle_out, uint64_t* offset_out);
@@ -304,7 +383,9 @@ OE_API int oe_ipc_close(int device, uint64_t base);
  * first call on a device also resolves the array's device address, which loads the module: make
  * it at start-up, before any stream capture begins.
  * No counterpart in the reference; same result as oe_grad_norm on a one-tensor plan up to the
- * summation order of the float64 partial sums. */
+ * summation order of the float64 partial sums. This one entry point uses the CUDA runtime: a positive
+ * return value is a cudaError_t, which has the same numbering as CUresult for every code that can occur
+ * here (invalid value 1, out of memory 2, no kernel image 209, invalid device 101, launch failures 7xx). */
 OE_API int oe_grad_norm_static(int device, uint64_t grad, uint64_t numel, uint64_t norm_out, uint64_t stream);
 
 /* ---- launch counters ---------------------------------------------------------------------------- */

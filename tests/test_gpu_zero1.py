@@ -50,8 +50,10 @@ def _oracle_run(world, steps):
     return ref, norms
 
 
-@pytest.mark.parametrize("world", [2, 3, 8])
-def test_peer_kernels_with_emulated_ranks(world):
+@pytest.mark.parametrize("world,tuned", [(2, False), (3, False), (8, False), (3, True), (8, True)])
+def test_peer_kernels_with_emulated_ranks(world, tuned):
+    """tuned: every launch-shape knob of the peer kernels away from its default (first-issued rank,
+    small grids, warp-rotated and rank-rotated store order); no result may change."""
     import gograd_b200 as eng
     from gograd_b200.engine import OE_PARTIAL_ONLY, OE_WRITE_SHADOW
     from gograd_b200.workload import bias_corrections
@@ -78,6 +80,13 @@ def test_peer_kernels_with_emulated_ranks(world):
                                         S[r][a:b], *GROUPS[pc.tensor]))
         plans.append(eng.Plan(descs))
         records.append(torch.as_tensor(_RawCuda(plans[r].norm_address(), (1,), "<f8"), device="cuda"))
+        if tuned:
+            from gograd_b200.engine import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST,
+                                            OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID)
+            plans[r].set_tuning(OE_TUNE_PEER_REDUCE_FIRST, (r + 1) % world)
+            plans[r].set_tuning(OE_TUNE_PEER_REDUCE_GRID, 3)
+            plans[r].set_tuning(OE_TUNE_PEER_UPDATE_GRID, 5)
+            plans[r].set_tuning(OE_TUNE_PEER_PUSH_WARP_ROTATE, 1)
     steps = 2
     ref, want_norms = _oracle_run(world, steps)
     for step in range(1, steps + 1):
@@ -98,6 +107,8 @@ def test_peer_kernels_with_emulated_ranks(world):
             b1, b2 = bias_corrections(HP["beta1"], HP["beta2"], step)
             hp = eng.AdamWHParams(HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], b1, b2, HP["max_norm"], OE_WRITE_SHADOW)
             deltas = [S[k].data_ptr() - S[r].data_ptr() for k in range(world)]
+            if tuned:   # stores issued starting after this rank, ending with it
+                deltas = [deltas[(r + 1 + j) % world] for j in range(world)]
             plans[r].adamw_step_peers(hp, deltas)
     torch.cuda.synchronize()
     flat = {k: np.zeros(L.total, np.float32) for k in "pmv"}
@@ -119,13 +130,20 @@ def test_peer_kernels_with_emulated_ranks(world):
         p.close()
 
 
+def _comm_options(spec):
+    """"peer", "nccl", "abi", optionally "+mc" (multicast shadow stores) and "+rot" (rotated store order)."""
+    parts = spec.split("+")
+    return dict(comm=parts[0], multicast="mc" in parts[1:], push_order="rotated" if "rot" in parts[1:] else "ascending")
+
+
 def _rank_main(rank, world, port, comm, queue):
     import torch.distributed as dist
     from gograd_b200.zero1 import Zero1AdamW
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank, comm=comm)
+    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank,
+                     exchange_timeout_ms=20000, **_comm_options(comm))
     L = opt.layout
     weights = torch.zeros(L.total)
     for o, w in zip(L.offsets, _weights()):
@@ -139,6 +157,7 @@ def _rank_main(rank, world, port, comm, queue):
         opt.step()
         norms.append(opt.grad_norm())
     torch.cuda.synchronize()
+    assert opt.exchange_status() == 0
     queue.put((rank, opt.lo, opt.master.cpu().numpy(), opt.m.cpu().numpy(), opt.v.cpu().numpy(),
                opt.shadow_flat.view(torch.int16).cpu().numpy(), norms))
     opt.close()
@@ -171,9 +190,11 @@ def _run_real_ranks(world, comm):
     return ref, L, flat, results, oracle
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "peer+rot", "abi+mc"])
 def test_two_real_ranks(comm):
-    """Two ranks: both paths are bit-identical to the oracle (a two-term sum has one order)."""
+    """Two ranks: every path is bit-identical to the oracle (a two-term sum has one order). "abi" runs
+    the whole step through oe_zero1_adamw_step with the library's own exchanges between the ranks;
+    "+mc" sends the shadow through the NVLink multicast mapping."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     ref, L, flat, results, oracle = _run_real_ranks(2, comm)
@@ -185,7 +206,7 @@ def test_two_real_ranks(comm):
             assert np.array_equal(shadow[o:o + n], want), f"rank {rank} shadow[{i}] ({comm})"
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+mc"])
 def test_all_real_ranks_of_the_box(comm):
     """Every GPU of the box as a rank (4 or 8): the peer path adds in ascending rank order and stays
     bit-identical to the oracle; NCCL's order is its own, so that path is held to the stated
@@ -196,7 +217,7 @@ def test_all_real_ranks_of_the_box(comm):
     world = 8 if world >= 8 else 4 if world >= 4 else world
     ref, L, flat, results, oracle = _run_real_ranks(world, comm)
     for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
-        if comm == "peer":
+        if comm != "nccl":
             assert np.array_equal(flat["p"][o:o + n], ref.params[i]), f"p[{i}] world {world}"
             assert np.array_equal(flat["m"][o:o + n], ref.m[i]) and np.array_equal(flat["v"][o:o + n], ref.v[i])
         else:
@@ -303,8 +324,9 @@ def _sgd_rank_main(rank, world, port, comm, queue):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    options = _comm_options(comm)
     opt = Zero1SGD(NUMELS, GROUPS, SGD_HP["lr"], SGD_HP["momentum"], SGD_HP["dampening"], SGD_HP["nesterov"],
-                   SGD_HP["maximize"], SGD_HP["max_norm"], rank, comm=comm)
+                   SGD_HP["maximize"], SGD_HP["max_norm"], rank, options.pop("comm"), **options)
     L = opt.layout
     weights = torch.zeros(L.total)
     for o, w in zip(L.offsets, _weights()):
@@ -322,7 +344,7 @@ def _sgd_rank_main(rank, world, port, comm, queue):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi"])
 def test_two_real_ranks_sgd(comm):
     """The sharded SGD over two real ranks, both data paths, bit-identical to the unsharded oracle."""
     if torch.cuda.device_count() < 2:
@@ -461,11 +483,14 @@ def _leaving_rank_main(rank, world, port, queue):
             after = (opt.master, opt.m, opt.v, opt.shadow_flat.view(torch.int16))
             same = all(bool(torch.equal(a, b)) for a, b in zip(before, after))
             result = (e.missing, e.step, opt.step_count, same)
+    if rank == 0:
+        opt.close()                                # the survivor cleans up: local, no collective, no barrier
+        opt.close()                                # and a second call does nothing
+        result = result + (len(opt._imported),)
     queue.put((rank, result))
     queue.close()
     queue.join_thread()
-    opt.close()                                    # local: unmaps the peers' buffers, frees the plan
-    os._exit(0)                                    # no communicator teardown against a rank that is gone
+    os._exit(0)                                    # the leaving rank never calls close(); no communicator teardown
 
 
 def test_a_rank_that_left_is_found_before_the_next_launch():
@@ -490,7 +515,7 @@ def test_a_rank_that_left_is_found_before_the_next_launch():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert results[1] == "left between steps"
-    assert results[0] == ([1], 2, 1, True), results
+    assert results[0] == ([1], 2, 1, True, 0), results
 
 
 def test_sharded_state_file_loads_into_unsharded_adamw_and_back(tmp_path):
@@ -619,3 +644,254 @@ def test_chunk_range_steps_and_accumulated_norm_equal_whole_launches():
     assert abs(whole_sq - want) <= 1e-12 * want
     for p in plans.values():
         p.close()
+
+
+def _single_rank_group():
+    import torch.distributed as dist
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    return dist
+
+
+def test_one_rank_through_the_library_alone():
+    """comm="abi" with a world of one on one GPU: oe_zero1_adamw_step enqueues exchange, pull-reduce,
+    exchange with the norm, update, exchange — five launches per step, no collective — and the result
+    is the unsharded oracle's, bit for bit. The exchanges of a single rank meet only themselves."""
+    import gograd_b200 as eng
+    from gograd_b200.zero1 import Zero1AdamW
+    from oracle import oracle
+    dist = _single_rank_group()
+    try:
+        opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], 0, comm="abi")
+        L = opt.layout
+        weights = torch.zeros(L.total)
+        for o, w in zip(L.offsets, _weights()):
+            weights[o:o + w.size] = torch.from_numpy(w)
+        opt.load_master(weights.cuda())
+        ref, want_norms = _oracle_run(1, 2)
+        eng.launch_count_reset()
+        for step in (1, 2):
+            opt.grad_flat.zero_()
+            for view, g in zip(opt.grads, _grads(0, step)):
+                view.copy_(torch.from_numpy(g))
+            opt.step()
+            assert abs(opt.grad_norm() - want_norms[step - 1]) <= 1e-6 * want_norms[step - 1]
+        assert opt.exchange_status() == 0
+        assert eng.launch_count() == 10 and eng.launch_count("oe_rank_exchange") == 6
+        p, m, v = opt.master.cpu().numpy(), opt.m.cpu().numpy(), opt.v.cpu().numpy()
+        shadow = opt.shadow_flat.view(torch.int16).cpu().numpy()
+        for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+            assert np.array_equal(p[o:o + n], ref.params[i]) and np.array_equal(m[o:o + n], ref.m[i])
+            assert np.array_equal(v[o:o + n], ref.v[i])
+            assert np.array_equal(shadow[o:o + n], oracle.f32_to_bf16(ref.params[i]).view(np.int16))
+        opt.close()
+        opt.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_an_exchange_gives_up_and_the_step_does_nothing():
+    """One GPU, a step of two ranks of which the second never arrives: its exchange area is a local
+    buffer that nothing writes. The first exchange's wait runs out after its limit (50 ms here), the
+    kernel records the missing rank in the status word and RETURNS; the pull-reduce, the update and
+    the later exchanges of that step see the word and do nothing, so master weights, moments and
+    shadow keep their values. Nothing hangs and the device still answers."""
+    import time
+
+    import gograd_b200 as eng
+    from gograd_b200.engine import OE_WRITE_SHADOW, OE_ZERO1_SYNC_BYTES, EngineError, Zero1Context
+    from gograd_b200.workload import bias_corrections
+    eng.init(0)
+    n = 3 * 4096
+    rng = np.random.default_rng(5)
+    mine, absent = (torch.from_numpy(rng.normal(0, 1e-3, 2 * n).astype(np.float32)).cuda() for _ in range(2))
+    p = torch.from_numpy(rng.normal(0, .02, n).astype(np.float32)).cuda()
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    shadows = [torch.full((2 * n,), -1, dtype=torch.int16, device="cuda") for _ in range(2)]
+    sync = [torch.zeros(OE_ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device="cuda") for _ in range(2)]
+    plan = eng.Plan([eng.TensorDesc(p, mine[:n], m, v, shadows[0][:n], 1.0, 0.1)])
+    ctx = Zero1Context(plan, 0, 2, 0, n, [mine.data_ptr(), absent.data_ptr()],
+                       [0, shadows[1].data_ptr() - shadows[0].data_ptr()], [s.data_ptr() for s in sync], timeout_ms=50)
+    before = [t.clone() for t in (p, m, v, mine, shadows[0], shadows[1])]
+    b1, b2 = bias_corrections(0.9, 0.999, 1)
+    t0 = time.perf_counter()
+    ctx.adamw_step(eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, b1, b2, 1.0, OE_WRITE_SHADOW))
+    with pytest.raises(EngineError) as err:
+        ctx.status()
+    waited = time.perf_counter() - t0
+    assert err.value.code == -6 and "rank 1" in err.value.message            # OE_ERR_DEVICE, names the rank
+    word = ctx.status_word()
+    assert word & 1 and (word >> 8) & 0xff == 0 and (word >> 16) & 0xff == 1  # timed out at exchange 0, rank 1 missing
+    assert 0.04 <= waited < 5.0, waited
+    for a, b in zip(before, (p, m, v, mine, shadows[0], shadows[1])):
+        assert torch.equal(a, b)
+    # the area of this rank shows its own arrival; the absent rank's area received this rank's announcement
+    assert int(sync[0][0].item()) == 1 and int(sync[0][1].item()) == 0 and int(sync[1][0].item()) == 1
+    # the device still works and the word is sticky: a second step is skipped at once
+    ctx.adamw_step(eng.AdamWHParams(1e-3, 0.9, 0.999, 1e-8, b1, b2, 1.0, OE_WRITE_SHADOW))
+    t1 = time.perf_counter()
+    assert ctx.status_word() == word and time.perf_counter() - t1 < 0.04
+    assert torch.equal(before[0], p)
+    plan.grad_norm()
+    assert plan.read_norm()[0] > 0
+    ctx.close()
+    plan.close()
+
+
+def test_sharded_sgd_state_file_loads_into_unsharded_sgd_and_back(tmp_path):
+    """The sharded SGD writes its momentum buffers in the reference's per-tensor layout ("gograd-sgd":
+    buffer.<i> only for initialised parameters, the flags in the metadata). The unsharded host-mirror
+    SGD loads that file and both continue bit for bit; the file the unsharded optimizer writes loads
+    back into a fresh sharded one; a file saved before the first step has no buffer entry at all."""
+    from gograd_b200 import autograd as ag
+    from gograd_b200.zero1 import Zero1SGD
+    dist = _single_rank_group()
+    try:
+        names = [f"t{i}" for i in range(len(NUMELS))]
+        shapes = [[n] for n in NUMELS]
+        groups = [(1.0, 5e-4)] * len(NUMELS)
+        hp = dict(lr=0.05, momentum=0.9, dampening=0.0, nesterov=True, maximize=False)
+
+        def make(comm="peer", **over):
+            c = dict(hp, **over)
+            return Zero1SGD(NUMELS, groups, c["lr"], c["momentum"], c["dampening"], c["nesterov"], c["maximize"],
+                            HP["max_norm"], 0, comm)
+
+        z = make()
+        L = z.layout
+        weights = torch.zeros(L.total)
+        for o, w in zip(L.offsets, _weights()):
+            weights[o:o + w.size] = torch.from_numpy(w)
+        z.load_master(weights.cuda())
+
+        def sharded_step(opt, step):
+            opt.grad_flat.zero_()
+            for view, g in zip(opt.grads, _grads(0, step)):
+                view.copy_(torch.from_numpy(g))
+            opt.step()
+
+        empty = str(tmp_path / "before_first_step.safetensors")
+        z.save_state(empty, names, shapes)
+        d = ag.safetensors_describe(empty)
+        assert d["entries"] == {} and d["metadata"]["format"] == "gograd-sgd" and d["metadata"]["step_count"] == "0"
+        for step in (1, 2):
+            sharded_step(z, step)
+        path = str(tmp_path / "sharded.safetensors")
+        z.save_state(path, names, shapes)
+        d = ag.safetensors_describe(path)
+        assert sorted(d["entries"]) == sorted(f"buffer.{i}" for i in range(len(NUMELS)))
+        assert d["metadata"]["step_count"] == "2" and '"Initialized":[true,true,true,true,true,true]' in d["metadata"]["optimizer"]
+        # the unsharded optimizer over the same weights
+        torch.cuda.synchronize()
+        flat = z.master.cpu().numpy()
+        params = [ag.Parameter(n, ag.Tensor(flat[o:o + k])) for n, o, k in zip(names, L.offsets, NUMELS)]
+        u = ag.NewSGD(params, ag.SGDOptions(LR=1.0, Momentum=0.5, WeightDecay=5e-4))
+        u.LoadSafeTensors(path)
+        assert u.StepCount == 2 and u.LearningRate() == np.float32(hp["lr"])
+        sharded_step(z, 3)
+        for p, g in zip(params, _grads(0, 3)):
+            p.Value.set_grad(g)
+        u.StepClipped(HP["max_norm"])
+        torch.cuda.synchronize()
+        flat = z.master.cpu().numpy()
+        for p, o, k in zip(params, L.offsets, NUMELS):
+            assert np.array_equal(p.Value.to_host(), flat[o:o + k]), p.Name
+        # and back: the unsharded file into a fresh sharded optimizer with other options
+        back = str(tmp_path / "unsharded.safetensors")
+        u.SaveSafeTensors(back)
+        z2 = make("nccl", lr=9.0, momentum=0.5, nesterov=False)
+        z2.master.copy_(z.master)
+        z2.load_state(back, names, shapes)
+        assert z2.step_count == 3 and np.float32(z2.lr) == np.float32(hp["lr"]) and z2.nesterov is True
+        assert np.float32(z2.momentum) == np.float32(hp["momentum"])
+        assert torch.equal(z2.buffer, z.buffer) and bool((z2.flags == 1).all())
+        sharded_step(z, 4)
+        sharded_step(z2, 4)
+        torch.cuda.synchronize()
+        assert torch.equal(z2.master, z.master) and torch.equal(z2.shadow_flat, z.shadow_flat)
+        # reject before mutate
+        kept = z2.buffer.clone()
+        with pytest.raises(ValueError, match="state count"):
+            z2.load_state(back, names[::-1], shapes)
+        with pytest.raises(ValueError, match="unsupported SGD state format"):
+            adamw_file = str(tmp_path / "adamw.safetensors")
+            ag.safetensors_write(adamw_file, {}, {"format": "gograd-adamw", "version": "1"})
+            z2.load_state(adamw_file, names, shapes)
+        assert torch.equal(kept, z2.buffer) and z2.step_count == 4
+        # the file from before the first step resets a stepped optimizer to "no buffer yet"
+        z2.load_state(empty, names, shapes)
+        assert z2.step_count == 0 and bool((z2.flags == 0).all())
+        z.close()
+        z2.close()
+    finally:
+        dist.destroy_process_group()
+
+
+def _sgd_saving_rank_main(rank, world, port, out_dir, queue):
+    import torch.distributed as dist
+    from gograd_b200.zero1 import Zero1SGD
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    opt = Zero1SGD(NUMELS, GROUPS, SGD_HP["lr"], SGD_HP["momentum"], SGD_HP["dampening"], SGD_HP["nesterov"],
+                   SGD_HP["maximize"], SGD_HP["max_norm"], rank, "peer")
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+    for step in (1, 2):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+        opt.step()
+    names = [f"t{i}" for i in range(len(NUMELS))]
+    path = os.path.join(out_dir, "sgd.safetensors")
+    opt.save_state(path, names, [[n] for n in NUMELS])
+    # a fresh pair of ranks reads the file back: every rank takes its own pieces
+    fresh = Zero1SGD(NUMELS, GROUPS, 1.0, 0.5, 0.0, False, False, SGD_HP["max_norm"], rank, "nccl")
+    fresh.load_state(path, names, [[n] for n in NUMELS])
+    same = bool(torch.equal(fresh.buffer, opt.buffer)) and bool((fresh.flags[:len(fresh.my_pieces)] == 1).all())
+    torch.cuda.synchronize()
+    queue.put((rank, opt.lo, opt.buffer.cpu().numpy(), same, fresh.step_count))
+    fresh.close()
+    opt.close()
+    dist.destroy_process_group()
+
+
+def test_two_real_ranks_write_and_read_an_sgd_state_file(tmp_path):
+    """Two ranks, tensors straddling the shard boundary: the file holds each tensor's whole momentum
+    buffer assembled from both owners' pieces, with one flag per tensor, and splits again on load."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from gograd_b200 import autograd as ag
+    from gograd_b200.zero1 import ShardLayout
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_sgd_saving_rank_main, args=(r, world, port, str(tmp_path), queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=300) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    L = ShardLayout(NUMELS, world)
+    flat = np.zeros(L.total, np.float32)
+    for rank, lo, buffer, same, step_count in results:
+        flat[lo:lo + buffer.size] = buffer
+        assert same and step_count == 2
+    ref = _oracle_sgd_run(world, 2)
+    d = ag.safetensors_describe(str(tmp_path / "sgd.safetensors"))
+    assert sorted(d["entries"]) == sorted(f"buffer.{i}" for i in range(len(NUMELS)))
+    for i, (o, n) in enumerate(zip(L.offsets, NUMELS)):
+        assert np.array_equal(flat[o:o + n], ref.buffers[i])
+        want = ref.buffers[i].astype(np.float64)
+        assert abs(d["entries"][f"buffer.{i}"]["sum"] - float(want.sum())) <= 1e-9 * float(np.abs(want).sum()) + 1e-30

@@ -300,3 +300,117 @@ def test_roll_call_passes_when_everyone_is_there():
     assert not server.check(["oe/alive/1/0"]) and server.check(["oe/alive/5/0"])
     with pytest.raises(ValueError):
         PeerLiveness(server, 0, 2, 0.0)
+
+
+def _sgd_state_worker(rank, world, port, out_dir, queue):
+    """A gloo rank that holds its shard of momentum buffers in CPU tensors and uses the sharded SGD's
+    own save_state / load_state (the file code needs no GPU: only the tensors' home differs)."""
+    import torch
+    import torch.distributed as dist
+    from gograd_b200.zero1 import Zero1Schedule, Zero1SGD
+
+    class CpuSGDRank(Zero1SGD):
+        def __init__(self, momentum):
+            Zero1Schedule.__init__(self, NUMELS, GROUPS, 0.05, momentum, 0.0, 0.0, 1.0, rank, world)
+            self.torch, self.dist, self.pg = torch, dist, None
+            self.momentum, self.dampening, self.nesterov, self.maximize = momentum, 0.0, False, False
+            self.buffer = torch.zeros(self.layout.shard_len)
+            self.flags = torch.zeros(max(len(self.my_pieces), 1))
+            self.loaded = 0
+
+        def _device_sync(self):
+            pass
+
+        def _state_loaded(self):
+            self.loaded += 1
+
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    names = [f"t{i}" for i in range(len(NUMELS))]
+    shapes = [[n] for n in NUMELS]
+    opt = CpuSGDRank(0.9)
+    # tensor 1 (3 elements) never received a gradient: its buffer stays uninitialised
+    full = [np.random.default_rng(50 + i).normal(0, 1, n).astype(np.float32) for i, n in enumerate(NUMELS)]
+    for k, pc in enumerate(opt.my_pieces):
+        if pc.tensor == 1:
+            continue
+        a = pc.flat_offset - opt.lo
+        opt.buffer[a:a + pc.length] = torch.from_numpy(full[pc.tensor][pc.tensor_offset:pc.tensor_offset + pc.length])
+        opt.flags[k] = 1.0
+    opt.step_count = 7
+    path = os.path.join(out_dir, "sgd.safetensors")
+    opt.save_state(path, names, shapes)
+    fresh = CpuSGDRank(0.5)
+    fresh.load_state(path, names, shapes)
+    same = bool(torch.equal(fresh.buffer, opt.buffer)) and bool(torch.equal(fresh.flags, opt.flags))
+    errors = []
+    kept = fresh.buffer.clone()
+    for bad_names, bad_shapes in ((names[::-1], shapes), (names, [[n + 1] for n in NUMELS])):
+        try:
+            fresh.load_state(path, bad_names, bad_shapes)
+            errors.append("accepted")
+        except ValueError as e:
+            errors.append(str(e))
+    plain = CpuSGDRank(0.0)
+    try:
+        plain.load_state(path, names, shapes)
+        errors.append("accepted")
+    except ValueError as e:
+        errors.append(str(e))
+    untouched = bool(torch.equal(kept, fresh.buffer)) and fresh.loaded == 1 and plain.loaded == 0
+    # a tensor whose pieces disagree about being initialised cannot be written
+    torn = None
+    if world > 1:
+        split = CpuSGDRank(0.9)
+        split.step_count = 1
+        if rank == 0:
+            split.flags[:] = 1.0
+        try:
+            split.save_state(os.path.join(out_dir, "torn.safetensors"), names, shapes)
+            torn = "written"
+        except ValueError as e:
+            torn = str(e)
+    queue.put((rank, same, fresh.step_count, float(np.float32(fresh.momentum)), errors, untouched, torn))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_write_and_read_a_sharded_sgd_state_file(tmp_path):
+    """Sharded SGD state files on the CPU: two gloo ranks stream their pieces into one "gograd-sgd" file
+    (one entry per initialised tensor, one flag per tensor reassembled from the pieces' flags), read it
+    back piece by piece, reject files that do not fit before changing anything, and refuse to write a
+    tensor that is initialised on one owner only."""
+    import json
+
+    import torch.multiprocessing as mp
+    from gograd_b200 import autograd as ag
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_sgd_state_worker, args=(r, world, port, str(tmp_path), queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = sorted([queue.get(timeout=120) for _ in range(world)], key=lambda x: x[0])
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, same, step_count, momentum, errors, untouched, torn in results:
+        assert same and step_count == 7 and momentum == float(np.float32(0.9)) and untouched
+        assert "state count" in errors[0] and "state count" in errors[1] and "disagree on momentum" in errors[2]
+        assert "initialised on some ranks only" in torn
+    d = ag.safetensors_describe(str(tmp_path / "sgd.safetensors"))
+    assert sorted(d["entries"]) == sorted(f"buffer.{i}" for i in range(len(NUMELS)) if i != 1)
+    cfg = json.loads(d["metadata"]["optimizer"])
+    assert cfg["Initialized"] == [True, False, True, True, True] and cfg["StepCount"] == 7
+    assert list(cfg) == ["StepCount", "Names", "Shapes", "Options", "Initialized", "Buffers", "Groups"]
+    assert list(cfg["Options"]) == ["LR", "Momentum", "Dampening", "WeightDecay", "Nesterov", "Maximize"]
+    for i, n in enumerate(NUMELS):
+        if i == 1:
+            continue
+        want = np.random.default_rng(50 + i).normal(0, 1, n).astype(np.float32).astype(np.float64)
+        assert d["entries"][f"buffer.{i}"]["shape"] == [n]
+        assert abs(d["entries"][f"buffer.{i}"]["sum"] - float(want.sum())) <= 1e-9 * float(np.abs(want).sum())
+    assert not (tmp_path / "torn.safetensors").exists()
