@@ -119,24 +119,52 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------
 # CPU path (the reference's host optimizer, restated in C under oracle/)
 # ---------------------------------------------------------------------------------------
+def _host_available_bytes() -> int:
+    try:
+        import psutil
+        return int(psutil.virtual_memory().available)
+    except Exception:
+        try:
+            return os.sysconf("SC_AVPHYS_PAGES") * os.sysconf("SC_PAGE_SIZE")
+        except Exception:
+            return 0
+
+
+def _synthetic(n: int, std: float, block):
+    """n float32 values of the given spread: one seeded block of normals repeated (the CPU path's speed
+    does not depend on the values, and drawing 1.3 B fresh normals per array would take longer than the
+    timed steps)."""
+    import numpy as np
+    out = np.empty(n, np.float32)
+    scaled = (block * np.float32(std)).astype(np.float32)
+    for a in range(0, n, scaled.size):
+        k = min(scaled.size, n - a)
+        out[a:a + k] = scaled[:k]
+    return out
+
+
 def cpu_reference_run(ps, sample_params: int, steps: int, warmup: int, cores: int):
     """Times clip (serial float64 sum + in-place scale) and AdamW (per-tensor worker split)
-    on a bounded sample: the leading tensors of the workload up to sample_params elements."""
+    on the leading tensors of the workload up to sample_params elements (all of it when that
+    many fit)."""
     import numpy as np
 
     from gograd_b200 import paramsets
     from oracle import oracle
     sample = paramsets.scaled(ps, sample_params)
     rng = np.random.default_rng(ps.grad_seed)
-    params = [(rng.standard_normal(s.numel, dtype=np.float32) * np.float32(0.02)) for s in sample.params]
-    grads0 = [(rng.standard_normal(s.numel, dtype=np.float32) * np.float32(ps.grad_std)) for s in sample.params]
+    block = rng.standard_normal(1 << 24, dtype=np.float32)
+    params = [_synthetic(s.numel, 0.02, block) for s in sample.params]
+    grads0 = [_synthetic(s.numel, ps.grad_std, block[::-1]) for s in sample.params]
     wd = sample.groups[0].weight_decay
     opt = oracle.OracleAdamW(params, lr=ps.hparams["lr"], weight_decay=wd, beta1=ps.hparams["beta1"],
                              beta2=ps.hparams["beta2"], eps=ps.hparams["eps"], max_procs=cores)
     n = sum(s.numel for s in sample.params)
+    grads = [np.empty_like(g) for g in grads0]
     times = []
     for it in range(warmup + steps):
-        grads = [g.copy() for g in grads0]  # fresh gradients; the copy is outside the timed region
+        for dst, src in zip(grads, grads0):   # fresh gradients; the copy is outside the timed region
+            np.copyto(dst, src)
         t0 = time.perf_counter()
         if ps.max_norm > 0:
             oracle.clip_grad_norm(grads, ps.max_norm)
@@ -145,14 +173,20 @@ def cpu_reference_run(ps, sample_params: int, steps: int, warmup: int, cores: in
         if it >= warmup:
             times.append(dt)
     sec = sum(times) / len(times)
+    whole = n == ps.numel
     return {"value": n / sec / 1e9, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": f"{len(sample.params)} leading tensors of {ps.key} = {n} params, {steps} steps after {warmup} warm-up; "
+            "sample": (f"the whole {ps.key} set" if whole else f"{len(sample.params)} leading tensors of {ps.key}") +
+                      f" = {n} params, {steps} steps after {warmup} warm-up; "
                       "C restatement of the Go host optimizer (AdamW split over min(cores, n/65536) workers per tensor, "
                       "clip single-threaded, as the reference)",
             "ms_per_step_sample": sec * 1e3}, n, sec
 
 
 def run_reference_arm(args):
+    """The reference's CPU implementation of the path on this host's cores: the configured number
+    of steps and warm-up steps, on the whole parameter set when the host can hold it (20 bytes per
+    parameter: p, g, m, v and the per-step fresh copy of g) and a step stays within seconds, else on
+    the leading tensors that fit, which config.note then says."""
     from gograd_b200 import paramsets
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -160,16 +194,25 @@ def run_reference_arm(args):
     key = args.workload if args.workload != "auto" else ("llama1b" if args.gpus == 1 else "llama8b")
     ps = paramsets.get(key)
     cores = os.cpu_count() or 1
-    steps = max(1, min(args.steps, 10))
-    warmup = max(1, min(args.warmup, 2))
-    base, n, sec = cpu_reference_run(ps, args.cpu_sample_params, steps, warmup, cores)
+    steps, warmup = max(1, args.steps), max(1, args.warmup)
+    available = _host_available_bytes()
+    by_memory = int(available * 0.7) // 20
+    # about 0.6 Gparams/s on 16 cores: 2e9 parameters keep a step near three seconds, so that
+    # steps + warm-up of the default run end within a few minutes
+    by_time = 2_000_000_000
+    limit = args.reference_sample_params or min(by_memory, by_time)
+    limit = max(limit, 1)
+    note = ("the reference is Go (no toolchain in this image): CPU host path restated in C, all host threads; "
+            f"host memory available {available / 1e9:.0f} GB")
+    if limit < ps.numel:
+        note += (f"; the {ps.numel}-parameter set is timed on its leading tensors up to {limit} parameters "
+                 "(host memory or step-time bound) and reported per parameter")
+    base, n, sec = cpu_reference_run(ps, limit, steps, warmup, cores)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "strong" if args.gpus > 1 else "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": key, "params_total": ps.numel, "params_in_sample": n,
-                   "note": "the reference is Go (no toolchain in this image): CPU host path restated in C, all host "
-                           "threads, bounded sample per step"},
+        "config": {"workload": key, "params_total": ps.numel, "params_in_sample": n, "note": note},
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -455,6 +498,8 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-params", type=int, default=120_000_000)
+    ap.add_argument("--reference-sample-params", type=int, default=0,
+                    help="--impl reference: parameters timed per step (0 = the whole set when host memory and step time allow)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

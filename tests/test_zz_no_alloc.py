@@ -30,8 +30,10 @@ def test_static_norm_matches_plan_norm_twice():
     stream = int(torch.cuda.current_stream().cuda_stream)
     out = torch.full((1,), -1.0, dtype=torch.float32, device="cuda")
     rng = np.random.default_rng(42)
-    # first a long buffer with a ragged tail, then a short one 4 bytes off a 16-byte boundary
-    for numel, offset, scale in ((3_000_001, 0, 1e-3), (70_001, 1, 5.0)):
+    # first a long buffer with a ragged tail, then a short one 4 bytes off a 16-byte boundary, then
+    # a buffer longer than the persistent grid's first sweep (148 SMs x 4 CTAs x 65536 elements), and
+    # one that crosses several spans on the element-by-element path (base 4 bytes off the boundary)
+    for numel, offset, scale in ((3_000_001, 0, 1e-3), (70_001, 1, 5.0), (45_000_003, 0, 2e-3), (400_003, 1, 0.5)):
         host = (rng.standard_normal(numel + offset) * scale).astype(np.float32)
         backing = torch.from_numpy(host).cuda()
         g = backing[offset:]
