@@ -457,16 +457,39 @@ def run_secondary(args):
     record("oe_zero_grads (4 B)", 4, timed(lambda: plain.zero_grads(stream)))
     big = max(range(len(state.p)), key=lambda i: state.p[i].numel())
     src, dst = state.p[big], state.shadow[big]
-    ms = timed(lambda: eng.cast_bf16(src, dst, stream))
-    out["oe_cast_bf16 (6 B), one %d-element tensor" % src.numel()] = {
-        "bytes_per_param": 6, "ms": ms, "GB/s": 6 * src.numel() / (ms * 1e-3) / 1e9,
-        "frac_of_peak": 6 * src.numel() / (ms * 1e-3) / 1e9 / peak}
+    lib = _lib.lib()
+    s_int = int(stream.cuda_stream)
     norm_out = torch.zeros(1, device="cuda:0")
-    ms = timed(lambda: _lib.check(_lib.lib().oe_grad_norm_static(0, src.data_ptr(), src.numel(), norm_out.data_ptr(),
-                                                                 int(stream.cuda_stream))))
-    out["oe_grad_norm_static (4 B), same tensor"] = {"bytes_per_param": 4, "ms": ms,
-                                                      "GB/s": 4 * src.numel() / (ms * 1e-3) / 1e9,
-                                                      "frac_of_peak": 4 * src.numel() / (ms * 1e-3) / 1e9 / peak}
+
+    def record_n(name, bytes_per_elem, elems, ms):
+        gbs = bytes_per_elem * elems / (ms * 1e-3) / 1e9
+        out[name] = {"bytes_per_param": bytes_per_elem, "elements": elems, "ms": ms, "GB/s": gbs, "frac_of_peak": gbs / peak}
+
+    # the two per-buffer entry points at three sizes: one tensor (a 50-70 us launch, ramp and tail
+    # included), every tensor of the set back to back, and one buffer that streams for a millisecond
+    record_n("oe_cast_bf16 (6 B), one %d-element tensor" % src.numel(), 6, src.numel(),
+             timed(lambda: eng.cast_bf16(src, dst, stream)))
+
+    def cast_all():
+        for a, b in zip(state.p, state.shadow):
+            eng.cast_bf16(a, b, stream)
+
+    record_n("oe_cast_bf16 (6 B), all %d tensors back to back" % len(state.p), 6, n, timed(cast_all, iters=5, warm=2))
+    record_n("oe_grad_norm_static (4 B), one %d-element tensor" % src.numel(), 4, src.numel(),
+             timed(lambda: _lib.check(lib.oe_grad_norm_static(0, src.data_ptr(), src.numel(), norm_out.data_ptr(), s_int))))
+
+    def norm_all():
+        for a in state.g:
+            _lib.check(lib.oe_grad_norm_static(0, a.data_ptr(), a.numel(), norm_out.data_ptr(), s_int))
+
+    record_n("oe_grad_norm_static (4 B), all %d tensors back to back" % len(state.g), 4, n, timed(norm_all, iters=5, warm=2))
+    long_elems = 1 << 30
+    long_src = torch.empty(long_elems, dtype=torch.float32, device="cuda:0").normal_(0.0, 1e-3)
+    long_dst = torch.empty(long_elems, dtype=torch.bfloat16, device="cuda:0")
+    record_n("oe_cast_bf16 (6 B), one 2^30-element buffer", 6, long_elems, timed(lambda: eng.cast_bf16(long_src, long_dst, stream)))
+    record_n("oe_grad_norm_static (4 B), one 2^30-element buffer", 4, long_elems,
+             timed(lambda: _lib.check(lib.oe_grad_norm_static(0, long_src.data_ptr(), long_elems, norm_out.data_ptr(), s_int))))
+    record_n("oe_grad_sumsq (4 B), the plan's norm over the whole set, for comparison", 4, n, timed(lambda: plain.grad_norm(0, stream)))
     print(json.dumps({"secondary_kernels": out, "params": n, "workload": ps.key, "peak_GBs": peak, "peak_kind": peak_kind}))
     return 0
 
@@ -480,7 +503,7 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--variant", default="")
     ap.add_argument("--chunk", type=int, default=0)
-    ap.add_argument("--comm", default="peer", choices=["peer", "abi", "nccl"],
+    ap.add_argument("--comm", default="abi", choices=["peer", "abi", "nccl"],
                     help="N > 1: fused peer-memory kernels ordered by tiny NCCL all-reduces (peer) or by the library's own "
                          "bounded exchanges, one C call per step (abi); or NCCL reduce-scatter / all-gather around the "
                          "single-GPU kernels (nccl)")

@@ -1,6 +1,7 @@
 #include "driver.h"
 
 #include <dlfcn.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <string>
@@ -18,7 +19,19 @@ std::once_flag g_once;
 #define OE_STR(x) OE_STR2(x)
 
 void load() {
-    void* h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
+    // OE_CUDA_DRIVER_LIBRARY names the driver library to bind instead of the system's libcuda.so.1:
+    // a driver installed in an unusual place, or the recording stand-in the CPU tests use.
+    const char* chosen = getenv("OE_CUDA_DRIVER_LIBRARY");
+    void* h = nullptr;
+    if (chosen && *chosen) {
+        h = dlopen(chosen, RTLD_NOW | RTLD_LOCAL);
+        if (!h) {
+            const char* e = dlerror();
+            g_why = std::string("CUDA driver library named by OE_CUDA_DRIVER_LIBRARY could not be loaded: ") + (e ? e : chosen);
+            return;
+        }
+    }
+    if (!h) h = dlopen("libcuda.so.1", RTLD_NOW | RTLD_GLOBAL);
     if (!h) h = dlopen("libcuda.so", RTLD_NOW | RTLD_GLOBAL);
     if (!h) {
         const char* e = dlerror();

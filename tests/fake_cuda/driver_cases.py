@@ -1,0 +1,169 @@
+"""Host-logic cases of liboptengine.so run against the recording stand-in driver (child process of
+tests/test_shim_host_logic_cpu.py; prints one JSON object). No GPU, no arithmetic."""
+import ctypes as C
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from gograd_b200 import _lib  # noqa: E402
+
+fake = C.CDLL(os.environ["OE_CUDA_DRIVER_LIBRARY"])
+fake.fake_cuda_calls.restype = C.c_long
+fake.fake_cuda_calls.argtypes = [C.c_char_p]
+fake.fake_cuda_fail.argtypes = [C.c_char_p, C.c_int, C.c_int, C.c_int]
+fake.fake_cuda_live_allocations.restype = C.c_long
+lib = _lib.lib()
+out = {}
+
+
+def launches():
+    rec = []
+    name, grid, block = C.create_string_buffer(64), C.c_uint(), C.c_uint()
+    i = 0
+    while fake.fake_cuda_launch(i, name, 64, C.byref(grid), C.byref(block)):
+        rec.append((name.value.decode(), grid.value, block.value))
+        i += 1
+    return rec
+
+
+def err():
+    return lib.oe_last_error().decode()
+
+
+class Buffers:
+    """"Device" buffers from the stand-in's allocator (host memory), kept alive for the run."""
+
+    def __init__(self):
+        self.addresses = []
+
+    def alloc(self, nbytes):
+        a = C.c_uint64()
+        assert lib.oe_mem_alloc(0, nbytes, C.byref(a)) == 0, err()
+        self.addresses.append(a.value)
+        return a.value
+
+
+assert lib.oe_init(0) == 0, err()
+assert lib.oe_device_sm_count(0) == 148
+buf = Buffers()
+
+
+def desc(numel, with_grad=True, wd=0.1, misalign=0):
+    p, g, m, v, sh = (buf.alloc(4 * numel + 64) for _ in range(5))
+    return _lib.oe_tensor_desc(p, (g + misalign) if with_grad else 0, m, v, sh, numel, 1.0, wd)
+
+
+def descs(*items):
+    arr = (_lib.oe_tensor_desc * len(items))(*items)
+    return arr, len(items)
+
+
+hp = _lib.oe_adamw_hparams(1e-3, 0.9, 0.999, 1e-8, 0.1, 0.001, 1.0, _lib.OE_WRITE_SHADOW, 0, 0)
+
+# ---- 1. tables: one row per tensor with a gradient, one work unit per chunk_elems elements ---------
+a, b, c = desc(10_000), desc(5, with_grad=False), desc(4096 * 3 + 1, misalign=4)
+arr, n = descs(a, b, c)
+plan = C.c_void_p()
+assert lib.oe_plan_create(0, arr, n, 4096, C.byref(plan)) == 0, err()
+out["tables"] = {"active": lib.oe_plan_info(plan, 0), "chunks": lib.oe_plan_info(plan, 1),
+                 "elems": lib.oe_plan_info(plan, 2), "uploads": lib.oe_plan_info(plan, 6)}
+fake.fake_cuda_reset_launches()
+assert lib.oe_grad_norm(plan, 0, 0) == 0, err()
+assert lib.oe_adamw_step(plan, C.byref(hp), 0) == 0, err()
+assert lib.oe_zero_grads(plan, 0) == 0, err()
+out["launches"] = launches()
+
+# ---- 2. an unchanged list uploads nothing; a changed one uploads once --------------------------------
+before = lib.oe_plan_info(plan, 6)
+assert lib.oe_plan_update(plan, arr, n, 0) == 0
+same = lib.oe_plan_info(plan, 6) - before
+b2 = desc(5)                       # the second parameter now has a gradient
+arr2, _ = descs(a, b2, c)
+assert lib.oe_plan_update(plan, arr2, n, 0) == 0, err()
+out["uploads"] = {"unchanged": same, "changed": lib.oe_plan_info(plan, 6) - before, "active": lib.oe_plan_info(plan, 0)}
+
+# ---- 3. a failed table growth: nothing launches until an update succeeds -----------------------------
+big = [desc(4096 * 40) for _ in range(12)]   # needs more rows and more work units than the tables hold
+arr3, n3 = descs(*big)
+fake.fake_cuda_fail(b"cuMemAlloc", 0, 2, 0)   # the next device allocation reports out of memory
+rc_update = lib.oe_plan_update(plan, arr3, n3, 0)
+message = err()
+fake.fake_cuda_reset_launches()
+rc_step = lib.oe_adamw_step(plan, C.byref(hp), 0)
+step_message = err()
+rc_norm = lib.oe_grad_norm(plan, 0, 0)
+rc_zero = lib.oe_zero_grads(plan, 0)
+rc_same = lib.oe_plan_update(plan, arr3, n3, 0)           # the same list again: must upload, not return early
+assert lib.oe_adamw_step(plan, C.byref(hp), 0) == 0, err()
+out["failed_growth"] = {"update": rc_update, "message": message, "step": rc_step, "step_message": step_message,
+                        "norm": rc_norm, "zero": rc_zero, "retry": rc_same, "launches_after_retry": launches(),
+                        "active": lib.oe_plan_info(plan, 0)}
+
+# ---- 4. a failed copy of the tables (the allocation succeeded): same rule ------------------------------
+arr4, n4 = descs(a, c)
+fake.fake_cuda_fail(b"cuMemcpyHtoDAsync", 0, 719, 0)
+rc_update = lib.oe_plan_update(plan, arr4, n4, 0)
+fake.fake_cuda_reset_launches()
+rc_step = lib.oe_adamw_step(plan, C.byref(hp), 0)
+launched = len(launches())
+rc_retry = lib.oe_plan_update(plan, arr4, n4, 0)
+rc_step2 = lib.oe_adamw_step(plan, C.byref(hp), 0)
+out["failed_copy"] = {"update": rc_update, "step": rc_step, "launched": launched, "retry": rc_retry, "step_after": rc_step2,
+                      "active": lib.oe_plan_info(plan, 0)}
+
+# ---- 5. validation happens before anything is launched or changed -----------------------------------
+fake.fake_cuda_reset_launches()
+bad = _lib.oe_adamw_hparams(1e-3, 1.5, 0.999, 1e-8, 0.1, 0.001, 1.0, 0, 0, 0)
+rc_bad = lib.oe_adamw_step(plan, C.byref(bad), 0)
+odd = _lib.oe_tensor_desc(buf.alloc(64) + 2, 0, 0, 0, 0, 4, 1.0, 0.0)
+arr5, _ = descs(odd)
+uploads = lib.oe_plan_info(plan, 6)
+rc_odd = lib.oe_plan_update(plan, arr5, 1, 0)
+out["validation"] = {"bad_beta": rc_bad, "odd_address": rc_odd, "launched": len(launches()),
+                     "uploads_unchanged": lib.oe_plan_info(plan, 6) == uploads, "still_steps": lib.oe_adamw_step(plan, C.byref(hp), 0)}
+
+# ---- 6. the sharded step driven through the library alone: five launches in order ---------------------
+z = C.c_void_p()
+d = _lib.oe_zero1_desc()
+d.rank, d.world, d.first_elem, d.numel = 1, 2, 4096, 4096
+grads = [buf.alloc(4 * 8192), buf.alloc(4 * 8192)]
+shadow = [buf.alloc(2 * 8192), buf.alloc(2 * 8192)]
+sync = [buf.alloc(512), buf.alloc(512)]
+for k in range(2):
+    d.grad_bases[k], d.sync_blocks[k] = grads[k], sync[k]
+    d.shadow_deltas[k] = shadow[k] - shadow[1]
+shard = _lib.oe_tensor_desc(buf.alloc(4 * 4096), grads[1] + 4 * 4096, buf.alloc(4 * 4096), buf.alloc(4 * 4096),
+                            shadow[1] + 2 * 4096, 4096, 1.0, 0.1)
+arr6, _ = descs(shard)
+plan2 = C.c_void_p()
+assert lib.oe_plan_create(0, arr6, 1, 0, C.byref(plan2)) == 0, err()
+assert lib.oe_zero1_create(plan2, C.byref(d), C.byref(z)) == 0, err()
+twice = lib.oe_zero1_create(plan2, C.byref(d), C.byref(C.c_void_p()))
+fake.fake_cuda_reset_launches()
+assert lib.oe_zero1_adamw_step(z, C.byref(hp), 0) == 0, err()
+seq = [x[0] for x in launches()]
+fake.fake_cuda_reset_launches()
+rc_bad_step = lib.oe_zero1_adamw_step(z, C.byref(bad), 0)   # refused before the first launch of the step
+bad_launched = len(launches())
+d_bad = _lib.oe_zero1_desc.from_buffer_copy(d)
+d_bad.rank = 2
+rc_rank = lib.oe_zero1_create(plan2, C.byref(d_bad), C.byref(C.c_void_p()))
+assert lib.oe_zero1_destroy(z) == 0
+out["zero1"] = {"sequence": seq, "second_create": twice, "bad_step": rc_bad_step, "bad_launched": bad_launched,
+                "bad_rank": rc_rank}
+
+# ---- 7. shutdown refuses while plans live; everything the library allocated is returned -------------------
+rc_shutdown_live = lib.oe_shutdown()
+assert lib.oe_plan_destroy(plan) == 0 and lib.oe_plan_destroy(plan2) == 0
+for addr in buf.addresses:
+    assert lib.oe_mem_free(0, addr) == 0
+out["teardown"] = {"shutdown_with_live_plans": rc_shutdown_live, "shutdown": lib.oe_shutdown(),
+                   "leaked_allocations": fake.fake_cuda_live_allocations()}
+
+# ---- 8. another architecture is refused ----------------------------------------------------------------------
+fake.fake_cuda_set_device(9, 0, 132)
+out["arch"] = {"rc": lib.oe_init(1), "message": err()}
+print(json.dumps(out))

@@ -1,0 +1,77 @@
+"""Host logic of liboptengine.so on the CPU: the library is pointed at a recording stand-in for the
+CUDA driver (tests/fake_cuda/fake_cuda.cpp: device memory is host memory, kernels are recorded, not
+run, any driver call can be made to fail), and a child process drives the C ABI through table building,
+updates, injected driver failures, validation, the sharded step's launch sequence and teardown."""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def cases(tmp_path_factory):
+    cxx = shutil.which("g++")
+    cuda_h = "/usr/local/cuda/include/cuda.h"
+    if cxx is None or not os.path.exists(cuda_h):
+        pytest.skip("needs g++ and cuda.h to build the stand-in driver")
+    lib = tmp_path_factory.mktemp("fake_cuda") / "libcuda_standin.so"
+    subprocess.run([cxx, "-std=c++17", "-O1", "-fPIC", "-shared", "-I/usr/local/cuda/include", "-o", str(lib),
+                    os.path.join(ROOT, "tests", "fake_cuda", "fake_cuda.cpp")], check=True)
+    env = dict(os.environ, OE_CUDA_DRIVER_LIBRARY=str(lib))
+    run = subprocess.run([sys.executable, os.path.join(ROOT, "tests", "fake_cuda", "driver_cases.py")], env=env,
+                         capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0, run.stderr[-2000:]
+    return json.loads(run.stdout.strip().splitlines()[-1])
+
+
+def test_tables_and_launch_shapes(cases):
+    # 10,000 elements = 3 units of 4096; 12,289 = 4 units; the parameter without a gradient has no row
+    assert cases["tables"] == {"active": 2, "chunks": 7, "elems": 22_289, "uploads": 1}
+    names = [x[0] for x in cases["launches"]]
+    assert names == ["oe_grad_sumsq", "oe_adamw_fused", "oe_zero_grads"]
+    (_, norm_grid, block), (_, update_grid, _), (_, zero_grid, _) = cases["launches"]
+    assert block == 256 and norm_grid == 4 and update_grid == 7 and zero_grid == 7   # spans of two units; one CTA per unit
+
+
+def test_update_uploads_only_on_change(cases):
+    assert cases["uploads"] == {"unchanged": 0, "changed": 1, "active": 3}
+
+
+def test_a_failed_table_growth_never_launches_with_stale_tables(cases):
+    """The allocation of a larger table fails (a caller whose arena owns the GPU sees exactly this):
+    the update reports it, every launch path then refuses the plan instead of launching with a missing
+    table, and the same descriptor list uploads on the next call instead of being taken for unchanged."""
+    f = cases["failed_growth"]
+    assert f["update"] == 2 and "cuMemAlloc" in f["message"] and "OUT_OF_MEMORY" in f["message"]
+    assert f["step"] == -1 and "stale" in f["step_message"] and f["norm"] == -1 and f["zero"] == -1
+    assert f["retry"] == 0 and f["active"] == 12
+    assert [x[0] for x in f["launches_after_retry"]] == ["oe_adamw_fused"], "nothing launched before the retry"
+
+
+def test_a_failed_table_copy_is_handled_the_same_way(cases):
+    f = cases["failed_copy"]
+    assert f["update"] == 719 and f["step"] == -1 and f["launched"] == 0
+    assert f["retry"] == 0 and f["step_after"] == 0 and f["active"] == 2
+
+
+def test_validation_comes_before_any_launch_or_change(cases):
+    v = cases["validation"]
+    assert v == {"bad_beta": -1, "odd_address": -1, "launched": 0, "uploads_unchanged": True, "still_steps": 0}
+
+
+def test_sharded_step_is_five_launches_in_order(cases):
+    z = cases["zero1"]
+    assert z["sequence"] == ["oe_rank_exchange", "oe_peer_reduce_sumsq_n2", "oe_rank_exchange", "oe_adamw_fused_peers",
+                             "oe_rank_exchange"]
+    assert z["second_create"] == -1 and z["bad_step"] == -1 and z["bad_launched"] == 0 and z["bad_rank"] == -1
+
+
+def test_teardown_and_architecture_check(cases):
+    t = cases["teardown"]
+    assert t["shutdown_with_live_plans"] == -1 and t["shutdown"] == 0 and t["leaked_allocations"] == 0
+    assert cases["arch"]["rc"] == -4 and "sm_90" in cases["arch"]["message"]
