@@ -367,6 +367,9 @@ def run_single(args):
     roofline = {"bound": "hbm", "kernel": "oe_sgd_fused" if is_sgd else "oe_adamw_fused", "achieved": achieved, "peak": peak, "unit": "GB/s",
                 "frac": achieved / peak, "peak_kind": peak_kind,
                 "traffic": None if traffic is None else traffic * n_params,
+                "traffic_source": None if traffic is None else
+                "not measured in this run: dram__bytes_read.sum + dram__bytes_write.sum per parameter from the ncu capture "
+                "summarised in profiles/oe_adamw_fused_gpt110m_ncu_full.md (109.6 M-parameter set), scaled by the parameter count",
                 "algorithmic_bytes_per_launch": BYTES_UPDATE * n_params, "kernel_ms": upd_ms,
                 "frac_of_nominal_8TBs": achieved / NOMINAL_HBM_GBS,
                 "norm_kernel": {"kernel": "oe_grad_sumsq", "kernel_ms": norm_ms,
@@ -513,6 +516,8 @@ def main():
     ap.add_argument("--reduce-grid", type=int, default=0)
     ap.add_argument("--update-grid", type=int, default=0)
     ap.add_argument("--push-warp-rotate", action="store_true")
+    ap.add_argument("--sweep", action="store_true",
+                    help="N > 1: time the two peer kernels over every launch-shape knob instead of the step")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")
     ap.add_argument("--secondary", action="store_true", help="time the other kernels of the path instead of the step")
     ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")

@@ -56,6 +56,17 @@ def run(args) -> int:
     stream = torch.cuda.current_stream()
 
     parity = None if args.no_parity_check else parity_check(opt, torch, dist)
+    if args.sweep:
+        records = launch_shape_sweep(opt, torch, dist)
+        if rank == 0:
+            sys.stdout.flush()
+            os.dup2(real_stdout, 1)
+            print(json.dumps({"launch_shape_sweep": records, "n_gpus": world, "workload": key, "comm": comm,
+                              "multicast_shadow_stores": bool(args.multicast), "parity_check": parity}), flush=True)
+            os.dup2(2, 1)
+        opt.close()
+        dist.destroy_process_group()
+        return 0 if (parity is None or parity["ok"]) else 3
 
     for _ in range(args.warmup):
         opt.step()
@@ -144,7 +155,7 @@ def run(args) -> int:
         reduce_floor = max(pull_remote / (NVLINK_PEER_GBS * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) * 1e3
         update_floor = max(30.0 * shard / (peak * 1e9), push_remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
         roofline = {
-            "bound": "nvlink", "kernel": "oe_peer_reduce_sumsq (pull reduce-scatter + norm)" if comm == "peer" else "ncclReduceScatter",
+            "bound": "nvlink", "kernel": "oe_peer_reduce_sumsq (pull reduce-scatter + norm)" if comm != "nccl" else "ncclReduceScatter",
             "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
             "frac": (pull_remote / (k1 * 1e-3) / 1e9 / NVLINK_PEER_GBS) if k1 else None,
             "peak_kind": "builder constant: 770 GB/s, a one-at-a-time copy-engine peer copy measured on this pool "
@@ -154,7 +165,7 @@ def run(args) -> int:
             "traffic_source": "none: the bytes that cross NVLink are not DRAM traffic of this GPU; ncu is not run on "
                               "multi-rank commands",
             "algorithmic_bytes_per_launch": pull_remote, "kernel_ms": k1,
-            "update_kernel": {"kernel": "oe_adamw_fused_peers" if comm == "peer" else "oe_adamw_fused + ncclAllGather",
+            "update_kernel": {"kernel": "oe_adamw_fused_peers" if comm != "nccl" else "oe_adamw_fused + ncclAllGather",
                               "kernel_ms": k2, "remote_store_bytes": push_remote,
                               "nvlink_achieved": push_remote / (k2 * 1e-3) / 1e9 if k2 else None,
                               "nvlink_frac_of_770_builder_constant": push_remote / (k2 * 1e-3) / 1e9 / NVLINK_PEER_GBS if k2 else None,
@@ -207,6 +218,87 @@ def apply_tuning(opt, args):
         opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 1)
         chosen["push_warp_rotate"] = True
     return chosen
+
+
+def launch_shape_sweep(opt, torch, dist, iters: int = 3):
+    """Times the two peer kernels of the step over every launch-shape knob the library exposes
+    (grid sizes, first-issued source rank, store order), one kernel at a time with a barrier before
+    each launch, max over ranks. A diagnostic for a new machine; no knob changes a result."""
+    from gograd_b200 import engine as E
+    from gograd_b200.engine import OE_PARTIAL_ONLY, OE_WRITE_SHADOW
+    world, rank = opt.world, opt.rank
+    dev = opt.master.device
+    stream = torch.cuda.current_stream()
+    shard = opt.layout.shard_len
+    pull_bytes, push_bytes = 4.0 * shard * (world - 1), 2.0 * shard * (world - 1)
+    own = opt.grad_flat[opt.lo:opt.hi]
+    records = []
+
+    def timed(fn):
+        vals = []
+        for _ in range(iters):
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            vals.append(a.elapsed_time(b))
+        t = torch.tensor([statistics.median(vals)], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def pull():
+        opt.plan.peer_reduce_grads(opt.grad_bases, opt.lo, shard, own.data_ptr(), 1.0 / world, OE_PARTIAL_ONLY)
+
+    for grid in (0, 148, 74):
+        for first in ("rank0", "rank+1"):
+            opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_GRID, grid)
+            opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, (rank + 1) % world if first == "rank+1" else 0)
+            ms = timed(pull)
+            records.append({"kernel": "oe_peer_reduce_sumsq", "grid": grid or "default", "first_source": first, "ms": ms,
+                            "pulled_GBs": pull_bytes / ms / 1e6})
+    opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_GRID, 0)
+    opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, 0)
+    # a norm for the updates that follow
+    if opt.comm == "abi":
+        opt.ctx.exchange(0)
+        pull()
+        opt.ctx.exchange(1)
+    else:
+        pull()
+        dist.all_reduce(opt.sumsq)
+        opt.plan.norm_finalize()
+    opt.step_count += 1
+    hp = opt._hparams(OE_WRITE_SHADOW)
+    keep_order = opt.push_order
+    if opt.multicast:
+        for grid in (0, 148, 74):
+            opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, grid)
+            ms = timed(lambda: opt.plan.adamw_step_multicast(hp, opt.shadow_deltas, opt.mc_delta))
+            records.append({"kernel": "oe_adamw_fused_peers (multimem.st)", "grid": grid or "default", "ms": ms,
+                            "received_GBs": push_bytes / ms / 1e6})
+    else:
+        for grid in (0, 148):
+            for order in ("ascending", "rotated"):
+                for warp_rotate in (0, 1):
+                    opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, grid)
+                    opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, warp_rotate)
+                    opt.push_order = order
+                    ms = timed(lambda: opt.plan.adamw_step_peers(hp, opt._push_deltas()))
+                    records.append({"kernel": "oe_adamw_fused_peers", "grid": grid or "default", "store_order": order,
+                                    "warp_rotate": bool(warp_rotate), "ms": ms, "pushed_GBs": push_bytes / ms / 1e6})
+    opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, 0)
+    opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 0)
+    opt.push_order = keep_order
+    if opt.comm == "abi":
+        opt.ctx.exchange(2)
+        records.append({"kernel": "oe_rank_exchange", "ms": timed(lambda: opt.ctx.exchange(0))})
+        opt.ctx.exchange(1)
+        opt.ctx.exchange(2)
+        opt.exchange_status()
+    return records
 
 
 def parity_check(opt, torch, dist, window: int = 65536):

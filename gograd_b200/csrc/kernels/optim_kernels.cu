@@ -625,25 +625,26 @@ oe_zero_grads(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __r
 // ---------------------------------------------------------------------------------
 extern "C" __global__ void __launch_bounds__(OE_THREADS, 4)
 oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t n) {
-    const uint64_t tid = (uint64_t)blockIdx.x * OE_THREADS + threadIdx.x;
-    const uint64_t stride = (uint64_t)gridDim.x * OE_THREADS;
     const bool aligned = (((uint64_t)src & 15u) == 0) && (((uint64_t)dst & 7u) == 0);
     uint64_t done = 0;
     if (aligned) {
+        // A CTA takes whole tiles of OE_THREADS x OE_UNROLL vectors (16 KB read, 8 KB written, both
+        // contiguous), tile after tile in steps of the grid: the layout of the update kernels' work
+        // units. Four 128-bit loads are in flight per thread before the first use.
         const uint64_t nvec = n >> 2;
         const float4* s4 = (const float4*)src;
         uint2* d2 = (uint2*)dst;
-        // four 128-bit loads in flight per thread before the first use, like the update kernels
-        for (uint64_t i0 = tid; i0 < nvec; i0 += stride * OE_UNROLL) {
+        const uint64_t tile = (uint64_t)OE_THREADS * OE_UNROLL;
+        for (uint64_t t0 = (uint64_t)blockIdx.x * tile; t0 < nvec; t0 += (uint64_t)gridDim.x * tile) {
             float4 x[OE_UNROLL];
 #pragma unroll
             for (int u = 0; u < OE_UNROLL; u++) {
-                uint64_t i = i0 + (uint64_t)u * stride;
+                uint64_t i = t0 + (uint64_t)u * OE_THREADS + threadIdx.x;
                 if (i < nvec) x[u] = __ldcs(s4 + i);
             }
 #pragma unroll
             for (int u = 0; u < OE_UNROLL; u++) {
-                uint64_t i = i0 + (uint64_t)u * stride;
+                uint64_t i = t0 + (uint64_t)u * OE_THREADS + threadIdx.x;
                 if (i < nvec) {
                     uint2 packed;
                     packed.x = oe_bf16_rne(x[u].x) | (oe_bf16_rne(x[u].y) << 16);
@@ -654,6 +655,8 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
         }
         done = nvec << 2;
     }
+    const uint64_t tid = (uint64_t)blockIdx.x * OE_THREADS + threadIdx.x;
+    const uint64_t stride = (uint64_t)gridDim.x * OE_THREADS;
     for (uint64_t i = done + tid; i < n; i += stride) dst[i] = (uint16_t)oe_bf16_rne(src[i]);
 }
 

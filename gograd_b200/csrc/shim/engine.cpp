@@ -879,8 +879,8 @@ extern "C" int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t num
     if (numel == 0) return 0;  // an empty launch is not an error (kernels/kernels_test.go:153-174)
     if (src == 0 || dst == 0 || (src & 3u) || (dst & 1u)) return fail(OE_ERR_INVALID, "oe_cast_bf16: bad address");
     CtxGuard guard(d, dc->ctx);
-    uint64_t vec_threads = (numel + 3) / 4;
-    uint64_t blocks = (vec_threads + kThreads - 1) / kThreads;
+    // one CTA per tile of 256 threads x 4 vectors x 4 elements, at most the persistent grid
+    uint64_t blocks = (numel + 4095) / 4096;
     uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_cast > 0 ? dc->occ_cast : 1);
     uint32_t grid = (uint32_t)(blocks < persistent ? blocks : persistent);
     void* args[] = {&src, &dst, &numel};
