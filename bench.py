@@ -239,6 +239,8 @@ def run_single(args):
     plan = eng.Plan(state.descs(), 0, args.chunk)
     if args.variant:
         plan.set_variant(args.variant)
+    if args.step_grid == "units":
+        plan.set_tuning(eng.engine.OE_TUNE_STEP_GRID, 1)
     n_params = state.numel
     hp = ps.hparams
     flags = OE_WRITE_SHADOW if ps.bf16_shadow else 0
@@ -497,6 +499,51 @@ def run_secondary(args):
     return 0
 
 
+def run_buffer_kernels(args):
+    """The two per-buffer entry points (oe_cast_bf16, oe_grad_norm_static) on ONE buffer of
+    --buffer-elems fp32 elements: a small, self-contained case (for a profiler capture, say)."""
+    import torch
+
+    import gograd_b200 as eng
+    from gograd_b200 import _lib
+
+    torch.cuda.set_device(0)
+    eng.init(0)
+    n = args.buffer_elems
+    stream = torch.cuda.current_stream()
+    s_int = int(stream.cuda_stream)
+    peak, peak_kind = measured_peak()
+    src = torch.empty(n, dtype=torch.float32, device="cuda:0").normal_(0.0, 1e-3)
+    dst = torch.empty(n, dtype=torch.bfloat16, device="cuda:0")
+    norm_out = torch.zeros(1, device="cuda:0")
+    lib = _lib.lib()
+
+    def timed(fn, iters=10, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for a, b in ev:
+            a.record(stream)
+            fn()
+            b.record(stream)
+        torch.cuda.synchronize()
+        return statistics.median(a.elapsed_time(b) for a, b in ev)
+
+    out = {}
+    for name, bytes_per, fn in (
+            ("oe_cast_bf16", 6, lambda: eng.cast_bf16(src, dst, stream)),
+            ("oe_grad_norm_static", 4, lambda: _lib.check(lib.oe_grad_norm_static(0, src.data_ptr(), n, norm_out.data_ptr(), s_int)))):
+        ms = timed(fn, iters=args.steps, warm=args.warmup)
+        gbs = bytes_per * n / (ms * 1e-3) / 1e9
+        out[name] = {"bytes_per_element": bytes_per, "ms": ms, "GB/s": gbs, "frac_of_peak": gbs / peak}
+    ok = bool(torch.equal(dst.view(torch.int16), src.to(torch.bfloat16).view(torch.int16)))
+    want = float(src.double().pow(2).sum().sqrt().item())
+    print(json.dumps({"buffer_kernels": out, "elements": n, "cast_equals_rne": ok,
+                      "norm_rel_err_vs_float64": abs(float(norm_out.item()) - want) / want, "peak_GBs": peak, "peak_kind": peak_kind}))
+    return 0 if ok else 3
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -506,6 +553,8 @@ def main():
     ap.add_argument("--workload", default="auto")
     ap.add_argument("--variant", default="")
     ap.add_argument("--chunk", type=int, default=0)
+    ap.add_argument("--step-grid", default="persistent", choices=["persistent", "units"],
+                    help="N = 1: grid of the update launch (a persistent grid, or one CTA per work unit in table order)")
     ap.add_argument("--comm", default="abi", choices=["peer", "abi", "nccl"],
                     help="N > 1: fused peer-memory kernels ordered by tiny NCCL all-reduces (peer) or by the library's own "
                          "bounded exchanges, one C call per step (abi); or NCCL reduce-scatter / all-gather around the "
@@ -520,6 +569,8 @@ def main():
                     help="N > 1: time the two peer kernels over every launch-shape knob instead of the step")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")
     ap.add_argument("--secondary", action="store_true", help="time the other kernels of the path instead of the step")
+    ap.add_argument("--buffer-elems", type=int, default=0,
+                    help="time only the per-buffer entry points (bf16 cast, allocation-free norm) on one buffer of this many elements")
     ap.add_argument("--graph", action="store_true", help="also time the step captured in a CUDA graph and replayed")
     ap.add_argument("--graph-steps", type=int, default=1,
                     help="with --graph: also capture this many steps in one graph (shares the host's graph-launch cost)")
@@ -532,6 +583,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.buffer_elems > 0:
+        return run_buffer_kernels(args)
     if args.secondary:
         return run_secondary(args)
     world = int(os.environ.get("WORLD_SIZE", "1"))

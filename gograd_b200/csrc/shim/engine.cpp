@@ -5,6 +5,7 @@
 #include <math.h>
 #include <stddef.h>
 #include <stdint.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -183,6 +184,7 @@ struct oe_plan {
     bool tables_valid = false;  // the device tables describe `descs`; false after a failed update
     // tuning knobs of the peer kernels (0 = the library's choice); none changes a result
     uint32_t tune_reduce_grid = 0, tune_update_grid = 0, tune_reduce_first = 0, tune_push_warp_rotate = 0;
+    uint32_t tune_step_grid = 0;  // single-GPU update / scale launches: 0 = persistent grid, 1 = one CTA per work unit
     uint64_t status_word = 0;   // device address of a sharded step's status word, 0 = none
 };
 
@@ -588,6 +590,7 @@ extern "C" int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value) {
         case OE_TUNE_PEER_UPDATE_GRID: plan->tune_update_grid = (uint32_t)value; return 0;
         case OE_TUNE_PEER_REDUCE_FIRST: plan->tune_reduce_first = (uint32_t)value % OE_MAX_PEERS; return 0;
         case OE_TUNE_PEER_PUSH_WARP_ROTATE: plan->tune_push_warp_rotate = value ? 1u : 0u; return 0;
+        case OE_TUNE_STEP_GRID: plan->tune_step_grid = value ? 1u : 0u; return 0;
         default: return fail(OE_ERR_INVALID, "oe_plan_set_tuning: unknown knob");
     }
 }
@@ -655,8 +658,8 @@ extern "C" int oe_clip_grad_norm(oe_plan* plan, const float* max_norm, uint32_t 
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     float mx = *max_norm;
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &plan->d_norm, &mx, &flags};
-    return launch(d, plan->dc->k.scale, "oe_scale_grads", grid_for(plan, plan->dc->occ_scale), kThreads,
-                  (CUstream)stream, args);
+    return launch(d, plan->dc->k.scale, "oe_scale_grads", plan->tune_step_grid == 1 ? n_chunks : grid_for(plan, plan->dc->occ_scale),
+                  kThreads, (CUstream)stream, args);
 }
 
 extern "C" int oe_read_norm(oe_plan* plan, float* norm_out, double* sumsq_out, uint64_t stream) {
@@ -733,7 +736,7 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
                       kThreads, stream, peer_args);
     }
     uint32_t grid = grid_for(p, p->dc->occ_adamw[p->variant]);
-    if (grid > n_chunks) grid = n_chunks;
+    if (grid > n_chunks || p->tune_step_grid == 1) grid = n_chunks;
     void* args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a};
     return launch(d, p->dc->k.adamw[p->variant], kAdamwNames[p->variant], grid, kThreads, stream, args);
 }
@@ -818,7 +821,8 @@ int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_
                       kThreads, (CUstream)stream, peer_args);
     }
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
-    return launch(d, plan->dc->k.sgd, "oe_sgd_fused", grid_for(plan, plan->dc->occ_sgd), kThreads, (CUstream)stream, args);
+    return launch(d, plan->dc->k.sgd, "oe_sgd_fused", plan->tune_step_grid == 1 ? n_chunks : grid_for(plan, plan->dc->occ_sgd),
+                  kThreads, (CUstream)stream, args);
 }
 
 int peer_set_from(const int64_t* shadow_deltas, uint32_t n_ranks, const char* who, oe_peer_set* ps,
@@ -879,10 +883,10 @@ extern "C" int oe_cast_bf16(int device, uint64_t src, uint64_t dst, uint64_t num
     if (numel == 0) return 0;  // an empty launch is not an error (kernels/kernels_test.go:153-174)
     if (src == 0 || dst == 0 || (src & 3u) || (dst & 1u)) return fail(OE_ERR_INVALID, "oe_cast_bf16: bad address");
     CtxGuard guard(d, dc->ctx);
-    // one CTA per tile of 256 threads x 4 vectors x 4 elements, at most the persistent grid
+    // One CTA per tile of 256 threads x 4 vectors x 4 elements, in address order (see the kernel: a
+    // compact window sweeping the buffer beats a persistent grid by a quarter for this stream).
     uint64_t blocks = (numel + 4095) / 4096;
-    uint64_t persistent = (uint64_t)dc->sm_count * (uint64_t)(dc->occ_cast > 0 ? dc->occ_cast : 1);
-    uint32_t grid = (uint32_t)(blocks < persistent ? blocks : persistent);
+    uint32_t grid = (uint32_t)(blocks < 0x7fffffffull ? blocks : 0x7fffffffull);
     void* args[] = {&src, &dst, &numel};
     return launch(d, dc->k.cast, "oe_cast_bf16", grid, kThreads, (CUstream)stream, args);
 }

@@ -305,6 +305,8 @@ OE_API int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const 
 #define OE_TUNE_PEER_UPDATE_GRID      2
 #define OE_TUNE_PEER_REDUCE_FIRST     3
 #define OE_TUNE_PEER_PUSH_WARP_ROTATE 4
+#define OE_TUNE_STEP_GRID             5 /* single-GPU update and in-place clip launches: 0 = a persistent grid strides
+                                           over the work units, 1 = one CTA per work unit in table order */
 OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);
 
 /* ---- sharded step driven through this interface alone -------------------------------------------- */
