@@ -62,6 +62,34 @@ def ncu_traffic_per_param():
     return NCU_TRAFFIC_BYTES_PER_PARAM
 
 
+def bind_to_gpu_numa_node(gpu_index: int):
+    """Pins this process to the CPUs of the NUMA node the GPU hangs off, so that the page-locked
+    staging memory it allocates next (first touch) and the threads that feed the copies are local to
+    the GPU's PCIe root: what a host feeding eight GPUs at once has to do to keep every link busy.
+    Returns a short description for the JSON line, or None when the topology cannot be read."""
+    try:
+        import torch
+        props = torch.cuda.get_device_properties(gpu_index)
+        bus = "%04x:%02x:%02x.0" % (props.pci_domain_id, props.pci_bus_id, props.pci_device_id)
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as f:
+            node = int(f.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            text = f.read().strip()
+        cpus = set()
+        for part in text.split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return {"gpu": gpu_index, "pci": bus, "numa_node": node, "cpus": len(allowed)}
+    except Exception:
+        return None
+
+
 class ClockSampler:
     """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
@@ -443,10 +471,14 @@ def run_secondary(args):
     flags1 = [torch.zeros(1, device="cuda:0") for _ in state.p]
     descs = [eng.TensorDesc(state.p[i], state.g[i], state.s1[i], flags1[i], state.shadow[i]) for i in range(len(state.p))]
     plan = eng.Plan(descs, 0, args.chunk)
+    if args.step_grid == "units":
+        plan.set_tuning(eng.engine.OE_TUNE_STEP_GRID, 1)
     record("oe_sgd_fused momentum (20 B)", 20, timed(lambda: plan.sgd_step(eng.SGDHParams(1e-3, 0.9), stream)))
     record("oe_sgd_fused momentum + shadow (22 B)", 22,
            timed(lambda: plan.sgd_step(eng.SGDHParams(1e-3, 0.9, flags=eng.engine.OE_WRITE_SHADOW), stream)))
     plain = eng.Plan([eng.TensorDesc(state.p[i], state.g[i]) for i in range(len(state.p))], 0, args.chunk)
+    if args.step_grid == "units":
+        plain.set_tuning(eng.engine.OE_TUNE_STEP_GRID, 1)
     record("oe_sgd_fused plain (12 B)", 12, timed(lambda: plain.sgd_step(eng.SGDHParams(1e-3), stream)))
     plain.grad_norm(0, stream)
     # Halving max_norm on every call keeps the norm above it, so the scale kernel really rewrites

@@ -103,6 +103,7 @@ def run(args) -> int:
     e2e = None
     if not args.no_e2e:
         try:
+            numa = B.bind_to_gpu_numa_node(local)   # before the page-locked allocation: first touch decides the node
             stage_elems = 1 << 28  # 1 GiB staging buffer, reused for every range of the gradient buffer
             stage = torch.empty(stage_elems, dtype=torch.float32).pin_memory()
             stage.normal_(0.0, ps.grad_std)
@@ -129,7 +130,8 @@ def run(args) -> int:
             e2e = {"value": n_params / float(dt.item()) / 1e9, "unit": B.UNIT, "h2d_bytes_per_step": 4 * used * world,
                    "d2h_bytes_per_step": 32 * world, "ms_per_step": float(dt.item()) * 1e3, "steps": e2e_steps,
                    "api": "Zero1AdamW.step after copying every rank's full fp32 gradient buffer from page-locked host "
-                          "memory (1 GiB staging buffer reused per range), norm read back"}
+                          "memory (1 GiB staging buffer reused per range), norm read back",
+                   "numa_binding_rank0": numa}
             del stage
         except Exception as exc:
             e2e = {"value": None, "unit": B.UNIT, "error": str(exc)[:200]}
@@ -280,15 +282,19 @@ def launch_shape_sweep(opt, torch, dist, iters: int = 3):
             records.append({"kernel": "oe_adamw_fused_peers (multimem.st)", "grid": grid or "default", "ms": ms,
                             "received_GBs": push_bytes / ms / 1e6})
     else:
-        for grid in (0, 148):
-            for order in ("ascending", "rotated"):
-                for warp_rotate in (0, 1):
-                    opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, grid)
-                    opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, warp_rotate)
-                    opt.push_order = order
-                    ms = timed(lambda: opt.plan.adamw_step_peers(hp, opt._push_deltas()))
-                    records.append({"kernel": "oe_adamw_fused_peers", "grid": grid or "default", "store_order": order,
-                                    "warp_rotate": bool(warp_rotate), "ms": ms, "pushed_GBs": push_bytes / ms / 1e6})
+        shapes = [(4, g, "ascending", w) for g in (0, 222, 148, 111, 74, 37) for w in (0, 1)] + \
+                 [(4, g, "rotated", w) for g in (0, 148) for w in (0, 1)] + \
+                 [(2, g, "ascending", w) for g in (0, 296, 148) for w in (0, 1)]
+        for vectors, grid, order, warp_rotate in shapes:
+            opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_VECTORS, vectors)
+            opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, grid)
+            opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, warp_rotate)
+            opt.push_order = order
+            ms = timed(lambda: opt.plan.adamw_step_peers(hp, opt._push_deltas()))
+            records.append({"kernel": "oe_adamw_fused_peers", "vectors_in_flight": vectors, "grid": grid or "default",
+                            "store_order": order, "warp_rotate": bool(warp_rotate), "ms": ms,
+                            "pushed_GBs": push_bytes / ms / 1e6})
+        opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_VECTORS, 0)
     opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, 0)
     opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 0)
     opt.push_order = keep_order

@@ -39,7 +39,8 @@ extern "C" void oe_internal_set_error(const char* message);  // engine.cpp: feed
 namespace {
 
 constexpr int kThreads = 256;
-constexpr uint32_t kSpanElems = 65536;  // elements reduced by one CTA: one partial sum each
+constexpr uint32_t kSpanElems = 65536;  // elements behind one partial sum, for buffers that need all the slots
+constexpr uint32_t kShortSpanElems = 8192;  // ... for buffers short enough to afford finer spans (better balance)
 constexpr uint32_t kMaxSpans = 32768;   // partial sums the array can hold
 constexpr uint64_t kMaxElems = (uint64_t)kSpanElems * kMaxSpans;  // 2^31 elements, 8 GiB of fp32
 constexpr size_t kHeaderBytes = 256;    // arrival counter, padded to the array's alignment
@@ -66,22 +67,25 @@ __device__ __forceinline__ double block_sum(double x, double* warp_sums) {
 }
 
 // A persistent grid (resident CTAs x SMs, fewer for a short buffer) strides over the spans of
-// kSpanElems elements; a CTA reduces each of its spans to one float64 partial sum in the span's
-// own slot of the array. Float64 accumulation as in the plan-based reduction; the CTA that
-// arrives last adds the partial sums in span order, so the result depends only on the data and
-// its length, not on the grid or on timing.
+// span_elems elements; a CTA reduces each of its spans to one float64 partial sum in the span's
+// own slot of the array. The span is 8192 elements while the buffer fits the array's 32768 slots
+// that way (up to 2^28 elements: many spans per CTA, so the last sweep of the grid is short) and
+// 65536 beyond. Float64 accumulation as in the plan-based reduction; the CTA that arrives last
+// adds the partial sums in span order, so the result depends only on the data and its length,
+// not on the grid or on timing.
 __global__ void __launch_bounds__(kThreads, 4)
-oe_static_sumsq(const float* __restrict__ g, uint64_t numel, uint32_t n_spans, unsigned char* scratch, float* norm_out) {
+oe_static_sumsq(const float* __restrict__ g, uint64_t numel, uint32_t n_spans, uint32_t span_elems, unsigned char* scratch,
+                float* norm_out) {
     __shared__ double warp_sums[kThreads / 32];
     __shared__ uint32_t is_last;
     uint32_t* ticket = (uint32_t*)scratch;
     double* partials = (double*)(scratch + kHeaderBytes);
-    const bool vector_path = (((uint64_t)g) & 15u) == 0;  // spans start at multiples of 65536 elements: same alignment as g
+    const bool vector_path = (((uint64_t)g) & 15u) == 0;  // spans start at multiples of 8192 elements: same alignment as g
 
     for (uint32_t span = blockIdx.x; span < n_spans; span += gridDim.x) {
-        const uint64_t begin = (uint64_t)span * kSpanElems;
+        const uint64_t begin = (uint64_t)span * span_elems;
         const uint64_t left = begin < numel ? numel - begin : 0;
-        const uint32_t n = left < kSpanElems ? (uint32_t)left : kSpanElems;
+        const uint32_t n = left < span_elems ? (uint32_t)left : span_elems;
         const float* __restrict__ x = g + begin;
         double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
         uint32_t done = 0;
@@ -205,12 +209,13 @@ extern "C" OE_API int oe_grad_norm_static(int device, uint64_t grad, uint64_t nu
     // interrupted earlier could have left it half-counted.
     e = cudaMemsetAsync(scratch, 0, sizeof(uint32_t), s);
     if (e != cudaSuccess) return fail_rt(e, "cudaMemsetAsync(arrival counter)");
-    uint32_t spans = (uint32_t)((numel + kSpanElems - 1) / kSpanElems);  // 0 for an empty gradient: norm 0
+    uint32_t span_elems = numel <= (uint64_t)kShortSpanElems * kMaxSpans ? kShortSpanElems : kSpanElems;
+    uint32_t spans = (uint32_t)((numel + span_elems - 1) / span_elems);  // 0 for an empty gradient: norm 0
     uint32_t grid = spans < persistent ? spans : persistent;
     if (grid == 0) grid = 1;
     const float* g = (const float*)grad;
     float* out = (float*)norm_out;
-    void* args[] = {&g, &numel, &spans, &scratch, &out};
+    void* args[] = {&g, &numel, &spans, &span_elems, &scratch, &out};
     // The launch call's own return value: a sticky error left by an earlier, unrelated call is
     // neither reported under this kernel's name nor cleared here.
     e = cudaLaunchKernel((const void*)oe_static_sumsq, dim3(grid), dim3(kThreads), args, 0, s);

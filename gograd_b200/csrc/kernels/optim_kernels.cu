@@ -295,15 +295,21 @@ OE_ADAMW_VARIANT(oe_adamw_fused_u1, 1, 4)
 OE_ADAMW_VARIANT(oe_adamw_fused_u2, 2, 3)
 OE_ADAMW_VARIANT(oe_adamw_fused_u8, 8, 1)
 
-// Sharded step: same update, shadow stored into every rank's shadow buffer.
-extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
-oe_adamw_fused_peers(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks,
-                     uint32_t n_chunks, uint32_t chunk_elems, oe_adamw_args a, const __grid_constant__ oe_peer_set peers) {
-    if (a.grad_scale == 1.0f)
-        oe_adamw_body<4, true, false>(tensors, chunks, n_chunks, chunk_elems, a, peers);
-    else
-        oe_adamw_body<4, true, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);
-}
+// Sharded step: same update, shadow stored into every rank's shadow buffer. Built in the same
+// shapes as the single-GPU kernel (vectors in flight per thread x resident CTAs per SM); which one
+// keeps the NVLink stores flowing best depends on the number of ranks, so the shim exposes the choice.
+#define OE_ADAMW_PEERS_VARIANT(name, unroll, min_blocks)                                                    \
+    extern "C" __global__ void __launch_bounds__(OE_THREADS, min_blocks)                                    \
+    name(const oe_dev_tensor* __restrict__ tensors, const oe_dev_chunk* __restrict__ chunks, uint32_t n_chunks, \
+         uint32_t chunk_elems, oe_adamw_args a, const __grid_constant__ oe_peer_set peers) {                \
+        if (a.grad_scale == 1.0f)                                                                           \
+            oe_adamw_body<unroll, true, false>(tensors, chunks, n_chunks, chunk_elems, a, peers);           \
+        else                                                                                                \
+            oe_adamw_body<unroll, true, true>(tensors, chunks, n_chunks, chunk_elems, a, peers);            \
+    }
+OE_ADAMW_PEERS_VARIANT(oe_adamw_fused_peers, 4, 2)
+OE_ADAMW_PEERS_VARIANT(oe_adamw_fused_peers_u2, 2, 3)
+OE_ADAMW_PEERS_VARIANT(oe_adamw_fused_peers_u8, 8, 1)
 
 // Advances a device step counter on its own: used when a captured step has no work unit
 // at all (no parameter has a gradient), so no update launch could do it.

@@ -53,12 +53,14 @@ int fail_cu(const oe_driver* d, CUresult r, const char* op) {
 
 struct KernelSet {
     CUfunction adamw[4] = {nullptr, nullptr, nullptr, nullptr};  // "", u1, u2, u8
-    CUfunction adamw_peers = nullptr, sgd_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
+    CUfunction adamw_peers[3] = {nullptr, nullptr, nullptr};  // 4, 2, 8 vectors in flight per thread
+    CUfunction sgd_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
     CUfunction step_increment = nullptr, sgd = nullptr, sumsq = nullptr, norm_finalize = nullptr,
                scale = nullptr, zero = nullptr, cast = nullptr, rank_exchange = nullptr;
 };
 const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2", "oe_adamw_fused_u8"};
 const char* const kVariantKeys[4] = {"", "u1", "u2", "u8"};
+const char* const kAdamwPeerNames[3] = {"oe_adamw_fused_peers", "oe_adamw_fused_peers_u2", "oe_adamw_fused_peers_u8"};
 
 struct DeviceCtx {
     bool ready = false;
@@ -69,7 +71,7 @@ struct DeviceCtx {
     int sm_count = 0;
     KernelSet k;
     int occ_adamw[4] = {0, 0, 0, 0};
-    int occ_adamw_peers = 0, occ_sgd_peers = 0, occ_peer_reduce[3] = {0, 0, 0};
+    int occ_adamw_peers[3] = {0, 0, 0}, occ_sgd_peers = 0, occ_peer_reduce[3] = {0, 0, 0};
     int occ_sgd = 0, occ_sumsq = 0, occ_scale = 0, occ_zero = 0, occ_cast = 0;
 };
 
@@ -184,6 +186,7 @@ struct oe_plan {
     bool tables_valid = false;  // the device tables describe `descs`; false after a failed update
     // tuning knobs of the peer kernels (0 = the library's choice); none changes a result
     uint32_t tune_reduce_grid = 0, tune_update_grid = 0, tune_reduce_first = 0, tune_push_warp_rotate = 0;
+    uint32_t tune_peer_unroll = 0;  // shape of the sharded AdamW update: 0 = 4 vectors in flight, 1 = 2, 2 = 8
     uint32_t tune_step_grid = 0;  // single-GPU update / scale launches: 0 = persistent grid, 1 = one CTA per work unit
     uint64_t status_word = 0;   // device address of a sharded step's status word, 0 = none
 };
@@ -411,7 +414,9 @@ extern "C" int oe_init(int device) {
     } table[] = {
         {&dc->k.adamw[0], kAdamwNames[0], &dc->occ_adamw[0]}, {&dc->k.adamw[1], kAdamwNames[1], &dc->occ_adamw[1]},
         {&dc->k.adamw[2], kAdamwNames[2], &dc->occ_adamw[2]}, {&dc->k.adamw[3], kAdamwNames[3], &dc->occ_adamw[3]},
-        {&dc->k.adamw_peers, "oe_adamw_fused_peers", &dc->occ_adamw_peers},
+        {&dc->k.adamw_peers[0], kAdamwPeerNames[0], &dc->occ_adamw_peers[0]},
+        {&dc->k.adamw_peers[1], kAdamwPeerNames[1], &dc->occ_adamw_peers[1]},
+        {&dc->k.adamw_peers[2], kAdamwPeerNames[2], &dc->occ_adamw_peers[2]},
         {&dc->k.peer_reduce[0], "oe_peer_reduce_sumsq_n2", &dc->occ_peer_reduce[0]},
         {&dc->k.peer_reduce[1], "oe_peer_reduce_sumsq_n4", &dc->occ_peer_reduce[1]},
         {&dc->k.peer_reduce[2], "oe_peer_reduce_sumsq_n8", &dc->occ_peer_reduce[2]},
@@ -591,6 +596,11 @@ extern "C" int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value) {
         case OE_TUNE_PEER_REDUCE_FIRST: plan->tune_reduce_first = (uint32_t)value % OE_MAX_PEERS; return 0;
         case OE_TUNE_PEER_PUSH_WARP_ROTATE: plan->tune_push_warp_rotate = value ? 1u : 0u; return 0;
         case OE_TUNE_STEP_GRID: plan->tune_step_grid = value ? 1u : 0u; return 0;
+        case OE_TUNE_PEER_UPDATE_VECTORS:
+            if (value != 0 && value != 2 && value != 4 && value != 8)
+                return fail(OE_ERR_INVALID, "oe_plan_set_tuning: the sharded update is built for 2, 4 or 8 vectors in flight");
+            plan->tune_peer_unroll = value == 2 ? 1u : value == 8 ? 2u : 0u;
+            return 0;
         default: return fail(OE_ERR_INVALID, "oe_plan_set_tuning: unknown knob");
     }
 }
@@ -732,7 +742,8 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
         oe_peer_set ps = *peers;
         if (p->tune_push_warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
         void* peer_args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a, &ps};
-        return launch(d, p->dc->k.adamw_peers, "oe_adamw_fused_peers", peer_update_grid(p, p->dc->occ_adamw_peers),
+        const uint32_t shape = p->tune_peer_unroll;
+        return launch(d, p->dc->k.adamw_peers[shape], kAdamwPeerNames[shape], peer_update_grid(p, p->dc->occ_adamw_peers[shape]),
                       kThreads, stream, peer_args);
     }
     uint32_t grid = grid_for(p, p->dc->occ_adamw[p->variant]);

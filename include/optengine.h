@@ -305,6 +305,8 @@ OE_API int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const 
 #define OE_TUNE_PEER_UPDATE_GRID      2
 #define OE_TUNE_PEER_REDUCE_FIRST     3
 #define OE_TUNE_PEER_PUSH_WARP_ROTATE 4
+#define OE_TUNE_PEER_UPDATE_VECTORS   6 /* sharded AdamW update: 2, 4 (default) or 8 128-bit vectors in flight per thread and
+                                           stream (3, 2 or 1 resident CTAs per SM) */
 #define OE_TUNE_STEP_GRID             5 /* single-GPU update and in-place clip launches: 0 = a persistent grid strides
                                            over the work units, 1 = one CTA per work unit in table order */
 OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);
@@ -375,8 +377,9 @@ OE_API int oe_ipc_close(int device, uint64_t base);
  * norm_out, without allocating anything: no plan, no cuMemAlloc/cudaMalloc, no free. It exists
  * for hosts that cannot allocate once training runs — a process that gave the whole GPU to its
  * own arena, so that a later driver allocation fails, or a step loop that must not take the
- * device-wide synchronisation an allocation implies. The reduction's scratch (one float64
- * partial sum per 65536 elements plus an arrival counter, 257 KB) is a fixed __device__ array
+ * device-wide synchronisation an allocation implies. The reduction's scratch (32768 float64
+ * partial sums — one per 8192 elements, or per 65536 for buffers beyond 2^28 elements — plus an
+ * arrival counter, 257 KB) is a fixed __device__ array
  * inside the library image: every GPU that loads the library holds it until the process ends,
  * and numel above OE_STATIC_NORM_MAX_ELEMS is refused with OE_ERR_LIMIT.
  * All calls on a device share that array and it keeps the previous call's contents (the entry

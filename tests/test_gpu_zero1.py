@@ -82,7 +82,9 @@ def test_peer_kernels_with_emulated_ranks(world, tuned):
         records.append(torch.as_tensor(_RawCuda(plans[r].norm_address(), (1,), "<f8"), device="cuda"))
         if tuned:
             from gograd_b200.engine import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST,
-                                            OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID)
+                                            OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID,
+                                            OE_TUNE_PEER_UPDATE_VECTORS)
+            plans[r].set_tuning(OE_TUNE_PEER_UPDATE_VECTORS, 2 if world == 8 else 8)   # the other two built shapes
             plans[r].set_tuning(OE_TUNE_PEER_REDUCE_FIRST, (r + 1) % world)
             plans[r].set_tuning(OE_TUNE_PEER_REDUCE_GRID, 3)
             plans[r].set_tuning(OE_TUNE_PEER_UPDATE_GRID, 5)

@@ -50,6 +50,25 @@ def test_static_norm_matches_plan_norm_twice():
         exact = float(np.sqrt(np.sum(host[offset:].astype(np.float64) ** 2)))
         assert abs(got - exact) <= 1e-6 * exact
         plan.close()
+    # beyond 2^28 elements the array's slots each stand for 65536 elements instead of 8192: one buffer
+    # on that side of the switch, generated on the device, against the plan norm and torch's float64 sum
+    numel = (1 << 28) + 70_001
+    g = torch.empty(numel, dtype=torch.float32, device="cuda").normal_(0.0, 1e-3)
+    p = torch.zeros(8, device="cuda")
+    plan = eng.Plan([eng.TensorDesc(g, g)])
+    plan.grad_norm()
+    want, _ = plan.read_norm()
+    rc = lib().oe_grad_norm_static(0, g.data_ptr(), numel, out.data_ptr(), stream)
+    assert rc == 0, lib().oe_last_error()
+    torch.cuda.synchronize()
+    got = float(out.item())
+    exact = 0.0
+    for a in range(0, numel, 1 << 26):
+        exact += float(g[a:a + (1 << 26)].double().pow(2).sum().item())
+    exact = exact ** 0.5
+    assert abs(got - want) <= 1e-6 * want and abs(got - exact) <= 1e-6 * exact, (got, want, exact)
+    plan.close()
+    del g, p
     # an empty buffer has norm 0; the address is not read
     rc = lib().oe_grad_norm_static(0, 0, 0, out.data_ptr(), stream)
     assert rc == 0, lib().oe_last_error()
