@@ -596,7 +596,7 @@ def main():
     ap.add_argument("--reduce-first", default="rank0", choices=["rank0", "rotated"])
     ap.add_argument("--reduce-grid", type=int, default=0)
     ap.add_argument("--update-grid", type=int, default=0)
-    ap.add_argument("--push-warp-rotate", action="store_true")
+    ap.add_argument("--push-warp-rotate", default="", choices=["", "on", "off"])
     ap.add_argument("--sweep", action="store_true",
                     help="N > 1: time the two peer kernels over every launch-shape knob instead of the step")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")

@@ -217,8 +217,8 @@ def apply_tuning(opt, args):
         opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, (opt.rank + 1) % opt.world)
         chosen["reduce_first"] = "rank+1"
     if args.push_warp_rotate:
-        opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 1)
-        chosen["push_warp_rotate"] = True
+        opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, {"on": 1, "off": 2}[args.push_warp_rotate])
+        chosen["push_warp_rotate"] = args.push_warp_rotate
     return chosen
 
 
@@ -282,19 +282,25 @@ def launch_shape_sweep(opt, torch, dist, iters: int = 3):
             records.append({"kernel": "oe_adamw_fused_peers (multimem.st)", "grid": grid or "default", "ms": ms,
                             "received_GBs": push_bytes / ms / 1e6})
     else:
-        shapes = [(4, g, "ascending", w) for g in (0, 222, 148, 111, 74, 37) for w in (0, 1)] + \
-                 [(4, g, "rotated", w) for g in (0, 148) for w in (0, 1)] + \
-                 [(2, g, "ascending", w) for g in (0, 296, 148) for w in (0, 1)]
+        # grid 0 and warp rotation 0 are "the library's choice"; the sweep pins both (296 = the persistent grid)
+        shapes = [(4, g, "ascending", w) for g in (296, 222, 148, 111, 74, 37) for w in (2, 1)] + \
+                 [(4, g, "rotated", w) for g in (296, 148) for w in (2, 1)] + \
+                 [(2, g, "ascending", w) for g in (444, 296, 148) for w in (2, 1)]
         for vectors, grid, order, warp_rotate in shapes:
             opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_VECTORS, vectors)
             opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, grid)
             opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, warp_rotate)
             opt.push_order = order
             ms = timed(lambda: opt.plan.adamw_step_peers(hp, opt._push_deltas()))
-            records.append({"kernel": "oe_adamw_fused_peers", "vectors_in_flight": vectors, "grid": grid or "default",
-                            "store_order": order, "warp_rotate": bool(warp_rotate), "ms": ms,
+            records.append({"kernel": "oe_adamw_fused_peers", "vectors_in_flight": vectors, "grid": grid,
+                            "store_order": order, "warp_rotate": warp_rotate == 1, "ms": ms,
                             "pushed_GBs": push_bytes / ms / 1e6})
         opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_VECTORS, 0)
+        opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, 0)
+        opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 0)
+        ms = timed(lambda: opt.plan.adamw_step_peers(hp, opt._push_deltas()))
+        records.append({"kernel": "oe_adamw_fused_peers", "shape": "the library's choice for %d ranks" % world, "ms": ms,
+                        "pushed_GBs": push_bytes / ms / 1e6})
     opt.plan.set_tuning(E.OE_TUNE_PEER_UPDATE_GRID, 0)
     opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, 0)
     opt.push_order = keep_order

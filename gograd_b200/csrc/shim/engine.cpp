@@ -321,11 +321,29 @@ int upload_tables(const oe_driver* d, oe_plan* p, CUstream stream) {
 
 uint32_t grid_for(const oe_plan* p, int occupancy);
 
-// Grid of an update launch that also stores into the peers' buffers: the tuned size when one is set.
-uint32_t peer_update_grid(const oe_plan* p, int occupancy) {
-    uint32_t g = grid_for(p, occupancy);
-    if (p->tune_update_grid && p->tune_update_grid < g) g = p->tune_update_grid;
-    return g;
+// Launch shape of an update that also stores into the peers' buffers. The caller's knobs win; where
+// they are unset the library chooses by the number of ranks, from measurements on 8-GPU B200 boxes
+// (`bench.py --gpus N --sweep`): with four ranks the AdamW update pushes 676-695 GB/s from one CTA
+// per SM whose warps start their round of stores at different targets, against 621 GB/s from the
+// persistent default; with two or eight ranks no shape beat the default.
+struct PeerLaunchShape {
+    uint32_t grid;
+    bool warp_rotate;
+};
+PeerLaunchShape peer_update_shape(const oe_plan* p, int occupancy, uint32_t n_ranks, bool adamw) {
+    PeerLaunchShape shape;
+    shape.grid = grid_for(p, occupancy);
+    const bool four = adamw && n_ranks == 4 && p->tune_peer_unroll == 0;
+    if (p->tune_update_grid) {
+        if (p->tune_update_grid < shape.grid) shape.grid = p->tune_update_grid;
+    } else if (four && (uint32_t)p->dc->sm_count < shape.grid) {
+        shape.grid = (uint32_t)p->dc->sm_count;
+    }
+    if (p->tune_push_warp_rotate)
+        shape.warp_rotate = p->tune_push_warp_rotate == 1;
+    else
+        shape.warp_rotate = four && shape.grid == (uint32_t)p->dc->sm_count;
+    return shape;
 }
 
 uint32_t grid_for(const oe_plan* p, int occupancy) {
@@ -594,7 +612,10 @@ extern "C" int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value) {
         case OE_TUNE_PEER_REDUCE_GRID: plan->tune_reduce_grid = (uint32_t)value; return 0;
         case OE_TUNE_PEER_UPDATE_GRID: plan->tune_update_grid = (uint32_t)value; return 0;
         case OE_TUNE_PEER_REDUCE_FIRST: plan->tune_reduce_first = (uint32_t)value % OE_MAX_PEERS; return 0;
-        case OE_TUNE_PEER_PUSH_WARP_ROTATE: plan->tune_push_warp_rotate = value ? 1u : 0u; return 0;
+        case OE_TUNE_PEER_PUSH_WARP_ROTATE:
+            if (value > 2) return fail(OE_ERR_INVALID, "oe_plan_set_tuning: warp rotation is 0 (library's choice), 1 (on) or 2 (off)");
+            plan->tune_push_warp_rotate = (uint32_t)value;
+            return 0;
         case OE_TUNE_STEP_GRID: plan->tune_step_grid = value ? 1u : 0u; return 0;
         case OE_TUNE_PEER_UPDATE_VECTORS:
             if (value != 0 && value != 2 && value != 4 && value != 8)
@@ -740,11 +761,11 @@ int launch_adamw(const oe_driver* d, oe_plan* p, const oe_adamw_hparams* hp, CUs
     }
     if (peers) {
         oe_peer_set ps = *peers;
-        if (p->tune_push_warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
+        const uint32_t variant = p->tune_peer_unroll;
+        const PeerLaunchShape shape = peer_update_shape(p, p->dc->occ_adamw_peers[variant], ps.n, !(ps.mode & OE_PEER_MULTICAST));
+        if (shape.warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
         void* peer_args[] = {&p->d_tensors, &chunk_table, &n_chunks, &chunk_elems, &a, &ps};
-        const uint32_t shape = p->tune_peer_unroll;
-        return launch(d, p->dc->k.adamw_peers[shape], kAdamwPeerNames[shape], peer_update_grid(p, p->dc->occ_adamw_peers[shape]),
-                      kThreads, stream, peer_args);
+        return launch(d, p->dc->k.adamw_peers[variant], kAdamwPeerNames[variant], shape.grid, kThreads, stream, peer_args);
     }
     uint32_t grid = grid_for(p, p->dc->occ_adamw[p->variant]);
     if (grid > n_chunks || p->tune_step_grid == 1) grid = n_chunks;
@@ -826,10 +847,10 @@ int sgd_step(oe_plan* plan, const oe_sgd_hparams* hp, uint64_t stream, const oe_
     uint32_t n_chunks = (uint32_t)plan->n_chunks, chunk_elems = plan->chunk_elems;
     if (peers) {
         oe_peer_set ps = *peers;
-        if (plan->tune_push_warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
+        const PeerLaunchShape shape = peer_update_shape(plan, plan->dc->occ_sgd_peers, ps.n, false);  // not measured for SGD: knobs only
+        if (shape.warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
         void* peer_args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a, &ps};
-        return launch(d, plan->dc->k.sgd_peers, "oe_sgd_fused_peers", peer_update_grid(plan, plan->dc->occ_sgd_peers),
-                      kThreads, (CUstream)stream, peer_args);
+        return launch(d, plan->dc->k.sgd_peers, "oe_sgd_fused_peers", shape.grid, kThreads, (CUstream)stream, peer_args);
     }
     void* args[] = {&plan->d_tensors, &plan->d_chunks, &n_chunks, &chunk_elems, &a};
     return launch(d, plan->dc->k.sgd, "oe_sgd_fused", plan->tune_step_grid == 1 ? n_chunks : grid_for(plan, plan->dc->occ_sgd),

@@ -155,6 +155,26 @@ assert lib.oe_zero1_destroy(z) == 0
 out["zero1"] = {"sequence": seq, "second_create": twice, "bad_step": rc_bad_step, "bad_launched": bad_launched,
                 "bad_rank": rc_rank}
 
+# ---- 6b. launch shape of the sharded update: the library's choice by the number of ranks, and the knobs ----
+wide = desc(4096 * 400)
+arr7, _ = descs(wide)
+plan3 = C.c_void_p()
+assert lib.oe_plan_create(0, arr7, 1, 4096, C.byref(plan3)) == 0, err()
+shapes = {}
+for ranks in (2, 4, 8):
+    deltas = (C.c_int64 * ranks)(*([0] * ranks))
+    fake.fake_cuda_reset_launches()
+    assert lib.oe_adamw_step_peers(plan3, C.byref(hp), deltas, ranks, 0) == 0, err()
+    shapes[str(ranks)] = launches()[0][1]
+assert lib.oe_plan_set_tuning(plan3, 2, 100) == 0          # OE_TUNE_PEER_UPDATE_GRID
+deltas = (C.c_int64 * 4)(0, 0, 0, 0)
+fake.fake_cuda_reset_launches()
+assert lib.oe_adamw_step_peers(plan3, C.byref(hp), deltas, 4, 0) == 0, err()
+shapes["4 with the grid knob at 100"] = launches()[0][1]
+shapes["bad knob"] = lib.oe_plan_set_tuning(plan3, 4, 3)   # warp rotation takes 0, 1 or 2
+assert lib.oe_plan_destroy(plan3) == 0
+out["peer_shapes"] = shapes
+
 # ---- 7. shutdown refuses while plans live; everything the library allocated is returned -------------------
 rc_shutdown_live = lib.oe_shutdown()
 assert lib.oe_plan_destroy(plan) == 0 and lib.oe_plan_destroy(plan2) == 0

@@ -71,6 +71,12 @@ def test_sharded_step_is_five_launches_in_order(cases):
     assert z["second_create"] == -1 and z["bad_step"] == -1 and z["bad_launched"] == 0 and z["bad_rank"] == -1
 
 
+def test_sharded_update_launch_shape_follows_the_rank_count(cases):
+    """400 work units on a 148-SM device whose kernels fit two CTAs per SM: the persistent grid is 296 CTAs; with
+    four ranks the library launches one CTA per SM (the measured optimum there); an explicit knob wins."""
+    assert cases["peer_shapes"] == {"2": 296, "4": 148, "8": 296, "4 with the grid knob at 100": 100, "bad knob": -1}
+
+
 def test_teardown_and_architecture_check(cases):
     t = cases["teardown"]
     assert t["shutdown_with_live_plans"] == -1 and t["shutdown"] == 0 and t["leaked_allocations"] == 0
