@@ -255,14 +255,16 @@ def launch_shape_sweep(opt, torch, dist, iters: int = 3):
         opt.plan.peer_reduce_grads(opt.grad_bases, opt.lo, shard, own.data_ptr(), 1.0 / world, OE_PARTIAL_ONLY)
 
     for grid in (0, 148, 74):
-        for first in ("rank0", "rank+1"):
+        for first in ("rank0", "rank+1", "rank+1+warp"):
             opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_GRID, grid)
-            opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, (rank + 1) % world if first == "rank+1" else 0)
+            opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, (rank + 1) % world if first != "rank0" else 0)
+            opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_WARP_ROTATE, 1 if first == "rank+1+warp" else 0)
             ms = timed(pull)
             records.append({"kernel": "oe_peer_reduce_sumsq", "grid": grid or "default", "first_source": first, "ms": ms,
                             "pulled_GBs": pull_bytes / ms / 1e6})
     opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_GRID, 0)
     opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_FIRST, 0)
+    opt.plan.set_tuning(E.OE_TUNE_PEER_REDUCE_WARP_ROTATE, 0)
     # a norm for the updates that follow
     if opt.comm == "abi":
         opt.ctx.exchange(0)

@@ -37,7 +37,7 @@ class oe_zero1_desc(C.Structure):
 OE_ZERO1_SYNC_BYTES = 512
 OE_ZERO1_NO_ENTRY_EXCHANGE = 1
 OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_PUSH_WARP_ROTATE = 1, 2, 3, 4
-OE_TUNE_STEP_GRID, OE_TUNE_PEER_UPDATE_VECTORS = 5, 6
+OE_TUNE_STEP_GRID, OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_PEER_REDUCE_WARP_ROTATE = 5, 6, 7
 
 
 class EngineError(RuntimeError):

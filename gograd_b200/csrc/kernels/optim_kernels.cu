@@ -683,12 +683,10 @@ oe_cast_bf16(const float* __restrict__ src, uint16_t* __restrict__ dst, uint64_t
 // writes before it writes it, and no other rank reads that range of this buffer.
 // No flag or barrier is waited on here; ordering against the other ranks is the host's
 // job (stream-ordered collectives before and after).
+// The streaming part of the reduction for one order of issue: returns this thread's sum of squares.
 template <int NP, int U, int ROT>
-__device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
-                                                    float* __restrict__ out, oe_dev_norm* rec, double* partials) {
-    __shared__ double warp_sums[OE_THREADS / 32];
-    __shared__ uint32_t is_last;
-    if (pg.status != 0 && *(const volatile uint32_t*)pg.status != 0u) return;  // a failed exchange: skip
+__device__ __forceinline__ double oe_peer_reduce_stream(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
+                                                        float* __restrict__ out) {
     const uint32_t n = pg.n;
     const float scale = pg.scale;
     double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
@@ -711,9 +709,8 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
 #pragma unroll
             for (int u = 0; u < U; u++) {
                 const uint64_t i = i0 + (uint64_t)u * stride;
-                // Issue order: rank ROT first, then upwards and around (the host passes its own
-                // rank + 1, so the ranks of a step do not all address the same source first).
-                // The slot of a value is its rank, whatever the order of issue.
+                // Issue order: rank ROT first, then upwards and around. The slot of a value is its
+                // rank, whatever the order of issue, so the adds below stay in ascending rank order.
 #pragma unroll
                 for (int kk = 0; kk < NP; kk++) {
                     const int k = (kk + ROT) % NP;
@@ -757,7 +754,32 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
         double x = (double)s;
         a0 = fma(x, x, a0);
     }
-    double block = oe_block_sum((a0 + a1) + (a2 + a3), warp_sums);
+    return (a0 + a1) + (a2 + a3);
+}
+
+// One instance of the streaming part per first-issued rank. pg.rot is uniform over the grid (the host
+// passes the rank's own number + 1, so the ranks of a step do not all address the same source first);
+// with OE_F_WARP_ROTATE every warp of a CTA adds its own number, so the warps of a CTA do not either.
+// The choice is uniform over a warp, so the switch costs nothing; block-wide barriers come after it.
+template <int NP, int U>
+__device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
+                                                    float* __restrict__ out, oe_dev_norm* rec, double* partials) {
+    __shared__ double warp_sums[OE_THREADS / 32];
+    __shared__ uint32_t is_last;
+    if (pg.status != 0 && *(const volatile uint32_t*)pg.status != 0u) return;  // a failed exchange: skip
+    const uint32_t rot = (pg.rot + ((pg.flags & OE_F_WARP_ROTATE) ? (threadIdx.x >> 5) : 0u)) % NP;
+    double mine;
+    switch (rot) {
+        case 1: mine = oe_peer_reduce_stream<NP, U, 1 % NP>(pg, first, numel, out); break;
+        case 2: mine = oe_peer_reduce_stream<NP, U, 2 % NP>(pg, first, numel, out); break;
+        case 3: mine = oe_peer_reduce_stream<NP, U, 3 % NP>(pg, first, numel, out); break;
+        case 4: mine = oe_peer_reduce_stream<NP, U, 4 % NP>(pg, first, numel, out); break;
+        case 5: mine = oe_peer_reduce_stream<NP, U, 5 % NP>(pg, first, numel, out); break;
+        case 6: mine = oe_peer_reduce_stream<NP, U, 6 % NP>(pg, first, numel, out); break;
+        case 7: mine = oe_peer_reduce_stream<NP, U, 7 % NP>(pg, first, numel, out); break;
+        default: mine = oe_peer_reduce_stream<NP, U, 0>(pg, first, numel, out); break;
+    }
+    double block = oe_block_sum(mine, warp_sums);
     if (threadIdx.x == 0) {
         partials[blockIdx.x] = block;
         __threadfence();
@@ -779,26 +801,10 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
     }
 }
 
-// One body per first-issued rank; pg.rot is uniform over the grid, so the switch costs nothing.
-template <int NP, int U>
-__device__ __forceinline__ void oe_peer_reduce_dispatch(const oe_peer_grads& pg, uint64_t first, uint64_t numel,
-                                                        float* __restrict__ out, oe_dev_norm* rec, double* partials) {
-    switch (pg.rot % NP) {
-        case 1: oe_peer_reduce_body<NP, U, 1 % NP>(pg, first, numel, out, rec, partials); break;
-        case 2: oe_peer_reduce_body<NP, U, 2 % NP>(pg, first, numel, out, rec, partials); break;
-        case 3: oe_peer_reduce_body<NP, U, 3 % NP>(pg, first, numel, out, rec, partials); break;
-        case 4: oe_peer_reduce_body<NP, U, 4 % NP>(pg, first, numel, out, rec, partials); break;
-        case 5: oe_peer_reduce_body<NP, U, 5 % NP>(pg, first, numel, out, rec, partials); break;
-        case 6: oe_peer_reduce_body<NP, U, 6 % NP>(pg, first, numel, out, rec, partials); break;
-        case 7: oe_peer_reduce_body<NP, U, 7 % NP>(pg, first, numel, out, rec, partials); break;
-        default: oe_peer_reduce_body<NP, U, 0>(pg, first, numel, out, rec, partials); break;
-    }
-}
-
 #define OE_PEER_REDUCE_VARIANT(name, np, unroll)                                                               \
     extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)                                       \
     name(const __grid_constant__ oe_peer_grads pg, uint64_t first, uint64_t numel, float* out, oe_dev_norm* rec, double* partials) { \
-        oe_peer_reduce_dispatch<np, unroll>(pg, first, numel, out, rec, partials);                         \
+        oe_peer_reduce_body<np, unroll>(pg, first, numel, out, rec, partials);                             \
     }
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2, 8)
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4, 4)

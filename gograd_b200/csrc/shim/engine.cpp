@@ -186,6 +186,7 @@ struct oe_plan {
     bool tables_valid = false;  // the device tables describe `descs`; false after a failed update
     // tuning knobs of the peer kernels (0 = the library's choice); none changes a result
     uint32_t tune_reduce_grid = 0, tune_update_grid = 0, tune_reduce_first = 0, tune_push_warp_rotate = 0;
+    uint32_t tune_reduce_warp_rotate = 0;  // pull-reduce: every warp starts at another source
     uint32_t tune_peer_unroll = 0;  // shape of the sharded AdamW update: 0 = 4 vectors in flight, 1 = 2, 2 = 8
     uint32_t tune_step_grid = 0;  // single-GPU update / scale launches: 0 = persistent grid, 1 = one CTA per work unit
     uint64_t status_word = 0;   // device address of a sharded step's status word, 0 = none
@@ -617,6 +618,7 @@ extern "C" int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value) {
             plan->tune_push_warp_rotate = (uint32_t)value;
             return 0;
         case OE_TUNE_STEP_GRID: plan->tune_step_grid = value ? 1u : 0u; return 0;
+        case OE_TUNE_PEER_REDUCE_WARP_ROTATE: plan->tune_reduce_warp_rotate = value ? 1u : 0u; return 0;
         case OE_TUNE_PEER_UPDATE_VECTORS:
             if (value != 0 && value != 2 && value != 4 && value != 8)
                 return fail(OE_ERR_INVALID, "oe_plan_set_tuning: the sharded update is built for 2, 4 or 8 vectors in flight");
@@ -1130,6 +1132,7 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     pg.flags = flags;
     pg.scale = *scale;
     pg.rot = plan->tune_reduce_first;
+    if (plan->tune_reduce_warp_rotate) pg.flags |= OE_F_WARP_ROTATE;
     pg.status = plan->status_word;
     for (uint32_t k = 0; k < n_ranks; k++) {
         if (rank_bases[k] == 0 || (rank_bases[k] & 3u)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: bad gradient base of rank " + std::to_string(k));

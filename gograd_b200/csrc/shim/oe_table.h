@@ -126,5 +126,6 @@ typedef struct oe_sync_args {
 #define OE_F_MAXIMIZE     0x10u
 #define OE_F_PARTIAL_ONLY 0x20u /* norm pass: leave sumsq, do not finalise        */
 #define OE_F_ACCUMULATE   0x40u /* reduce pass: add to the record's sumsq instead of replacing it */
+#define OE_F_WARP_ROTATE  0x80u /* reduce pass (kernel side only): warp w issues its loads starting w sources later */
 
 #endif

@@ -7,6 +7,7 @@ from typing import Optional, Sequence
 
 from . import _lib
 from ._lib import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_REDUCE_GRID,
+                   OE_TUNE_PEER_REDUCE_WARP_ROTATE,
                    OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_STEP_GRID, OE_ZERO1_NO_ENTRY_EXCHANGE,
                    OE_ZERO1_SYNC_BYTES)
 from ._lib import (OE_ACCUMULATE, OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,

@@ -310,6 +310,8 @@ OE_API int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const 
 #define OE_TUNE_PEER_PUSH_WARP_ROTATE 4
 #define OE_TUNE_PEER_UPDATE_VECTORS   6 /* sharded AdamW update: 2, 4 (default) or 8 128-bit vectors in flight per thread and
                                            stream (3, 2 or 1 resident CTAs per SM) */
+#define OE_TUNE_PEER_REDUCE_WARP_ROTATE 7 /* pull-reduce: non-zero makes warp w of a CTA issue its loads starting w
+                                             sources after OE_TUNE_PEER_REDUCE_FIRST (the adds keep rank order) */
 #define OE_TUNE_STEP_GRID             5 /* single-GPU update and in-place clip launches: 0 = a persistent grid strides
                                            over the work units, 1 = one CTA per work unit in table order */
 OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);

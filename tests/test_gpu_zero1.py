@@ -83,7 +83,8 @@ def test_peer_kernels_with_emulated_ranks(world, tuned):
         if tuned:
             from gograd_b200.engine import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST,
                                             OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID,
-                                            OE_TUNE_PEER_UPDATE_VECTORS)
+                                            OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_PEER_REDUCE_WARP_ROTATE)
+            plans[r].set_tuning(OE_TUNE_PEER_REDUCE_WARP_ROTATE, 1)
             plans[r].set_tuning(OE_TUNE_PEER_UPDATE_VECTORS, 2 if world == 8 else 8)   # the other two built shapes
             plans[r].set_tuning(OE_TUNE_PEER_REDUCE_FIRST, (r + 1) % world)
             plans[r].set_tuning(OE_TUNE_PEER_REDUCE_GRID, 3)
