@@ -239,10 +239,12 @@ class Zero1Schedule:
 class Zero1AdamW(Zero1Schedule):
     """Sharded AdamW + clip + bf16 shadow over torch.distributed (NCCL), one rank per GPU.
 
-    group_of[i] = (lr_scale, weight_decay) of parameter i. `comm` selects the data path
-    ("peer" or "nccl"). Gradients are written by the caller into `self.grad_flat`
-    (or the per-tensor views `self.grads`); after `step()` every rank's `self.shadow_flat`
-    holds the bf16 weights of the whole model."""
+    group_of[i] = (lr_scale, weight_decay) of parameter i. `comm` selects the path ("peer", "abi"
+    or "nccl", see the module text); torch.distributed is used for set-up in every case (exchange
+    of the IPC handles, the layout check) and, on the abi path, for nothing after that. Gradients
+    are written by the caller into `self.grad_flat` (or the per-tensor views `self.grads`); after
+    `step()` every rank's `self.shadow_flat` holds the bf16 weights of the whole model.
+    `exchange_timeout_ms` bounds every wait of the abi path's exchange kernels (0 = 10 s)."""
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
                  beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
