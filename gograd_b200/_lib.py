@@ -59,6 +59,8 @@ PROTOTYPES = {
     "oe_init": (_i, [_i]),
     "oe_shutdown": (_i, []),
     "oe_device_sm_count": (_i, [_i]),
+    "oe_device_count": (_i, [C.POINTER(_i)]),
+    "oe_enable_peer_access": (_i, [_i, _i]),
     "oe_plan_create": (_i, [_i, C.POINTER(oe_tensor_desc), _u32, _u32, C.POINTER(_plan)]),
     "oe_plan_update": (_i, [_plan, C.POINTER(oe_tensor_desc), _u32, _u64]),
     "oe_plan_destroy": (_i, [_plan]),

@@ -481,6 +481,33 @@ extern "C" int oe_shutdown(void) {
     return 0;
 }
 
+extern "C" int oe_device_count(int* count_out) {
+    if (!count_out) return fail(OE_ERR_INVALID, "count_out is NULL");
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    OE_CU(d->cuDeviceGetCount_(count_out), "cuDeviceGetCount");
+    return 0;
+}
+
+extern "C" int oe_enable_peer_access(int device, int peer_device) {
+    int rc = 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    DeviceCtx* dc = device_or_fail(device, &rc);
+    if (!dc) return rc;
+    DeviceCtx* peer = device_or_fail(peer_device, &rc);
+    if (!peer) return rc;
+    if (device == peer_device) return 0;
+    int can = 0;
+    OE_CU(d->cuDeviceCanAccessPeer_(&can, dc->dev, peer->dev), "cuDeviceCanAccessPeer");
+    if (!can) return fail(OE_ERR_INVALID, "device " + std::to_string(device) + " cannot address the memory of device " + std::to_string(peer_device));
+    CtxGuard guard(d, dc->ctx);
+    CUresult r = d->cuCtxEnablePeerAccess_(peer->ctx, 0);
+    if (r != CUDA_SUCCESS && r != CUDA_ERROR_PEER_ACCESS_ALREADY_ENABLED) return fail_cu(d, r, "cuCtxEnablePeerAccess");
+    return 0;
+}
+
 extern "C" int oe_device_sm_count(int device) {
     int rc = 0;
     DeviceCtx* dc = device_or_fail(device, &rc);

@@ -139,6 +139,15 @@ OE_API int oe_init(int device);
  * must be destroyed first. */
 OE_API int oe_shutdown(void);
 
+/* Number of CUDA devices the driver offers. */
+OE_API int oe_device_count(int* count_out);
+
+/* Lets `device` address memory allocated on `peer_device` (both initialised): what a single process
+ * that drives several GPUs — one OS thread per device, as autograd/cuda_context.go:29-54 — needs
+ * before it hands one device's buffers to kernels of another. Processes that own one GPU each
+ * use oe_ipc_* instead, which brings the access with the mapping. Enabling twice is not an error. */
+OE_API int oe_enable_peer_access(int device, int peer_device);
+
 /* Number of SMs of an initialised device (148 on B200); < 0 on error. */
 OE_API int oe_device_sm_count(int device);
 
