@@ -898,3 +898,80 @@ def test_two_real_ranks_write_and_read_an_sgd_state_file(tmp_path):
         assert np.array_equal(flat[o:o + n], ref.buffers[i])
         want = ref.buffers[i].astype(np.float64)
         assert abs(d["entries"][f"buffer.{i}"]["sum"] - float(want.sum())) <= 1e-9 * float(np.abs(want).sum()) + 1e-30
+
+
+def _absent_rank_main(rank, world, port, queue):
+    """Two real ranks on the abi path. Both take step 1. Rank 1 then sits out step 2 (it stays alive,
+    its buffers stay mapped, nothing of it is in flight); rank 0's step 2 therefore meets an exchange
+    whose partner never announces itself."""
+    import time
+
+    import torch.distributed as dist
+    from gograd_b200.engine import EngineError
+    from gograd_b200.zero1 import Zero1AdamW
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank, comm="abi",
+                     exchange_timeout_ms=1000)
+    L = opt.layout
+    weights = torch.zeros(L.total)
+    for o, w in zip(L.offsets, _weights()):
+        weights[o:o + w.size] = torch.from_numpy(w)
+    opt.load_master(weights.cuda())
+
+    def load(step):
+        opt.grad_flat.zero_()
+        for view, g in zip(opt.grads, _grads(rank, step)):
+            view.copy_(torch.from_numpy(g))
+
+    load(1)
+    opt.step()
+    torch.cuda.synchronize()
+    assert opt.exchange_status() == 0
+    dist.barrier()
+    result = None
+    if rank == 0:
+        before = [t.clone() for t in (opt.master, opt.m, opt.v, opt.shadow_flat.view(torch.int16))]
+        load(2)
+        t0 = time.perf_counter()
+        opt.step()                       # enqueues five launches; the first one waits for rank 1, in vain
+        try:
+            opt.exchange_status()
+            result = "no error"
+        except EngineError as e:
+            waited = time.perf_counter() - t0
+            after = (opt.master, opt.m, opt.v, opt.shadow_flat.view(torch.int16))
+            same = all(bool(torch.equal(a, b)) for a, b in zip(before, after))
+            probe = float((opt.master * 0 + 1).sum().item())      # the device still answers
+            result = (e.code, "rank 1" in e.message, same, 0.9 <= waited < 20.0, probe == opt.master.numel())
+    dist.barrier()                       # rank 1 waited here, on the host side of its own stream
+    queue.put((rank, result))
+    opt.close()
+    dist.destroy_process_group()
+
+
+def test_a_rank_that_sits_out_a_step_costs_a_time_out_not_a_hang():
+    """The library-only sharded step on two real GPUs when one rank does not take part in a step: the
+    other rank's exchange kernel gives up after its one-second limit, the status names the absent rank,
+    the step's remaining launches do nothing (weights, moments and shadow unchanged), and both GPUs stay
+    usable — the next collective between the two processes completes."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    procs = [ctx.Process(target=_absent_rank_main, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(queue.get(timeout=300) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert results[1] is None
+    assert results[0] == (-6, True, True, True, True), results
