@@ -8,6 +8,12 @@
 // so what the engine needs per optimizer lives in side tables keyed by the optimizer's address
 // and is released from AdamW.Close / SGD.Close (autograd/optimizer_state.go:262-274,
 // autograd/sgd.go:247-257).
+//
+// cuda.CurrentDevice and cuda.CurrentStreamHandle are the per-thread device state of the cuda
+// package (cuda/cuda_windows.go:258, cuda_stub.go:34,74): on Linux they have to come from the
+// device binding that takes cuda_stub.go's place (go/cuda/optengine_linux.go supplies the memory and
+// copy calls such a binding wraps); with the stub still in place useEngine reports false and the
+// optimizers keep their CPU branches.
 package autograd
 
 import (

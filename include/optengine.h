@@ -338,7 +338,9 @@ OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);
  * Set-up: every rank allocates OE_ZERO1_SYNC_BYTES of zeroed device memory (256-byte aligned), exports it
  * with oe_ipc_export like its gradient and shadow buffers, and maps the others' (oe_ipc_import). All
  * ranks must call the step the same number of times. A rank's kernels wait on kernels of OTHER GPUs
- * only: never run two ranks of one step on the same GPU. */
+ * only: never run two ranks of one step on the same GPU. The step number each exchange waits for is a
+ * launch parameter that the host advances per call, so these calls cannot be recorded once in a stream
+ * capture and replayed. */
 #define OE_ZERO1_SYNC_BYTES 512
 #define OE_ZERO1_NO_ENTRY_EXCHANGE 0x1u /* the caller already knows that every rank's gradients are complete */
 
