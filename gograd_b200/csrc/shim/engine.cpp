@@ -591,6 +591,8 @@ extern "C" int oe_plan_update(oe_plan* plan, const oe_tensor_desc* tensors, uint
 
 extern "C" int oe_plan_destroy(oe_plan* plan) {
     if (!plan) return 0;
+    if (plan->status_word != 0)
+        return fail(OE_ERR_INVALID, "oe_plan_destroy: a sharded step (oe_zero1) is still bound to this plan; destroy it first");
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;

@@ -358,7 +358,8 @@ typedef struct oe_zero1_desc {
 typedef struct oe_zero1 oe_zero1;
 
 /* Binds a plan (whose tensors are the pieces of this rank's shard) to the ranks' buffers. Allocates
- * nothing on the device. */
+ * nothing on the device. One binding per plan; destroy it before the plan (oe_plan_destroy refuses a
+ * plan that is still bound). */
 OE_API int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero1** out);
 OE_API int oe_zero1_destroy(oe_zero1* z);
 

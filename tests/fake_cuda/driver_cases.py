@@ -151,8 +151,9 @@ bad_launched = len(launches())
 d_bad = _lib.oe_zero1_desc.from_buffer_copy(d)
 d_bad.rank = 2
 rc_rank = lib.oe_zero1_create(plan2, C.byref(d_bad), C.byref(C.c_void_p()))
+rc_plan_first = lib.oe_plan_destroy(plan2)                  # refused while the sharded step is bound to it
 assert lib.oe_zero1_destroy(z) == 0
-out["zero1"] = {"sequence": seq, "second_create": twice, "bad_step": rc_bad_step, "bad_launched": bad_launched,
+out["zero1"] = {"plan_destroyed_first": rc_plan_first, "sequence": seq, "second_create": twice, "bad_step": rc_bad_step, "bad_launched": bad_launched,
                 "bad_rank": rc_rank}
 
 # ---- 6b. launch shape of the sharded update: the library's choice by the number of ranks, and the knobs ----

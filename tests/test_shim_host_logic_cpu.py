@@ -69,6 +69,7 @@ def test_sharded_step_is_five_launches_in_order(cases):
     assert z["sequence"] == ["oe_rank_exchange", "oe_peer_reduce_sumsq_n2", "oe_rank_exchange", "oe_adamw_fused_peers",
                              "oe_rank_exchange"]
     assert z["second_create"] == -1 and z["bad_step"] == -1 and z["bad_launched"] == 0 and z["bad_rank"] == -1
+    assert z["plan_destroyed_first"] == -1
 
 
 def test_sharded_update_launch_shape_follows_the_rank_count(cases):
