@@ -4,7 +4,7 @@
 // variable OE_CUDA_DRIVER_LIBRARY) its host logic can be exercised on the CPU: "device memory"
 // is host memory, copies are memcpy, kernels are not executed but every launch is recorded
 // (kernel name, grid, block), and any driver entry point can be told to fail on its n-th call.
-// Nothing here computes an optimizer step: parity is never judged through this library.
+// Nothing here computes an optimizer step: parity is never checked through this library.
 #include <cuda.h>
 #include <stdlib.h>
 #include <string.h>
