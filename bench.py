@@ -55,7 +55,7 @@ def measured_peak():
 # (oe_adamw_fused_gpt110m_ncu_full.md, oe_grad_sumsq_gpt110m_ncu_full.md): dram__bytes_read.sum +
 # dram__bytes_write.sum over 109,630,464 parameters. Traffic grows in proportion to the parameter
 # count, so the figure is scaled to the launch that is timed.
-NCU_TRAFFIC_BYTES_PER_PARAM = {"oe_adamw_fused_bytes_per_param": 29.47, "oe_grad_sumsq_bytes_per_param": 4.03}
+NCU_TRAFFIC_BYTES_PER_PARAM = {"oe_adamw_fused_bytes_per_param": 29.50, "oe_grad_sumsq_bytes_per_param": 4.03}
 
 
 def ncu_traffic_per_param():
