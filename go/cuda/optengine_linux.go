@@ -13,6 +13,7 @@ package cuda
 
 import (
 	"fmt"
+	"runtime"
 	"sync"
 	"unsafe"
 
@@ -179,8 +180,10 @@ func NewPlan(device int, tensors []TensorDesc) (*Plan, error) {
 		return nil, err
 	}
 	p := &Plan{device: device}
-	if err := oeCall("oe_plan_create", uintptr(device), descPointer(tensors), uintptr(len(tensors)), 0,
-		uintptr(unsafe.Pointer(&p.handle))); err != nil {
+	err := oeCall("oe_plan_create", uintptr(device), descPointer(tensors), uintptr(len(tensors)), 0,
+		uintptr(unsafe.Pointer(&p.handle)))
+	runtime.KeepAlive(tensors) // descPointer handed out a bare address: the slice must outlive the call
+	if err != nil {
 		return nil, err
 	}
 	return p, nil
@@ -190,7 +193,9 @@ func NewPlan(device int, tensors []TensorDesc) (*Plan, error) {
 // addresses and sizes (the pool may return a freed block to a parameter of another size,
 // autograd/cuda_clip.go:80-93) and uploads, on stream, only when something changed.
 func (p *Plan) Update(tensors []TensorDesc, stream uintptr) error {
-	return oeCall("oe_plan_update", p.handle, descPointer(tensors), uintptr(len(tensors)), stream)
+	err := oeCall("oe_plan_update", p.handle, descPointer(tensors), uintptr(len(tensors)), stream)
+	runtime.KeepAlive(tensors)
+	return err
 }
 
 // SetGradScale makes norm and update read every gradient element as float32(g*scale).
