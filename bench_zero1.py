@@ -55,13 +55,14 @@ def run(args) -> int:
     opt.master.normal_(0.0, 0.02, generator=gen)
     stream = torch.cuda.current_stream()
 
+    link = measure_link_peaks(opt, torch, dist) if comm != "nccl" else None
     parity = None if args.no_parity_check else parity_check(opt, torch, dist)
     if args.sweep:
         records = launch_shape_sweep(opt, torch, dist)
         if rank == 0:
             sys.stdout.flush()
             os.dup2(real_stdout, 1)
-            print(json.dumps({"launch_shape_sweep": records, "n_gpus": world, "workload": key, "comm": comm,
+            print(json.dumps({"launch_shape_sweep": records, "link_peaks": link, "n_gpus": world, "workload": key, "comm": comm,
                               "multicast_shadow_stores": bool(args.multicast), "parity_check": parity}), flush=True)
             os.dup2(2, 1)
         opt.close()
@@ -149,6 +150,9 @@ def run(args) -> int:
         pull_remote = 4.0 * shard * (world - 1)          # bytes this rank pulls over NVLink in the reduce kernel
         push_remote = 2.0 * shard * (world - 1)          # bytes it stores into peers' shadows in the update kernel
         k1, k2 = phases.get("reduce_ms"), phases.get("update_ms")
+        # the link rates this box gave the two access patterns a moment ago, with nothing else riding on them
+        read_peak = link["reads_GBs"] if link else None
+        store_peak = link["stores_GBs"] if link else None
         nvlink_ms = (pull_remote + push_remote) / (NVLINK_PEER_GBS * 1e9) * 1e3
         hbm_ms = ((4.0 * world + 4.0) + 30.0) * shard / (peak * 1e9) * 1e3
         # The update cannot start before the global norm is known, i.e. before every rank's reduction is
@@ -158,10 +162,14 @@ def run(args) -> int:
         update_floor = max(30.0 * shard / (peak * 1e9), push_remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
         roofline = {
             "bound": "nvlink", "kernel": "oe_peer_reduce_sumsq (pull reduce-scatter + norm)" if comm != "nccl" else "ncclReduceScatter",
-            "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": NVLINK_PEER_GBS, "unit": "GB/s",
-            "frac": (pull_remote / (k1 * 1e-3) / 1e9 / NVLINK_PEER_GBS) if k1 else None,
-            "peak_kind": "builder constant: 770 GB/s, a one-at-a-time copy-engine peer copy measured on this pool "
+            "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": read_peak or NVLINK_PEER_GBS, "unit": "GB/s",
+            "frac": (pull_remote / (k1 * 1e-3) / 1e9 / (read_peak or NVLINK_PEER_GBS)) if k1 else None,
+            "peak_kind": ("measured in this run: every rank reading its shard of every peer's gradient buffer at the same time, "
+                          "nothing stored (oe_link_probe_reads)") if read_peak else
+                         "builder constant: 770 GB/s, a one-at-a-time copy-engine peer copy measured on this pool "
                          "(not measured in this run)",
+            "frac_of_770_builder_constant": (pull_remote / (k1 * 1e-3) / 1e9 / NVLINK_PEER_GBS) if k1 else None,
+            "link_peaks": link,
             "frac_of_nominal_900GBs": (pull_remote / (k1 * 1e-3) / 1e9 / NVLINK_NOMINAL_GBS) if k1 else None,
             "traffic": None,
             "traffic_source": "none: the bytes that cross NVLink are not DRAM traffic of this GPU; ncu is not run on "
@@ -170,11 +178,17 @@ def run(args) -> int:
             "update_kernel": {"kernel": "oe_adamw_fused_peers" if comm != "nccl" else "oe_adamw_fused + ncclAllGather",
                               "kernel_ms": k2, "remote_store_bytes": push_remote,
                               "nvlink_achieved": push_remote / (k2 * 1e-3) / 1e9 if k2 else None,
+                              "nvlink_peak_measured": store_peak,
+                              "nvlink_frac_of_measured": push_remote / (k2 * 1e-3) / 1e9 / store_peak if (k2 and store_peak) else None,
                               "nvlink_frac_of_770_builder_constant": push_remote / (k2 * 1e-3) / 1e9 / NVLINK_PEER_GBS if k2 else None,
                               "nvlink_frac_of_nominal_900GBs": push_remote / (k2 * 1e-3) / 1e9 / NVLINK_NOMINAL_GBS if k2 else None,
                               "hbm_bytes": 30.0 * shard,
                               "hbm_achieved": 30.0 * shard / (k2 * 1e-3) / 1e9 if k2 else None, "hbm_peak": peak},
-            "step_floor_ms": {"nvlink": nvlink_ms, "hbm": hbm_ms, "reduce_then_update": reduce_floor + update_floor},
+            "step_floor_ms": {"nvlink": nvlink_ms, "hbm": hbm_ms, "reduce_then_update": reduce_floor + update_floor,
+                              "reduce_then_update_at_measured_link_rates":
+                                  (max(pull_remote / (read_peak * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) +
+                                   max(30.0 * shard / (peak * 1e9), push_remote / (store_peak * 1e9))) * 1e3
+                                  if (read_peak and store_peak) else None},
             "step_frac_of_floor": max(nvlink_ms, hbm_ms) / ms_per_step,
             "step_frac_of_serial_floor": (reduce_floor + update_floor) / ms_per_step,
             "phases_ms": phases,
@@ -220,6 +234,40 @@ def apply_tuning(opt, args):
         opt.plan.set_tuning(E.OE_TUNE_PEER_PUSH_WARP_ROTATE, {"on": 1, "off": 2}[args.push_warp_rotate])
         chosen["push_warp_rotate"] = args.push_warp_rotate
     return chosen
+
+
+def measure_link_peaks(opt, torch, dist, iters: int = 3):
+    """What the NVLink fabric of this box gives the step's two access patterns when nothing else rides on them,
+    all ranks at once (a barrier before each launch, max over ranks): every load of the pull-reduce with no store,
+    and bf16 stores to every peer's shadow in the update's launch shape with no update around them. The store
+    probe writes zeros over ranges the next step rewrites, so it runs before anything is checked or timed."""
+    world = opt.world
+    if world < 2:
+        return None
+    dev = opt.master.device
+    stream = torch.cuda.current_stream()
+    shard = opt.layout.shard_len
+
+    def timed(fn):
+        vals = []
+        for _ in range(iters + 1):          # the first launch warms up
+            dist.barrier()
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            fn()
+            b.record(stream)
+            torch.cuda.synchronize()
+            vals.append(a.elapsed_time(b))
+        t = torch.tensor([statistics.median(vals[1:])], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    r = timed(lambda: opt.plan.link_probe_reads(opt.grad_bases, opt.lo, shard))
+    w = timed(lambda: opt.plan.link_probe_stores(opt.shadow_flat.data_ptr() + 2 * opt.lo, opt.shadow_deltas, shard))
+    return {"reads_GBs": 4.0 * shard * (world - 1) / r / 1e6, "reads_ms": r,
+            "stores_GBs": 2.0 * shard * (world - 1) / w / 1e6, "stores_ms": w,
+            "how": "oe_link_probe_reads / oe_link_probe_stores on every rank at once, median of %d, max over ranks" % iters}
 
 
 def launch_shape_sweep(opt, torch, dist, iters: int = 3):

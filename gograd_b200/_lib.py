@@ -87,6 +87,8 @@ PROTOTYPES = {
     "oe_sgd_step_multicast": (_i, [_plan, C.POINTER(oe_sgd_hparams), C.POINTER(C.c_int64), _u32,
                                    C.POINTER(C.c_int64), _u64]),
     "oe_plan_set_tuning": (_i, [_plan, _i, _u64]),
+    "oe_link_probe_reads": (_i, [_plan, C.POINTER(_u64), _u32, _u64, _u64, _u64]),
+    "oe_link_probe_stores": (_i, [_plan, _u64, C.POINTER(C.c_int64), _u32, _u64, _u64]),
     "oe_zero1_create": (_i, [_plan, C.POINTER(oe_zero1_desc), C.POINTER(_vp)]),
     "oe_zero1_destroy": (_i, [_vp]),
     "oe_zero1_adamw_step": (_i, [_vp, C.POINTER(oe_adamw_hparams), _u64]),

@@ -735,7 +735,7 @@ __device__ __forceinline__ double oe_peer_reduce_stream(const oe_peer_grads& pg,
                     s.y = __fmul_rn(s.y, scale);
                     s.z = __fmul_rn(s.z, scale);
                     s.w = __fmul_rn(s.w, scale);
-                    __stcs(o4 + i, s);
+                    if (!(pg.flags & OE_F_NO_STORE)) __stcs(o4 + i, s);
                     double x = (double)s.x, y = (double)s.y, z = (double)s.z, w = (double)s.w;
                     a0 = fma(x, x, a0);
                     a1 = fma(y, y, a1);
@@ -750,7 +750,7 @@ __device__ __forceinline__ double oe_peer_reduce_stream(const oe_peer_grads& pg,
         float s = __ldcg((const float*)pg.base[0] + first + i);
         for (uint32_t k = 1; k < n; k++) s = __fadd_rn(s, __ldcg((const float*)pg.base[k] + first + i));
         s = __fmul_rn(s, scale);
-        out[i] = s;
+        if (!(pg.flags & OE_F_NO_STORE)) out[i] = s;
         double x = (double)s;
         a0 = fma(x, x, a0);
     }
@@ -809,6 +809,29 @@ __device__ __forceinline__ void oe_peer_reduce_body(const oe_peer_grads& pg, uin
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n2, 2, 8)
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n4, 4, 4)
 OE_PEER_REDUCE_VARIANT(oe_peer_reduce_sumsq_n8, 8, 2)
+
+// Link-rate probe for the stores of the sharded update: bf16 zeros over [0, n_vec) 8-byte vectors of every
+// target in peers.delta, issued like the update kernel issues its shadow stores (four vectors per thread,
+// one round of targets per vector, optional warp rotation) with no other memory traffic beside them.
+extern "C" __global__ void __launch_bounds__(OE_THREADS, 2)
+oe_probe_peer_stores(uint16_t* sh, uint64_t n_vec, const __grid_constant__ oe_peer_set peers) {
+    const uint2 zero = make_uint2(0u, 0u);
+    const uint64_t tile = (uint64_t)OE_THREADS * OE_UNROLL;
+    for (uint64_t t0 = (uint64_t)blockIdx.x * tile; t0 < n_vec; t0 += (uint64_t)gridDim.x * tile) {
+#pragma unroll
+        for (int u = 0; u < OE_UNROLL; u++) {
+            const uint64_t i = t0 + (uint64_t)u * OE_THREADS + threadIdx.x;
+            if (i < n_vec) {
+                uint32_t k = (peers.mode & OE_PEER_WARP_ROTATE) ? (threadIdx.x >> 5) % peers.n : 0u;
+                for (uint32_t j = 0; j < peers.n; j++) {
+                    __stcs((uint2*)((char*)sh + peers.delta[k]) + i, zero);
+                    if (++k == peers.n) k = 0;
+                }
+            }
+        }
+    }
+    __threadfence_system();
+}
 
 // ---------------------------------------------------------------------------------
 // sharded step: exchange between the ranks without a collective library

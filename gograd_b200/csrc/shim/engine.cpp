@@ -56,7 +56,7 @@ struct KernelSet {
     CUfunction adamw_peers[3] = {nullptr, nullptr, nullptr};  // 4, 2, 8 vectors in flight per thread
     CUfunction sgd_peers = nullptr, peer_reduce[3] = {nullptr, nullptr, nullptr};  // n <= 2, 4, 8
     CUfunction step_increment = nullptr, sgd = nullptr, sumsq = nullptr, norm_finalize = nullptr,
-               scale = nullptr, zero = nullptr, cast = nullptr, rank_exchange = nullptr;
+               scale = nullptr, zero = nullptr, cast = nullptr, rank_exchange = nullptr, probe_stores = nullptr;
 };
 const char* const kAdamwNames[4] = {"oe_adamw_fused", "oe_adamw_fused_u1", "oe_adamw_fused_u2", "oe_adamw_fused_u8"};
 const char* const kVariantKeys[4] = {"", "u1", "u2", "u8"};
@@ -445,6 +445,7 @@ extern "C" int oe_init(int device) {
         {&dc->k.norm_finalize, "oe_norm_finalize", nullptr},   {&dc->k.scale, "oe_scale_grads", &dc->occ_scale},
         {&dc->k.zero, "oe_zero_grads", &dc->occ_zero},         {&dc->k.cast, "oe_cast_bf16", &dc->occ_cast},
         {&dc->k.rank_exchange, "oe_rank_exchange", nullptr},
+        {&dc->k.probe_stores, "oe_probe_peer_stores", nullptr},
     };
     for (auto& e : table) {
         r = d->cuModuleGetFunction_(e.f, dc->module, e.name);
@@ -1144,11 +1145,23 @@ extern "C" int oe_event_elapsed_ms(int device, uint64_t start, uint64_t stop, fl
 // -------------------------------------------------------------------------------------
 // sharded step (ZeRO-1 style): peer-memory kernels and the IPC plumbing they need
 // -------------------------------------------------------------------------------------
+namespace {
+int peer_reduce(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem, uint64_t numel, uint64_t out,
+                const float* scale, uint32_t flags, uint64_t stream);
+}
+
 extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
                                     uint64_t numel, uint64_t out, const float* scale, uint32_t flags, uint64_t stream) {
+    if (flags & ~(OE_PARTIAL_ONLY | OE_ACCUMULATE)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
+    return peer_reduce(plan, rank_bases, n_ranks, first_elem, numel, out, scale, flags, stream);
+}
+
+namespace {
+// flags may carry the kernel-side bits of oe_table.h beside the public ones
+int peer_reduce(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem, uint64_t numel, uint64_t out,
+                const float* scale, uint32_t flags, uint64_t stream) {
     if (!plan || !rank_bases || !scale) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: NULL argument");
     if (n_ranks < 1 || n_ranks > OE_MAX_PEERS) return fail(OE_ERR_LIMIT, "oe_peer_reduce_grads: 1 to 8 ranks are supported");
-    if (flags & ~(OE_PARTIAL_ONLY | OE_ACCUMULATE)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: unknown flag");
     if (!isfinite(*scale)) return fail(OE_ERR_INVALID, "oe_peer_reduce_grads: scale is not finite");
     // This kernel writes the scaled sum in place and takes its own factor; a plan-level scale
     // would be applied again by the update that follows.
@@ -1184,6 +1197,41 @@ extern "C" int oe_peer_reduce_grads(oe_plan* plan, const uint64_t* rank_bases, u
     if (grid == 0) grid = 1;
     void* args[] = {&pg, &first_elem, &numel, &out, &plan->d_norm, &plan->d_partials};
     return launch(d, dc->k.peer_reduce[which], names[which], (uint32_t)grid, kThreads, (CUstream)stream, args);
+}
+}  // namespace
+
+extern "C" int oe_link_probe_reads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
+                                   uint64_t numel, uint64_t stream) {
+    if (!plan || !rank_bases) return fail(OE_ERR_INVALID, "oe_link_probe_reads: NULL argument");
+    // the pull-reduce with its stores switched off: every load of the real launch, nothing written but the plan's norm record
+    const float one = 1.0f;
+    uint64_t anywhere = rank_bases[0] + 4ull * first_elem;
+    return peer_reduce(plan, rank_bases, n_ranks, first_elem, numel, anywhere, &one, OE_PARTIAL_ONLY | OE_F_NO_STORE, stream);
+}
+
+extern "C" int oe_link_probe_stores(oe_plan* plan, uint64_t shadow_shard, const int64_t* shadow_deltas, uint32_t n_ranks,
+                                    uint64_t numel, uint64_t stream) {
+    if (!plan || !shadow_deltas) return fail(OE_ERR_INVALID, "oe_link_probe_stores: NULL argument");
+    if (shadow_shard == 0 || (shadow_shard & 7u) || (numel & 3u))
+        return fail(OE_ERR_INVALID, "oe_link_probe_stores: the range must start on an 8-byte boundary and hold a multiple of 4 elements");
+    oe_peer_set all;
+    int rc = peer_set_from(shadow_deltas, n_ranks, "oe_link_probe_stores", &all);
+    if (rc) return rc;
+    oe_peer_set ps;   // every target but the caller's own buffer
+    memset(&ps, 0, sizeof(ps));
+    for (uint32_t k = 0; k < all.n; k++)
+        if (all.delta[k] != 0) ps.delta[ps.n++] = all.delta[k];
+    if (ps.n == 0 || numel == 0) return 0;
+    const oe_driver* d = driver_or_fail(&rc);
+    if (!d) return rc;
+    CtxGuard guard(d, plan->dc->ctx);
+    const PeerLaunchShape shape = peer_update_shape(plan, plan->dc->occ_adamw_peers[0], n_ranks, true);
+    if (shape.warp_rotate) ps.mode |= OE_PEER_WARP_ROTATE;
+    uint64_t n_vec = numel / 4;
+    uint64_t tiles = (n_vec + 1023) / 1024;
+    uint32_t grid = (uint32_t)(tiles < shape.grid ? tiles : shape.grid);
+    void* args[] = {&shadow_shard, &n_vec, &ps};
+    return launch(d, plan->dc->k.probe_stores, "oe_probe_peer_stores", grid ? grid : 1, kThreads, (CUstream)stream, args);
 }
 
 extern "C" int oe_adamw_step_peers(oe_plan* plan, const oe_adamw_hparams* hp, const int64_t* shadow_deltas,

@@ -127,5 +127,6 @@ typedef struct oe_sync_args {
 #define OE_F_PARTIAL_ONLY 0x20u /* norm pass: leave sumsq, do not finalise        */
 #define OE_F_ACCUMULATE   0x40u /* reduce pass: add to the record's sumsq instead of replacing it */
 #define OE_F_WARP_ROTATE  0x80u /* reduce pass (kernel side only): warp w issues its loads starting w sources later */
+#define OE_F_NO_STORE     0x100u /* reduce pass (kernel side only): read and add, write no element (link-rate probe) */
 
 #endif

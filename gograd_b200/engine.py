@@ -197,6 +197,16 @@ class Plan:
         check(lib().oe_sgd_step_multicast(self._h, C.byref(c), deltas, len(shadow_deltas),
                                           C.byref(C.c_int64(mc_delta)), _stream(stream)))
 
+    def link_probe_reads(self, rank_bases: Sequence[int], first_elem: int, numel: int, stream=None) -> None:
+        """Every load of the pull-reduce over the range, no element stored (oe_link_probe_reads)."""
+        bases = (C.c_uint64 * len(rank_bases))(*rank_bases)
+        check(lib().oe_link_probe_reads(self._h, bases, len(rank_bases), first_elem, numel, _stream(stream)))
+
+    def link_probe_stores(self, shadow_shard: int, shadow_deltas: Sequence[int], numel: int, stream=None) -> None:
+        """bf16 zeros over the range of every other rank's shadow buffer (oe_link_probe_stores)."""
+        deltas = (C.c_int64 * len(shadow_deltas))(*shadow_deltas)
+        check(lib().oe_link_probe_stores(self._h, shadow_shard, deltas, len(shadow_deltas), numel, _stream(stream)))
+
     def set_tuning(self, what: int, value: int) -> None:
         """A launch-shape knob of the peer kernels (oe_plan_set_tuning); results never change."""
         check(lib().oe_plan_set_tuning(self._h, what, value))

@@ -325,6 +325,17 @@ OE_API int oe_sgd_step_multicast(oe_plan* plan, const oe_sgd_hparams* hp, const 
                                            over the work units, 1 = one CTA per work unit in table order */
 OE_API int oe_plan_set_tuning(oe_plan* plan, int what, uint64_t value);
 
+/* Link-rate probes: what the NVLink fabric gives the two access patterns of the sharded step when nothing else
+ * rides on them, to rate the step's kernels against (run them on every rank at the same time, as the step does).
+ * oe_link_probe_reads issues every load of oe_peer_reduce_grads over the same range and stores no element (the
+ * plan's norm record is overwritten). oe_link_probe_stores writes bf16 ZEROS over [shadow_shard, shadow_shard +
+ * 2*numel) of every OTHER rank's shadow buffer, in the launch shape the update would use: call it only where a
+ * following step rewrites that range. */
+OE_API int oe_link_probe_reads(oe_plan* plan, const uint64_t* rank_bases, uint32_t n_ranks, uint64_t first_elem,
+                               uint64_t numel, uint64_t stream);
+OE_API int oe_link_probe_stores(oe_plan* plan, uint64_t shadow_shard, const int64_t* shadow_deltas, uint32_t n_ranks,
+                                uint64_t numel, uint64_t stream);
+
 /* ---- sharded step driven through this interface alone -------------------------------------------- */
 /* For a host with no collective library (the reference has none: one OS thread per device,
  * autograd/cuda_context.go:29-54). The three points at which the ranks of a step must meet are small

@@ -975,3 +975,29 @@ def test_a_rank_that_sits_out_a_step_costs_a_time_out_not_a_hang():
         assert p.exitcode == 0
     assert results[1] is None
     assert results[0] == (-6, True, True, True, True), results
+
+
+def test_link_probes_touch_only_what_they_say():
+    """The two link-rate probes on one GPU with two emulated ranks: the read probe stores no element (the
+    output range keeps its canary) and leaves the sum of squares of the mean in the norm record; the store
+    probe writes bf16 zeros over the given range of the OTHER rank's shadow only."""
+    import gograd_b200 as eng
+    eng.init(0)
+    n = 3 * 4096
+    rng = np.random.default_rng(11)
+    g = [torch.from_numpy(rng.normal(0, 1e-3, 2 * n).astype(np.float32)).cuda() for _ in range(2)]
+    keep = [x.clone() for x in g]
+    p = torch.zeros(8, device="cuda")
+    plan = eng.Plan([eng.TensorDesc(p, p)])
+    plan.link_probe_reads([x.data_ptr() for x in g], n, n)
+    _, sumsq = plan.read_norm()
+    want = float((g[0][n:] + g[1][n:]).double().pow(2).sum().item())
+    assert abs(sumsq - want) <= 1e-12 * want
+    assert all(bool(torch.equal(a, b)) for a, b in zip(g, keep))
+    shadows = [torch.full((2 * n,), -1, dtype=torch.int16, device="cuda") for _ in range(2)]
+    deltas = [0, shadows[1].data_ptr() - shadows[0].data_ptr()]
+    plan.link_probe_stores(shadows[0].data_ptr() + 2 * n, deltas, n)
+    torch.cuda.synchronize()
+    assert bool((shadows[0] == -1).all()), "the caller's own buffer is not a target"
+    assert bool((shadows[1][:n] == -1).all()) and bool((shadows[1][n:] == 0).all())
+    plan.close()
