@@ -597,6 +597,10 @@ def main():
     ap.add_argument("--reduce-grid", type=int, default=0)
     ap.add_argument("--update-grid", type=int, default=0)
     ap.add_argument("--push-warp-rotate", default="", choices=["", "on", "off"])
+    ap.add_argument("--ce-pull-sources", type=int, default=None,
+                    help="N > 1, --comm abi: peers whose gradient range a copy stages before the pull kernel (default: the library's choice; 0 = none)")
+    ap.add_argument("--ce-push-targets", type=int, default=None,
+                    help="N > 1, --comm abi: ranks served by a shadow copy after the update kernel (default: the library's choice; 0 = none)")
     ap.add_argument("--sweep", action="store_true",
                     help="N > 1: time the two peer kernels over every launch-shape knob instead of the step")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")

@@ -46,7 +46,10 @@ def run(args) -> int:
     comm = getattr(args, "comm", "peer") or "peer"
     opt = Zero1AdamW([s.numel for s in ps.params], group_of, hp["lr"], hp["beta1"], hp["beta2"], hp["eps"],
                      ps.max_norm, local, comm=comm, chunk_elems=args.chunk, multicast=args.multicast,
-                     push_order=args.push_order, exchange_timeout_ms=30000)
+                     push_order=args.push_order, exchange_timeout_ms=30000,
+                     ce_pull_sources=getattr(args, "ce_pull_sources", None) if comm == "abi" else None,
+                     ce_push_targets=getattr(args, "ce_push_targets", None) if comm == "abi" else None)
+    ce_pull, ce_push = opt.ctx.copy_engine_use() if opt.ctx is not None else (0, 0)
     tuning = apply_tuning(opt, args)
     n_params = ps.numel
     gen = torch.Generator(device=f"cuda:{local}").manual_seed(ps.grad_seed * 1000 + rank)
@@ -153,6 +156,11 @@ def run(args) -> int:
         # the link rates this box gave the two access patterns a moment ago, with nothing else riding on them
         read_peak = link["reads_GBs"] if link else None
         store_peak = link["stores_GBs"] if link else None
+        copy_peak = link["ring_copy_GBs"] if link else None
+        # With copies carrying part of a phase, the phase is rated against the better of the two rates the
+        # fabric gave a moment ago: SM-issued accesses to every peer at once, or one copy between neighbours.
+        reduce_peak = max(read_peak, copy_peak) if (read_peak and ce_pull) else read_peak
+        push_peak = max(store_peak, copy_peak) if (store_peak and ce_push) else store_peak
         nvlink_ms = (pull_remote + push_remote) / (NVLINK_PEER_GBS * 1e9) * 1e3
         hbm_ms = ((4.0 * world + 4.0) + 30.0) * shard / (peak * 1e9) * 1e3
         # The update cannot start before the global norm is known, i.e. before every rank's reduction is
@@ -161,10 +169,15 @@ def run(args) -> int:
         reduce_floor = max(pull_remote / (NVLINK_PEER_GBS * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) * 1e3
         update_floor = max(30.0 * shard / (peak * 1e9), push_remote / (NVLINK_PEER_GBS * 1e9)) * 1e3
         roofline = {
-            "bound": "nvlink", "kernel": "oe_peer_reduce_sumsq (pull reduce-scatter + norm)" if comm != "nccl" else "ncclReduceScatter",
-            "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": read_peak or NVLINK_PEER_GBS, "unit": "GB/s",
-            "frac": (pull_remote / (k1 * 1e-3) / 1e9 / (read_peak or NVLINK_PEER_GBS)) if k1 else None,
-            "peak_kind": ("measured in this run: every rank reading its shard of every peer's gradient buffer at the same time, "
+            "bound": "nvlink",
+            "kernel": ("ncclReduceScatter" if comm == "nccl" else
+                       "%d staged peer copies + oe_peer_reduce_sumsq (pull reduce-scatter + norm)" % ce_pull if ce_pull else
+                       "oe_peer_reduce_sumsq (pull reduce-scatter + norm)"),
+            "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": reduce_peak or NVLINK_PEER_GBS, "unit": "GB/s",
+            "frac": (pull_remote / (k1 * 1e-3) / 1e9 / (reduce_peak or NVLINK_PEER_GBS)) if k1 else None,
+            "peak_kind": ("measured in this run: the better of every rank reading its shard of every peer's gradient buffer at "
+                          "the same time (oe_link_probe_reads) and every rank copying from its neighbour at the same time") if (reduce_peak and ce_pull) else
+                         ("measured in this run: every rank reading its shard of every peer's gradient buffer at the same time, "
                           "nothing stored (oe_link_probe_reads)") if read_peak else
                          "builder constant: 770 GB/s, a one-at-a-time copy-engine peer copy measured on this pool "
                          "(not measured in this run)",
@@ -175,20 +188,21 @@ def run(args) -> int:
             "traffic_source": "none: the bytes that cross NVLink are not DRAM traffic of this GPU; ncu is not run on "
                               "multi-rank commands",
             "algorithmic_bytes_per_launch": pull_remote, "kernel_ms": k1,
-            "update_kernel": {"kernel": "oe_adamw_fused_peers" if comm != "nccl" else "oe_adamw_fused + ncclAllGather",
+            "update_kernel": {"kernel": ("oe_adamw_fused + ncclAllGather" if comm == "nccl" else
+                                         "oe_adamw_fused_peers + %d shadow copies" % ce_push if ce_push else "oe_adamw_fused_peers"),
                               "kernel_ms": k2, "remote_store_bytes": push_remote,
                               "nvlink_achieved": push_remote / (k2 * 1e-3) / 1e9 if k2 else None,
-                              "nvlink_peak_measured": store_peak,
-                              "nvlink_frac_of_measured": push_remote / (k2 * 1e-3) / 1e9 / store_peak if (k2 and store_peak) else None,
+                              "nvlink_peak_measured": push_peak,
+                              "nvlink_frac_of_measured": push_remote / (k2 * 1e-3) / 1e9 / push_peak if (k2 and push_peak) else None,
                               "nvlink_frac_of_770_builder_constant": push_remote / (k2 * 1e-3) / 1e9 / NVLINK_PEER_GBS if k2 else None,
                               "nvlink_frac_of_nominal_900GBs": push_remote / (k2 * 1e-3) / 1e9 / NVLINK_NOMINAL_GBS if k2 else None,
                               "hbm_bytes": 30.0 * shard,
                               "hbm_achieved": 30.0 * shard / (k2 * 1e-3) / 1e9 if k2 else None, "hbm_peak": peak},
             "step_floor_ms": {"nvlink": nvlink_ms, "hbm": hbm_ms, "reduce_then_update": reduce_floor + update_floor,
                               "reduce_then_update_at_measured_link_rates":
-                                  (max(pull_remote / (read_peak * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) +
-                                   max(30.0 * shard / (peak * 1e9), push_remote / (store_peak * 1e9))) * 1e3
-                                  if (read_peak and store_peak) else None},
+                                  (max(pull_remote / (reduce_peak * 1e9), (4.0 * world + 4.0) * shard / (peak * 1e9)) +
+                                   max(30.0 * shard / (peak * 1e9), push_remote / (push_peak * 1e9))) * 1e3
+                                  if (reduce_peak and push_peak) else None},
             "step_frac_of_floor": max(nvlink_ms, hbm_ms) / ms_per_step,
             "step_frac_of_serial_floor": (reduce_floor + update_floor) / ms_per_step,
             "phases_ms": phases,
@@ -200,7 +214,8 @@ def run(args) -> int:
             "config": {"workload": key, "title": ps.title, "params": n_params, "tensors": len(ps.params),
                        "optimizer": "adamw", "max_norm": ps.max_norm, "bf16_shadow": True, "sharding": f"zero1 x{world}",
                        "comm": comm, "multicast_shadow_stores": bool(args.multicast), "push_order": args.push_order,
-                       "tuning": tuning, "shard_elems": shard, "grad_reduce": "mean, ascending rank order",
+                       "tuning": tuning, "copy_engine": {"staged_pull_sources": ce_pull, "shadow_copy_targets": ce_push},
+                       "shard_elems": shard, "grad_reduce": "mean, ascending rank order",
                        "l2": "inputs larger than L2: %.1f GB per rank" % ((6.0 * opt.layout.total + 12.0 * shard) / 1e9),
                        "grad_norm": norm_value},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "clocks": clocks, "gpu_launches": launches,
@@ -265,9 +280,22 @@ def measure_link_peaks(opt, torch, dist, iters: int = 3):
 
     r = timed(lambda: opt.plan.link_probe_reads(opt.grad_bases, opt.lo, shard))
     w = timed(lambda: opt.plan.link_probe_stores(opt.shadow_flat.data_ptr() + 2 * opt.lo, opt.shadow_deltas, shard))
+    # and what a copy gets when every rank copies from the rank after it at the same time (one reader and one
+    # writer per GPU): this rank's shard range of the next rank's gradient buffer into a scratch tensor
+    scratch = torch.empty(shard, dtype=torch.float32, device=dev)
+    source = opt.grad_bases[(opt.rank + 1) % world] + 4 * opt.lo
+    c = timed(lambda: engine_copy(opt, scratch.data_ptr(), source, 4 * shard))
+    del scratch
     return {"reads_GBs": 4.0 * shard * (world - 1) / r / 1e6, "reads_ms": r,
             "stores_GBs": 2.0 * shard * (world - 1) / w / 1e6, "stores_ms": w,
-            "how": "oe_link_probe_reads / oe_link_probe_stores on every rank at once, median of %d, max over ranks" % iters}
+            "ring_copy_GBs": 4.0 * shard / c / 1e6, "ring_copy_ms": c,
+            "how": "oe_link_probe_reads / oe_link_probe_stores / one oe_memcpy_d2d from the next rank, on every rank at once, "
+                   "median of %d, max over ranks" % iters}
+
+
+def engine_copy(opt, dst: int, src: int, nbytes: int) -> None:
+    from gograd_b200 import engine as E
+    E.check(E.lib().oe_memcpy_d2d(opt.device, dst, src, nbytes, E._stream(None)))
 
 
 def launch_shape_sweep(opt, torch, dist, iters: int = 3):
@@ -515,7 +543,9 @@ def phase_times(opt, torch, dist, iters: int):
         return float(t.item())
 
     own = opt.grad_flat[opt.lo:opt.hi]
-    if opt.comm != "nccl":
+    if opt.comm == "abi":
+        out["reduce_ms"] = timed(opt.ctx.reduce)          # staged copies (if the context uses them) + pull kernel
+    elif opt.comm != "nccl":
         out["reduce_ms"] = timed(lambda: opt.plan.peer_reduce_grads(opt.grad_bases, opt.lo, opt.layout.shard_len,
                                                                     own.data_ptr(), 1.0 / opt.world, OE_PARTIAL_ONLY))
     else:
@@ -532,6 +562,8 @@ def phase_times(opt, torch, dist, iters: int):
     if opt.comm == "nccl":
         out["update_ms"] = timed(lambda: opt.plan.adamw_step(hp))
         out["allgather_ms"] = timed(lambda: dist.all_gather_into_tensor(opt.shadow_flat, opt.shadow_flat[opt.lo:opt.hi]))
+    elif opt.comm == "abi":
+        out["update_ms"] = timed(lambda: opt.ctx.adamw_update(hp))   # fused update + shadow stores, then shadow copies
     elif opt.multicast:
         out["update_ms"] = timed(lambda: opt.plan.adamw_step_multicast(hp, opt.shadow_deltas, opt.mc_delta))
     else:

@@ -40,15 +40,17 @@ type SGDHParams struct {
 	StepDev, LRDev                   uint64
 }
 
-// Zero1Desc mirrors oe_zero1_desc (232 bytes): the ranks of a sharded step as seen from one GPU.
+// Zero1Desc mirrors oe_zero1_desc (256 bytes): the ranks of a sharded step as seen from one GPU.
 type Zero1Desc struct {
-	Rank, World       uint32
-	FirstElem, Numel  uint64
-	GradBases         [8]uint64
-	ShadowDeltas      [8]int64
-	ShadowMCDelta     int64
-	SyncBlocks        [8]uint64
-	TimeoutMS, Flags  uint32
+	Rank, World                  uint32
+	FirstElem, Numel             uint64
+	GradBases                    [8]uint64
+	ShadowDeltas                 [8]int64
+	ShadowMCDelta                int64
+	SyncBlocks                   [8]uint64
+	TimeoutMS, Flags             uint32
+	Staging, StagingBytes        uint64 // caller-owned scratch for the copy-engine-assisted reduction, or 0
+	CEPullSources, CEPushTargets uint32 // 0 = the library's choice, 0xffffffff = none
 }
 
 // Flag bits of AdamWHParams.Flags / SGDHParams.Flags / GradNorm.

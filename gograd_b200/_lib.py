@@ -31,11 +31,14 @@ class oe_sgd_hparams(C.Structure):
 class oe_zero1_desc(C.Structure):
     _fields_ = [("rank", C.c_uint32), ("world", C.c_uint32), ("first_elem", C.c_uint64), ("numel", C.c_uint64),
                 ("grad_bases", C.c_uint64 * 8), ("shadow_deltas", C.c_int64 * 8), ("shadow_mc_delta", C.c_int64),
-                ("sync_blocks", C.c_uint64 * 8), ("timeout_ms", C.c_uint32), ("flags", C.c_uint32)]
+                ("sync_blocks", C.c_uint64 * 8), ("timeout_ms", C.c_uint32), ("flags", C.c_uint32),
+                ("staging", C.c_uint64), ("staging_bytes", C.c_uint64), ("ce_pull_sources", C.c_uint32),
+                ("ce_push_targets", C.c_uint32)]
 
 
 OE_ZERO1_SYNC_BYTES = 512
 OE_ZERO1_NO_ENTRY_EXCHANGE = 1
+OE_ZERO1_CE_NONE = 0xffffffff
 OE_TUNE_PEER_REDUCE_GRID, OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_PUSH_WARP_ROTATE = 1, 2, 3, 4
 OE_TUNE_STEP_GRID, OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_PEER_REDUCE_WARP_ROTATE = 5, 6, 7
 
@@ -94,6 +97,10 @@ PROTOTYPES = {
     "oe_zero1_adamw_step": (_i, [_vp, C.POINTER(oe_adamw_hparams), _u64]),
     "oe_zero1_sgd_step": (_i, [_vp, C.POINTER(oe_sgd_hparams), _u64]),
     "oe_zero1_exchange": (_i, [_vp, _u32, _u64]),
+    "oe_zero1_reduce": (_i, [_vp, _u64]),
+    "oe_zero1_info": (C.c_int64, [_vp, _i]),
+    "oe_zero1_adamw_update": (_i, [_vp, C.POINTER(oe_adamw_hparams), _u64]),
+    "oe_zero1_sgd_update": (_i, [_vp, C.POINTER(oe_sgd_hparams), _u64]),
     "oe_zero1_status": (_i, [_vp, C.POINTER(_u32), _u64]),
     "oe_ipc_export": (_i, [_i, _u64, _vp, C.POINTER(_u64)]),
     "oe_ipc_import": (_i, [_i, _vp, C.POINTER(_u64)]),

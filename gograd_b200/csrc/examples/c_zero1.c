@@ -50,7 +50,10 @@ static uint16_t bf16_rne(float x) {
     return (uint16_t)((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
 }
 
-int main(void) {
+int main(int argc, char** argv) {
+    /* "copies": ask for the copy-assisted form of the step (all peers' gradient ranges but one staged by copies,
+     * the last rank of the ring served by a shadow copy), which the library would not choose for shards this small */
+    const int copies = argc > 1 && strcmp(argv[1], "copies") == 0;
     int devices = 0;
     CHECK(oe_device_count(&devices));
     int world = devices > MAX_RANKS ? MAX_RANKS : devices;
@@ -61,6 +64,8 @@ int main(void) {
     const uint32_t total = SHARD * (uint32_t)world;
     const float lr = 3e-4f, beta1 = 0.9f, beta2 = 0.95f, eps = 1e-8f, decay = 0.1f, max_norm = 0.01f;
     uint64_t grad[MAX_RANKS], shadow[MAX_RANKS], master[MAX_RANKS], m[MAX_RANKS], v[MAX_RANKS], sync[MAX_RANKS];
+    uint64_t staging[MAX_RANKS];
+    const uint32_t staged = (copies && world > 1) ? (uint32_t)(world > 2 ? world - 2 : 1) : 0;
     oe_plan* plan[MAX_RANKS];
     oe_zero1* z[MAX_RANKS];
     float* host = (float*)malloc(sizeof(float) * total);
@@ -81,6 +86,8 @@ int main(void) {
         CHECK(oe_mem_alloc(r, 4ull * SHARD, &m[r]));
         CHECK(oe_mem_alloc(r, 4ull * SHARD, &v[r]));
         CHECK(oe_mem_alloc(r, OE_ZERO1_SYNC_BYTES, &sync[r]));
+        staging[r] = 0;
+        if (staged) CHECK(oe_mem_alloc(r, 4ull * SHARD * staged, &staging[r]));
         CHECK(oe_memset_u32(r, shadow[r], 0, total / 2, 0));
         CHECK(oe_memset_u32(r, m[r], 0, SHARD, 0));
         CHECK(oe_memset_u32(r, v[r], 0, SHARD, 0));
@@ -112,7 +119,19 @@ int main(void) {
             d.sync_blocks[q] = sync[q];
         }
         d.timeout_ms = 10000;
+        if (staged) {
+            d.staging = staging[r];
+            d.staging_bytes = 4ull * SHARD * staged; /* 4 * SHARD is a multiple of 256: one slot per staged peer */
+            d.ce_pull_sources = staged;
+            d.ce_push_targets = 1;
+        } else {
+            d.ce_pull_sources = d.ce_push_targets = OE_ZERO1_CE_NONE;
+        }
         CHECK(oe_zero1_create(plan[r], &d, &z[r]));
+        if (oe_zero1_info(z[r], 0) != (int64_t)staged || oe_zero1_info(z[r], 1) != (staged ? 1 : 0)) {
+            fprintf(stderr, "rank %d: the context did not take the requested copy plan\n", r);
+            return 1;
+        }
     }
 
     for (int step = 1; step <= STEPS; step++) {
@@ -198,6 +217,7 @@ int main(void) {
         CHECK(oe_mem_free(r, m[r]));
         CHECK(oe_mem_free(r, v[r]));
         CHECK(oe_mem_free(r, sync[r]));
+        if (staging[r]) CHECK(oe_mem_free(r, staging[r]));
     }
     CHECK(oe_shutdown());
     printf("c_zero1 ok: %d rank(s), %d sharded AdamW steps driven from C, master weights and every rank's bf16 shadow equal the host loop bit for bit\n",

@@ -34,6 +34,7 @@
     X(cuMemcpyHtoDAsync)                     \
     X(cuMemcpyDtoHAsync)                     \
     X(cuMemcpyDtoDAsync)                     \
+    X(cuMemcpyAsync)                         \
     X(cuMemsetD32Async)                      \
     X(cuMemsetD8Async)                       \
     X(cuMemGetInfo)                          \

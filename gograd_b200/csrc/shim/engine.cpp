@@ -8,11 +8,13 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <atomic>
 #include <map>
 #include <mutex>
 #include <new>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../../include/optengine.h"
@@ -1070,7 +1072,8 @@ extern "C" int oe_memcpy_d2d(int device, uint64_t dst, uint64_t src, uint64_t by
     if (bytes == 0) return 0;
     if (!dst || !src) return fail(OE_ERR_INVALID, "oe_memcpy_d2d: NULL address");
     OE_DEVICE_PROLOGUE;
-    OE_CU(d->cuMemcpyDtoDAsync_((CUdeviceptr)dst, (CUdeviceptr)src, bytes, (CUstream)stream), "cuMemcpyDtoDAsync");
+    // the unified-address form: either side may be a peer's buffer mapped on this device
+    OE_CU(d->cuMemcpyAsync_((CUdeviceptr)dst, (CUdeviceptr)src, bytes, (CUstream)stream), "cuMemcpyAsync");
     return 0;
 }
 extern "C" int oe_memset_u32(int device, uint64_t dst, uint32_t value, uint64_t count, uint64_t stream) {
@@ -1277,6 +1280,13 @@ struct oe_zero1 {
     oe_zero1_desc desc;
     uint32_t epoch = 0;
     float mean_scale = 1.0f;
+    // copy-engine assistance, resolved from the descriptor when the context is made
+    uint32_t ce_pull = 0;      // peers whose range a copy stages before the pull kernel
+    uint64_t ce_slot = 0;      // bytes of one staged range
+    uint32_t ce_push = 0;      // ranks served by a copy after the update kernel
+    bool ce_push_auto = false; // the library chose: small shards stay on the kernel's stores
+    int64_t runs_for_upload = -1;                      // plan->uploads the runs below were derived from
+    std::vector<std::pair<uint64_t, uint64_t>> runs;   // this rank's shadow values as (address, bytes) ranges
 };
 
 namespace {
@@ -1297,38 +1307,117 @@ int launch_exchange(const oe_driver* d, oe_zero1* z, uint32_t phase, bool with_n
     return launch(d, z->plan->dc->k.rank_exchange, "oe_rank_exchange", 1, 32, stream, args);
 }
 
-int zero1_step(oe_zero1* z, const oe_adamw_hparams* ahp, const oe_sgd_hparams* shp, uint64_t stream) {
-    if (!z || (!ahp && !shp)) return fail(OE_ERR_INVALID, "oe_zero1 step: NULL argument");
+constexpr size_t kMaxShadowRuns = 64;                  // more ranges than this per target: the kernel stores them itself
+constexpr uint64_t kCopyEngineMinBytes = 64ull << 20;  // the library's own choice leaves smaller shards to the kernels
+
+// The bf16 shadow values this rank's update writes, as maximal contiguous ranges of its shadow buffer.
+void shadow_runs(oe_zero1* z) {
+    const oe_plan* plan = z->plan;
+    if (z->runs_for_upload == plan->uploads) return;
+    z->runs.clear();
+    std::vector<std::pair<uint64_t, uint64_t>> pieces;
+    for (const oe_tensor_desc& t : plan->descs)
+        if (t.grad && t.shadow) pieces.emplace_back(t.shadow, 2ull * t.numel);
+    std::sort(pieces.begin(), pieces.end());
+    for (const auto& p : pieces) {
+        if (!z->runs.empty() && z->runs.back().first + z->runs.back().second == p.first)
+            z->runs.back().second += p.second;
+        else
+            z->runs.push_back(p);
+    }
+    z->runs_for_upload = plan->uploads;
+}
+
+// The reduce phase: staged copies (if any), then the pull kernel that leaves the mean in place and this
+// rank's partial sum of squares in the plan's norm record.
+int zero1_reduce(const oe_driver* d, oe_zero1* z, uint64_t stream) {
+    const oe_zero1_desc& D = z->desc;
+    oe_plan* plan = z->plan;
+    CUstream s = (CUstream)stream;
+    uint64_t out = D.grad_bases[D.rank] + 4ull * D.first_elem;
+    uint64_t bases[OE_MAX_PEERS];
+    for (uint32_t k = 0; k < OE_MAX_PEERS; k++) bases[k] = D.grad_bases[k];
+    if (z->ce_pull && D.numel) {
+        // Window j: every rank copies from the rank j+1 places after it, so each GPU serves one reader at a
+        // time. The pull kernel then finds those ranges in local memory, under the source rank's slot of the sum.
+        CtxGuard guard(d, plan->dc->ctx);
+        for (uint32_t j = 0; j < z->ce_pull; j++) {
+            const uint32_t src = (D.rank + 1 + j) % D.world;
+            const uint64_t dst = D.staging + (uint64_t)j * z->ce_slot;
+            OE_CU(d->cuMemcpyAsync_((CUdeviceptr)dst, (CUdeviceptr)(D.grad_bases[src] + 4ull * D.first_elem), 4ull * D.numel, s),
+                  "cuMemcpyAsync(stage gradients)");
+            bases[src] = dst - 4ull * D.first_elem;
+        }
+    }
+    return oe_peer_reduce_grads(plan, bases, D.world, D.first_elem, D.numel, out, &z->mean_scale, OE_PARTIAL_ONLY, stream);
+}
+
+// The update phase: the fused update storing the shadow to this rank and the next `stored` ranks, then copies
+// of this rank's shadow ranges to the remaining ones.
+int zero1_update(const oe_driver* d, oe_zero1* z, const oe_adamw_hparams* ahp, const oe_sgd_hparams* shp, uint64_t stream) {
+    const oe_zero1_desc& D = z->desc;
+    oe_plan* plan = z->plan;
+    CUstream s = (CUstream)stream;
+    const int64_t* mc = D.shadow_mc_delta ? &D.shadow_mc_delta : nullptr;
+    uint32_t copied = mc ? 0 : z->ce_push;
+    if (copied) {
+        shadow_runs(z);
+        uint64_t bytes = 0;
+        for (const auto& r : z->runs) bytes += r.second;
+        if (z->runs.empty() || z->runs.size() > kMaxShadowRuns || (z->ce_push_auto && bytes < kCopyEngineMinBytes)) copied = 0;
+    }
+    const uint32_t stored = D.world - 1 - copied;
+    int64_t deltas[OE_MAX_PEERS];
+    deltas[0] = 0;
+    for (uint32_t j = 0; j < stored; j++) deltas[1 + j] = D.shadow_deltas[(D.rank + 1 + j) % D.world];
+    const int64_t* use = copied ? deltas : D.shadow_deltas;
+    const uint32_t n_use = copied ? stored + 1 : D.world;
+    int rc;
+    if (ahp)
+        rc = mc ? oe_adamw_step_multicast(plan, ahp, D.shadow_deltas, D.world, mc, stream) : oe_adamw_step_peers(plan, ahp, use, n_use, stream);
+    else
+        rc = mc ? oe_sgd_step_multicast(plan, shp, D.shadow_deltas, D.world, mc, stream) : oe_sgd_step_peers(plan, shp, use, n_use, stream);
+    if (rc || !copied) return rc;
+    // After an exchange that gave up the kernel above did nothing, and these copies carry the values every
+    // rank already holds.
+    CtxGuard guard(d, plan->dc->ctx);
+    for (uint32_t j = stored; j + 1 < D.world; j++) {
+        const int64_t delta = D.shadow_deltas[(D.rank + 1 + j) % D.world];
+        for (const auto& r : z->runs)
+            OE_CU(d->cuMemcpyAsync_((CUdeviceptr)(r.first + (uint64_t)delta), (CUdeviceptr)r.first, r.second, s), "cuMemcpyAsync(shadow)");
+    }
+    return 0;
+}
+
+int zero1_phase_prologue(oe_zero1* z, const oe_adamw_hparams* ahp, const oe_sgd_hparams* shp, const oe_driver** d_out) {
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;
+    // everything that can be refused is checked before the first launch
+    if (ahp && (rc = validate_adamw(z->plan, ahp)) != 0) return rc;
+    if (shp && (rc = validate_sgd(z->plan, shp)) != 0) return rc;
+    *d_out = d;
+    return 0;
+}
+
+int zero1_step(oe_zero1* z, const oe_adamw_hparams* ahp, const oe_sgd_hparams* shp, uint64_t stream) {
+    if (!z || (!ahp && !shp)) return fail(OE_ERR_INVALID, "oe_zero1 step: NULL argument");
+    const oe_driver* d = nullptr;
+    int rc = zero1_phase_prologue(z, ahp, shp, &d);
+    if (rc) return rc;
     oe_plan* plan = z->plan;
-    // everything that can be refused is checked before the first launch of the step
-    if (ahp && (rc = validate_adamw(plan, ahp)) != 0) return rc;
-    if (shp && (rc = validate_sgd(plan, shp)) != 0) return rc;
-    const oe_zero1_desc& D = z->desc;
     CUstream s = (CUstream)stream;
     z->epoch += 1;
     {
         CtxGuard guard(d, plan->dc->ctx);
-        if (!(D.flags & OE_ZERO1_NO_ENTRY_EXCHANGE) && (rc = launch_exchange(d, z, OE_SYNC_GRADS_READY, false, s)) != 0) return rc;
+        if (!(z->desc.flags & OE_ZERO1_NO_ENTRY_EXCHANGE) && (rc = launch_exchange(d, z, OE_SYNC_GRADS_READY, false, s)) != 0) return rc;
     }
-    uint64_t out = D.grad_bases[D.rank] + 4ull * D.first_elem;
-    if ((rc = oe_peer_reduce_grads(plan, D.grad_bases, D.world, D.first_elem, D.numel, out, &z->mean_scale, OE_PARTIAL_ONLY,
-                                   stream)) != 0)
-        return rc;
+    if ((rc = zero1_reduce(d, z, stream)) != 0) return rc;
     {
         CtxGuard guard(d, plan->dc->ctx);
         if ((rc = launch_exchange(d, z, OE_SYNC_REDUCED, true, s)) != 0) return rc;
     }
-    const int64_t* mc = D.shadow_mc_delta ? &D.shadow_mc_delta : nullptr;
-    if (ahp)
-        rc = mc ? oe_adamw_step_multicast(plan, ahp, D.shadow_deltas, D.world, mc, stream)
-                : oe_adamw_step_peers(plan, ahp, D.shadow_deltas, D.world, stream);
-    else
-        rc = mc ? oe_sgd_step_multicast(plan, shp, D.shadow_deltas, D.world, mc, stream)
-                : oe_sgd_step_peers(plan, shp, D.shadow_deltas, D.world, stream);
-    if (rc) return rc;
+    if ((rc = zero1_update(d, z, ahp, shp, stream)) != 0) return rc;
     CtxGuard guard(d, plan->dc->ctx);
     return launch_exchange(d, z, OE_SYNC_PUSHED, false, s);
 }
@@ -1350,11 +1439,36 @@ extern "C" int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero
     }
     if (desc->shadow_deltas[desc->rank] != 0) return fail(OE_ERR_INVALID, "oe_zero1_create: the rank's own shadow distance must be 0");
     if (plan->status_word != 0) return fail(OE_ERR_INVALID, "oe_zero1_create: the plan already drives a sharded step");
+    // copy-engine assistance: an explicit request is honoured or refused, the library's own choice adapts
+    const uint32_t others = desc->world - 1;
+    const uint64_t slot = (4ull * desc->numel + 255ull) & ~255ull;
+    if (desc->staging & 15u) return fail(OE_ERR_INVALID, "oe_zero1_create: staging must be 16-byte aligned");
+    const uint64_t slots = (desc->staging && slot) ? desc->staging_bytes / slot : 0;
+    uint32_t pull = 0, push = 0;
+    if (desc->ce_pull_sources == 0) {
+        if (desc->world >= 4 && 4ull * desc->numel >= kCopyEngineMinBytes) pull = (uint32_t)std::min<uint64_t>(others - 1, slots);
+    } else if (desc->ce_pull_sources != OE_ZERO1_CE_NONE) {
+        if (desc->ce_pull_sources > others) return fail(OE_ERR_INVALID, "oe_zero1_create: ce_pull_sources exceeds the number of peers");
+        if (desc->ce_pull_sources > slots)
+            return fail(OE_ERR_INVALID, "oe_zero1_create: staging holds " + std::to_string(slots) + " gradient ranges of " +
+                                            std::to_string(slot) + " bytes, ce_pull_sources asks for " + std::to_string(desc->ce_pull_sources));
+        pull = desc->ce_pull_sources;
+    }
+    if (desc->ce_push_targets == 0) {
+        if (desc->world >= 8) push = others - 3;
+    } else if (desc->ce_push_targets != OE_ZERO1_CE_NONE) {
+        if (desc->ce_push_targets > others) return fail(OE_ERR_INVALID, "oe_zero1_create: ce_push_targets exceeds the number of peers");
+        push = desc->ce_push_targets;
+    }
     oe_zero1* z = new (std::nothrow) oe_zero1();
     if (!z) return fail(OE_ERR_INVALID, "out of host memory");
     z->plan = plan;
     z->desc = *desc;
     z->mean_scale = (float)(1.0 / (double)desc->world);
+    z->ce_slot = (4ull * desc->numel + 255ull) & ~255ull;
+    z->ce_pull = pull;
+    z->ce_push = push;
+    z->ce_push_auto = desc->ce_push_targets == 0;
     plan->status_word = desc->sync_blocks[desc->rank] + offsetof(oe_sync_block, status);
     *out = z;
     return 0;
@@ -1373,6 +1487,37 @@ extern "C" int oe_zero1_adamw_step(oe_zero1* z, const oe_adamw_hparams* hp, uint
 
 extern "C" int oe_zero1_sgd_step(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream) {
     return zero1_step(z, nullptr, hp, stream);
+}
+
+extern "C" int64_t oe_zero1_info(const oe_zero1* z, int what) {
+    if (!z) return -1;
+    switch (what) {
+        case 0: return z->ce_pull;
+        case 1: return (z->desc.shadow_mc_delta != 0) ? 0 : z->ce_push;
+        case 2: return z->epoch;
+        default: return -1;
+    }
+}
+
+extern "C" int oe_zero1_reduce(oe_zero1* z, uint64_t stream) {
+    if (!z) return fail(OE_ERR_INVALID, "oe_zero1_reduce: NULL argument");
+    const oe_driver* d = nullptr;
+    int rc = zero1_phase_prologue(z, nullptr, nullptr, &d);
+    return rc ? rc : zero1_reduce(d, z, stream);
+}
+
+extern "C" int oe_zero1_adamw_update(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream) {
+    if (!z || !hp) return fail(OE_ERR_INVALID, "oe_zero1_adamw_update: NULL argument");
+    const oe_driver* d = nullptr;
+    int rc = zero1_phase_prologue(z, hp, nullptr, &d);
+    return rc ? rc : zero1_update(d, z, hp, nullptr, stream);
+}
+
+extern "C" int oe_zero1_sgd_update(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream) {
+    if (!z || !hp) return fail(OE_ERR_INVALID, "oe_zero1_sgd_update: NULL argument");
+    const oe_driver* d = nullptr;
+    int rc = zero1_phase_prologue(z, nullptr, hp, &d);
+    return rc ? rc : zero1_update(d, z, nullptr, hp, stream);
 }
 
 extern "C" int oe_zero1_exchange(oe_zero1* z, uint32_t phase, uint64_t stream) {

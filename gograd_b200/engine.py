@@ -3,13 +3,13 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
-from typing import Optional, Sequence
+from typing import Optional, Sequence, Tuple
 
 from . import _lib
 from ._lib import (OE_TUNE_PEER_PUSH_WARP_ROTATE, OE_TUNE_PEER_REDUCE_FIRST, OE_TUNE_PEER_REDUCE_GRID,
                    OE_TUNE_PEER_REDUCE_WARP_ROTATE,
-                   OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_STEP_GRID, OE_ZERO1_NO_ENTRY_EXCHANGE,
-                   OE_ZERO1_SYNC_BYTES)
+                   OE_TUNE_PEER_UPDATE_GRID, OE_TUNE_PEER_UPDATE_VECTORS, OE_TUNE_STEP_GRID, OE_ZERO1_CE_NONE,
+                   OE_ZERO1_NO_ENTRY_EXCHANGE, OE_ZERO1_SYNC_BYTES)
 from ._lib import (OE_ACCUMULATE, OE_CLIP_DEVFORM, OE_MAXIMIZE, OE_NESTEROV, OE_PARTIAL_ONLY, OE_WRITE_SHADOW, OE_ZERO_GRAD,
                    EngineError, check, lib)
 
@@ -277,12 +277,15 @@ class Zero1Context:
 
     def __init__(self, plan: Plan, rank: int, world: int, first_elem: int, numel: int, grad_bases: Sequence[int],
                  shadow_deltas: Sequence[int], sync_blocks: Sequence[int], mc_delta: int = 0, timeout_ms: int = 0,
-                 flags: int = 0):
+                 flags: int = 0, staging: int = 0, staging_bytes: int = 0, ce_pull_sources: int = 0,
+                 ce_push_targets: int = 0):
         d = _lib.oe_zero1_desc()
         d.rank, d.world, d.first_elem, d.numel = rank, world, first_elem, numel
         for k in range(world):
             d.grad_bases[k], d.shadow_deltas[k], d.sync_blocks[k] = grad_bases[k], shadow_deltas[k], sync_blocks[k]
         d.shadow_mc_delta, d.timeout_ms, d.flags = mc_delta, timeout_ms, flags
+        d.staging, d.staging_bytes = staging, staging_bytes
+        d.ce_pull_sources, d.ce_push_targets = ce_pull_sources, ce_push_targets
         self._plan = plan  # the context borrows the plan
         self._h = C.c_void_p()
         check(lib().oe_zero1_create(plan._h, C.byref(d), C.byref(self._h)))
@@ -297,6 +300,23 @@ class Zero1Context:
 
     def exchange(self, phase: int, stream=None) -> None:
         check(lib().oe_zero1_exchange(self._h, phase, _stream(stream)))
+
+    def copy_engine_use(self) -> Tuple[int, int]:
+        """(peers staged by a copy in the reduce phase, ranks served by a shadow copy in the update phase)."""
+        return int(lib().oe_zero1_info(self._h, 0)), int(lib().oe_zero1_info(self._h, 1))
+
+    def reduce(self, stream=None) -> None:
+        """The reduce phase alone: staged copies (if the context uses them) and the pull kernel."""
+        check(lib().oe_zero1_reduce(self._h, _stream(stream)))
+
+    def adamw_update(self, hp: AdamWHParams, stream=None) -> None:
+        """The update phase alone: fused update with its shadow stores, then the shadow copies."""
+        c = hp.to_c()
+        check(lib().oe_zero1_adamw_update(self._h, C.byref(c), _stream(stream)))
+
+    def sgd_update(self, hp: SGDHParams, stream=None) -> None:
+        c = hp.to_c()
+        check(lib().oe_zero1_sgd_update(self._h, C.byref(c), _stream(stream)))
 
     def status(self, stream=None) -> int:
         """Waits for the stream; 0 when every exchange completed, else raises EngineError (OE_ERR_DEVICE)."""

@@ -244,12 +244,17 @@ class Zero1AdamW(Zero1Schedule):
     of the IPC handles, the layout check) and, on the abi path, for nothing after that. Gradients
     are written by the caller into `self.grad_flat` (or the per-tensor views `self.grads`); after
     `step()` every rank's `self.shadow_flat` holds the bf16 weights of the whole model.
-    `exchange_timeout_ms` bounds every wait of the abi path's exchange kernels (0 = 10 s)."""
+    `exchange_timeout_ms` bounds every wait of the abi path's exchange kernels (0 = 10 s).
+    `ce_pull_sources` / `ce_push_targets` (abi path): how many peers' gradient ranges a copy stages
+    before the pull kernel, and how many ranks get their shadow values from a copy after the update
+    kernel; None leaves the choice to the library (by world size and shard size), 0 switches it off.
+    The staging buffer (4 bytes x shard length per staged peer) is allocated here."""
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
                  beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
                  chunk_elems: int = 0, multicast: bool = False, exchange_timeout_ms: int = 0,
-                 push_order: str = "ascending"):
+                 push_order: str = "ascending", ce_pull_sources: Optional[int] = None,
+                 ce_push_targets: Optional[int] = None):
         import torch
         import torch.distributed as dist
 
@@ -296,6 +301,7 @@ class Zero1AdamW(Zero1Schedule):
         self.sumsq = torch.as_tensor(_RawCuda(self.plan.norm_address(), (1,), "<f8"), device=dev)
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._imported: List[int] = []
+        self._staging = None
         self.grad_bases: Optional[List[int]] = None
         self.shadow_deltas: Optional[List[int]] = None
         self.mc_delta = 0
@@ -307,8 +313,23 @@ class Zero1AdamW(Zero1Schedule):
             self._sync = torch.zeros(engine.OE_ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device=dev)
             self._map_peers()
         if comm == "abi":
+            # staging for the copy-assisted reduction: what an explicit request needs, else what the library
+            # would use (all peers but one from four ranks on, shards of 64 MiB and more)
+            if ce_pull_sources is None:
+                staged = self.world - 2 if self.world >= 4 and 4 * L.shard_len >= (64 << 20) else 0
+            else:
+                staged = int(ce_pull_sources)
+            slot = -(-4 * L.shard_len // 256) * 256
+            self._staging = torch.empty(max(staged * slot, 16), dtype=torch.uint8, device=dev) if staged else None
+
+            def knob(value):
+                return 0 if value is None else (engine.OE_ZERO1_CE_NONE if int(value) == 0 else int(value))
+
             self.ctx = engine.Zero1Context(self.plan, self.rank, self.world, self.lo, L.shard_len, self.grad_bases,
-                                           self.shadow_deltas, self.sync_bases, self.mc_delta, exchange_timeout_ms)
+                                           self.shadow_deltas, self.sync_bases, self.mc_delta, exchange_timeout_ms,
+                                           staging=self._staging.data_ptr() if staged else 0,
+                                           staging_bytes=staged * slot, ce_pull_sources=knob(ce_pull_sources),
+                                           ce_push_targets=knob(ce_push_targets))
 
     def _allocate_state(self, dev) -> None:
         torch = self.torch
@@ -411,7 +432,9 @@ class Zero1AdamW(Zero1Schedule):
             return
         if self.comm == "abi":
             self.ctx.exchange(0)
-        elif self.sync_before_pull:
+            self.ctx.reduce()      # staged copies, if the context uses them, then the pull kernel
+            return
+        if self.sync_before_pull:
             # every rank's gradients must be complete before anyone pulls them
             dist.all_reduce(self._token, op=dist.ReduceOp.SUM, group=self.pg)
         self.plan.peer_reduce_grads(self.grad_bases, self.lo, self.layout.shard_len, own.data_ptr(),
@@ -430,6 +453,8 @@ class Zero1AdamW(Zero1Schedule):
         hp = self._hparams(OE_WRITE_SHADOW)
         if self.comm == "nccl":
             self.plan.adamw_step(hp)
+        elif self.comm == "abi":
+            self.ctx.adamw_update(hp)   # shadow stores, then the shadow copies the context uses
         elif self.multicast:
             self.plan.adamw_step_multicast(hp, self.shadow_deltas, self.mc_delta)
         else:
@@ -654,6 +679,8 @@ class Zero1SGD(Zero1AdamW):
         hp = self._sgd_hparams()
         if self.comm == "nccl":
             self.plan.sgd_step(hp)
+        elif self.comm == "abi":
+            self.ctx.sgd_update(hp)
         elif self.multicast:
             self.plan.sgd_step_multicast(hp, self.shadow_deltas, self.mc_delta)
         else:

@@ -364,7 +364,28 @@ typedef struct oe_zero1_desc {
     uint64_t sync_blocks[8];       /* rank k's exchange area as mapped on this GPU                     */
     uint32_t timeout_ms;           /* limit of every wait, 0 = 10000                                   */
     uint32_t flags;                /* OE_ZERO1_NO_ENTRY_EXCHANGE                                       */
+    /* Copy-engine assistance (see below); all four may be 0.                                          */
+    uint64_t staging;              /* caller-owned device scratch, 16-byte aligned, or 0               */
+    uint64_t staging_bytes;
+    uint32_t ce_pull_sources;      /* peers whose gradient range a copy brings into staging before the
+                                      pull kernel runs: 0 = the library's choice, OE_ZERO1_CE_NONE = none */
+    uint32_t ce_push_targets;      /* ranks that receive their shadow copy from a copy after the update
+                                      kernel: 0 = the library's choice, OE_ZERO1_CE_NONE = none          */
 } oe_zero1_desc;
+#define OE_ZERO1_CE_NONE 0xffffffffu
+/* Copy-engine assistance. With all GPUs of a box reading (or writing) each other at once, SM-issued loads
+ * reach about 665 GB/s and stores about 620 GB/s per GPU; copies issued in RING order — in window j every rank
+ * talks to the rank j places after it, so every GPU serves one reader and one writer at a time — reach
+ * 740 / 770 GB/s. So from four ranks on the step lets copies carry part of the traffic, all on the caller's
+ * stream, in whole-shard pieces:
+ *   reduce: the ranges of the first ce_pull_sources ranks after this one are copied into `staging` (4*numel
+ *           bytes each), then the pull kernel reads those locally and the remaining peers over NVLink — same
+ *           ascending-rank-order sum, bit for bit;
+ *   update: the kernel stores the shadow to this rank and the next world-1-ce_push_targets ranks, then copies
+ *           deliver this rank's shard to the remaining ranks.
+ * The library's choice (measured on 8-GPU B200 boxes): eight ranks: all but one peer through staging, four
+ * shadow copies; four to seven ranks: all but one peer through staging, no shadow copies; fewer: none. Without
+ * (enough) staging the reduce stays on the SM path. */
 
 typedef struct oe_zero1 oe_zero1;
 
@@ -381,9 +402,20 @@ OE_API int oe_zero1_destroy(oe_zero1* z);
 OE_API int oe_zero1_adamw_step(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream);
 OE_API int oe_zero1_sgd_step(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream);
 
-/* One exchange on its own (phase 0 gradients ready — it also begins a new step —, 1 reduced, 2 stored):
- * for a caller that enqueues the phases itself. */
+/* The phases on their own, for a caller that enqueues them itself (and for timing them one by one): one
+ * exchange (phase 0 gradients ready — it also begins a new step —, 1 reduced, 2 stored); the reduce phase
+ * (staged copies, if the context uses them, then the pull kernel); the update phase (fused update and shadow
+ * stores, then shadow copies, if the context uses them). A step is exchange 0, reduce, exchange 1, update,
+ * exchange 2 in that order on one stream. */
 OE_API int oe_zero1_exchange(oe_zero1* z, uint32_t phase, uint64_t stream);
+OE_API int oe_zero1_reduce(oe_zero1* z, uint64_t stream);
+OE_API int oe_zero1_adamw_update(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream);
+OE_API int oe_zero1_sgd_update(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream);
+
+/* what: 0 peers staged by a copy in the reduce phase, 1 ranks served by a shadow copy in the update phase (as
+ * resolved when the context was made; the library's own choice still leaves shadow ranges under 64 MiB to the
+ * kernel), 2 steps begun so far. -1 for anything else. */
+OE_API int64_t oe_zero1_info(const oe_zero1* z, int what);
 
 /* Waits for `stream` and reads the status word: 0 and *status_out = 0 when every exchange so far
  * completed; otherwise OE_ERR_DEVICE, *status_out = 1 | phase << 8 | missing rank << 16, and the message

@@ -176,6 +176,48 @@ shapes["bad knob"] = lib.oe_plan_set_tuning(plan3, 4, 3)   # warp rotation takes
 assert lib.oe_plan_destroy(plan3) == 0
 out["peer_shapes"] = shapes
 
+# ---- 6c. copy-engine assistance of the sharded step: which copies are issued, from where to where ---------
+W, R, SH = 4, 1, 4096                                         # four ranks, this one is rank 1, 4096 elements per shard
+g4 = [buf.alloc(4 * SH * W) for _ in range(W)]
+s4 = [buf.alloc(2 * SH * W) for _ in range(W)]
+y4 = [buf.alloc(512) for _ in range(W)]
+stage = buf.alloc(2 * 4 * SH)
+for k in range(W):                                            # rank k's gradient words all read 0x01010101 * (k + 1)
+    C.memset(g4[k], k + 1, 4 * SH * W)
+    C.memset(s4[k], 0, 2 * SH * W)
+C.memset(s4[R] + 2 * SH * R, 0x5a, 2 * SH)                    # "this rank's updated shadow values" (no kernel runs here)
+d4 = _lib.oe_zero1_desc()
+d4.rank, d4.world, d4.first_elem, d4.numel = R, W, SH * R, SH
+for k in range(W):
+    d4.grad_bases[k], d4.sync_blocks[k], d4.shadow_deltas[k] = g4[k], y4[k], s4[k] - s4[R]
+d4.staging, d4.staging_bytes, d4.ce_pull_sources, d4.ce_push_targets = stage, 2 * 4 * SH, 2, 1
+own = _lib.oe_tensor_desc(buf.alloc(4 * SH), g4[R] + 4 * SH * R, buf.alloc(4 * SH), buf.alloc(4 * SH), s4[R] + 2 * SH * R, SH, 1.0, 0.1)
+arr8, _ = descs(own)
+plan4 = C.c_void_p()
+assert lib.oe_plan_create(0, arr8, 1, 0, C.byref(plan4)) == 0, err()
+z4 = C.c_void_p()
+too_many = _lib.oe_zero1_desc.from_buffer_copy(d4)
+too_many.ce_pull_sources = 3
+rc_too_many = lib.oe_zero1_create(plan4, C.byref(too_many), C.byref(C.c_void_p()))
+odd = _lib.oe_zero1_desc.from_buffer_copy(d4)
+odd.staging = stage + 4
+rc_odd = lib.oe_zero1_create(plan4, C.byref(odd), C.byref(C.c_void_p()))
+assert lib.oe_zero1_create(plan4, C.byref(d4), C.byref(z4)) == 0, err()
+copies_before = fake.fake_cuda_calls(b"cuMemcpyAsync")
+fake.fake_cuda_reset_launches()
+assert lib.oe_zero1_adamw_step(z4, C.byref(hp), 0) == 0, err()
+seq4 = launches()
+staged = [C.string_at(stage + j * 4 * SH, 4 * SH) for j in range(2)]
+served = {k: C.string_at(s4[k] + 2 * SH * R, 2 * SH) == b"\x5a" * (2 * SH) for k in range(W)}
+out["zero1_copies"] = {
+    "too_many": rc_too_many, "odd_staging": rc_odd, "copies": fake.fake_cuda_calls(b"cuMemcpyAsync") - copies_before,
+    "sequence": [x[0] for x in seq4],
+    # window 0 stages rank 2 (the next rank), window 1 rank 3; rank 0, the last of the ring, is left to the kernel
+    "staged_ranks": [staged[0][0], staged[1][0]], "staged_whole": all(x == bytes([x[0]]) * (4 * SH) for x in staged),
+    # one shadow copy: the kernel serves ranks 1 (own), 2 and 3, the copy serves the last of the ring, rank 0
+    "served_by_copy": served}
+assert lib.oe_zero1_destroy(z4) == 0 and lib.oe_plan_destroy(plan4) == 0
+
 # ---- 7. shutdown refuses while plans live; everything the library allocated is returned -------------------
 rc_shutdown_live = lib.oe_shutdown()
 assert lib.oe_plan_destroy(plan) == 0 and lib.oe_plan_destroy(plan2) == 0

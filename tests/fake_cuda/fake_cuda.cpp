@@ -180,6 +180,11 @@ CUresult CUDAAPI cuMemcpyDtoDAsync(CUdeviceptr d, CUdeviceptr s, size_t n, CUstr
     memmove((void*)(uintptr_t)d, (const void*)(uintptr_t)s, n);
     return CUDA_SUCCESS;
 }
+CUresult CUDAAPI cuMemcpyAsync(CUdeviceptr d, CUdeviceptr s, size_t n, CUstream) {
+    ENTER("cuMemcpyAsync");
+    memmove((void*)(uintptr_t)d, (const void*)(uintptr_t)s, n);
+    return CUDA_SUCCESS;
+}
 CUresult CUDAAPI cuMemsetD32Async(CUdeviceptr d, unsigned v, size_t n, CUstream) {
     unsigned* p = (unsigned*)(uintptr_t)d;
     for (size_t i = 0; i < n; i++) p[i] = v;

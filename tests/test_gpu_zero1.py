@@ -133,10 +133,15 @@ def test_peer_kernels_with_emulated_ranks(world, tuned):
         p.close()
 
 
-def _comm_options(spec):
-    """"peer", "nccl", "abi", optionally "+mc" (multicast shadow stores) and "+rot" (rotated store order)."""
+def _comm_options(spec, world):
+    """"peer", "nccl", "abi", optionally "+mc" (multicast shadow stores), "+rot" (rotated store order) and "+ce"
+    (copies stage all peers' gradients but one, two with two ranks, and carry the shadow to the last ranks of
+    the ring: the library would not choose that for shards this small, so it is asked for)."""
     parts = spec.split("+")
-    return dict(comm=parts[0], multicast="mc" in parts[1:], push_order="rotated" if "rot" in parts[1:] else "ascending")
+    options = dict(comm=parts[0], multicast="mc" in parts[1:], push_order="rotated" if "rot" in parts[1:] else "ascending")
+    if "ce" in parts[1:]:
+        options.update(ce_pull_sources=1 if world == 2 else world - 2, ce_push_targets=1 if world <= 4 else world - 4)
+    return options
 
 
 def _rank_main(rank, world, port, comm, queue):
@@ -146,7 +151,7 @@ def _rank_main(rank, world, port, comm, queue):
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     opt = Zero1AdamW(NUMELS, GROUPS, HP["lr"], HP["beta1"], HP["beta2"], HP["eps"], HP["max_norm"], rank,
-                     exchange_timeout_ms=20000, **_comm_options(comm))
+                     exchange_timeout_ms=20000, **_comm_options(comm, world))
     L = opt.layout
     weights = torch.zeros(L.total)
     for o, w in zip(L.offsets, _weights()):
@@ -193,7 +198,7 @@ def _run_real_ranks(world, comm):
     return ref, L, flat, results, oracle
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "peer+rot", "abi+mc"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "peer+rot", "abi+mc", "abi+ce"])
 def test_two_real_ranks(comm):
     """Two ranks: every path is bit-identical to the oracle (a two-term sum has one order). "abi" runs
     the whole step through oe_zero1_adamw_step with the library's own exchanges between the ranks;
@@ -209,7 +214,7 @@ def test_two_real_ranks(comm):
             assert np.array_equal(shadow[o:o + n], want), f"rank {rank} shadow[{i}] ({comm})"
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+mc"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+mc", "abi+ce"])
 def test_all_real_ranks_of_the_box(comm):
     """Every GPU of the box as a rank (4 or 8): the peer path adds in ascending rank order and stays
     bit-identical to the oracle; NCCL's order is its own, so that path is held to the stated
@@ -327,7 +332,7 @@ def _sgd_rank_main(rank, world, port, comm, queue):
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
-    options = _comm_options(comm)
+    options = _comm_options(comm, world)
     opt = Zero1SGD(NUMELS, GROUPS, SGD_HP["lr"], SGD_HP["momentum"], SGD_HP["dampening"], SGD_HP["nesterov"],
                    SGD_HP["maximize"], SGD_HP["max_norm"], rank, options.pop("comm"), **options)
     L = opt.layout
@@ -347,7 +352,7 @@ def _sgd_rank_main(rank, world, port, comm, queue):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "abi"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+ce"])
 def test_two_real_ranks_sgd(comm):
     """The sharded SGD over two real ranks, both data paths, bit-identical to the unsharded oracle."""
     if torch.cuda.device_count() < 2:

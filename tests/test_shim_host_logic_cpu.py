@@ -72,6 +72,18 @@ def test_sharded_step_is_five_launches_in_order(cases):
     assert z["plan_destroyed_first"] == -1
 
 
+def test_sharded_step_with_copy_engine_assistance(cases):
+    """Rank 1 of 4 with two staged sources and one copied shadow target: the copies run in ring order from the
+    next rank on, the kernels keep their places in the sequence, and a request the staging cannot hold is refused."""
+    z = cases["zero1_copies"]
+    assert z["too_many"] == -1 and z["odd_staging"] == -1
+    assert z["copies"] == 3
+    assert z["sequence"] == ["oe_rank_exchange", "oe_peer_reduce_sumsq_n4", "oe_rank_exchange", "oe_adamw_fused_peers",
+                             "oe_rank_exchange"]
+    assert z["staged_ranks"] == [3, 4] and z["staged_whole"]           # ranks 2 and 3 fill their words with 3 and 4
+    assert z["served_by_copy"] == {"0": True, "1": True, "2": False, "3": False}
+
+
 def test_sharded_update_launch_shape_follows_the_rank_count(cases):
     """400 work units on a 148-SM device whose kernels fit two CTAs per SM: the persistent grid is 296 CTAs; with
     four ranks the library launches one CTA per SM (the measured optimum there); an explicit knob wins."""
