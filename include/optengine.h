@@ -479,6 +479,7 @@ OE_API int oe_mem_free(int device, uint64_t address);
 OE_API int oe_mem_info(int device, uint64_t* free_out, uint64_t* total_out);
 OE_API int oe_memcpy_h2d(int device, uint64_t dst, const void* src, uint64_t bytes, uint64_t stream);
 OE_API int oe_memcpy_d2h(int device, void* dst, uint64_t src, uint64_t bytes, uint64_t stream);
+/* either side may be a peer's buffer mapped on `device` (oe_ipc_import, oe_enable_peer_access) */
 OE_API int oe_memcpy_d2d(int device, uint64_t dst, uint64_t src, uint64_t bytes, uint64_t stream);
 OE_API int oe_memset_u32(int device, uint64_t dst, uint32_t value, uint64_t count, uint64_t stream);
 OE_API int oe_host_alloc(int device, uint64_t bytes, void** out); /* page-locked host memory */
