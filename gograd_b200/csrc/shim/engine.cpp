@@ -1359,7 +1359,8 @@ int zero1_update(const oe_driver* d, oe_zero1* z, const oe_adamw_hparams* ahp, c
     oe_plan* plan = z->plan;
     CUstream s = (CUstream)stream;
     const int64_t* mc = D.shadow_mc_delta ? &D.shadow_mc_delta : nullptr;
-    uint32_t copied = mc ? 0 : z->ce_push;
+    const uint32_t hp_flags = ahp ? ahp->flags : shp->flags;
+    uint32_t copied = (mc || !(hp_flags & OE_WRITE_SHADOW)) ? 0 : z->ce_push;   // no shadow written: nothing to deliver
     if (copied) {
         shadow_runs(z);
         uint64_t bytes = 0;
