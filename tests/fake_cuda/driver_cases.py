@@ -177,46 +177,73 @@ assert lib.oe_plan_destroy(plan3) == 0
 out["peer_shapes"] = shapes
 
 # ---- 6c. copy-engine assistance of the sharded step: which copies are issued, from where to where ---------
-W, R, SH = 4, 1, 4096                                         # four ranks, this one is rank 1, 4096 elements per shard
-g4 = [buf.alloc(4 * SH * W) for _ in range(W)]
-s4 = [buf.alloc(2 * SH * W) for _ in range(W)]
-y4 = [buf.alloc(512) for _ in range(W)]
-stage = buf.alloc(2 * 4 * SH)
-for k in range(W):                                            # rank k's gradient words all read 0x01010101 * (k + 1)
-    C.memset(g4[k], k + 1, 4 * SH * W)
-    C.memset(s4[k], 0, 2 * SH * W)
-C.memset(s4[R] + 2 * SH * R, 0x5a, 2 * SH)                    # "this rank's updated shadow values" (no kernel runs here)
-d4 = _lib.oe_zero1_desc()
-d4.rank, d4.world, d4.first_elem, d4.numel = R, W, SH * R, SH
-for k in range(W):
-    d4.grad_bases[k], d4.sync_blocks[k], d4.shadow_deltas[k] = g4[k], y4[k], s4[k] - s4[R]
-d4.staging, d4.staging_bytes, d4.ce_pull_sources, d4.ce_push_targets = stage, 2 * 4 * SH, 2, 1
-own = _lib.oe_tensor_desc(buf.alloc(4 * SH), g4[R] + 4 * SH * R, buf.alloc(4 * SH), buf.alloc(4 * SH), s4[R] + 2 * SH * R, SH, 1.0, 0.1)
-arr8, _ = descs(own)
-plan4 = C.c_void_p()
-assert lib.oe_plan_create(0, arr8, 1, 0, C.byref(plan4)) == 0, err()
-z4 = C.c_void_p()
-too_many = _lib.oe_zero1_desc.from_buffer_copy(d4)
-too_many.ce_pull_sources = 3
-rc_too_many = lib.oe_zero1_create(plan4, C.byref(too_many), C.byref(C.c_void_p()))
-odd = _lib.oe_zero1_desc.from_buffer_copy(d4)
-odd.staging = stage + 4
-rc_odd = lib.oe_zero1_create(plan4, C.byref(odd), C.byref(C.c_void_p()))
-assert lib.oe_zero1_create(plan4, C.byref(d4), C.byref(z4)) == 0, err()
-copies_before = fake.fake_cuda_calls(b"cuMemcpyAsync")
-fake.fake_cuda_reset_launches()
-assert lib.oe_zero1_adamw_step(z4, C.byref(hp), 0) == 0, err()
-seq4 = launches()
-staged = [C.string_at(stage + j * 4 * SH, 4 * SH) for j in range(2)]
-served = {k: C.string_at(s4[k] + 2 * SH * R, 2 * SH) == b"\x5a" * (2 * SH) for k in range(W)}
-out["zero1_copies"] = {
-    "too_many": rc_too_many, "odd_staging": rc_odd, "copies": fake.fake_cuda_calls(b"cuMemcpyAsync") - copies_before,
-    "sequence": [x[0] for x in seq4],
-    # window 0 stages rank 2 (the next rank), window 1 rank 3; rank 0, the last of the ring, is left to the kernel
-    "staged_ranks": [staged[0][0], staged[1][0]], "staged_whole": all(x == bytes([x[0]]) * (4 * SH) for x in staged),
-    # one shadow copy: the kernel serves ranks 1 (own), 2 and 3, the copy serves the last of the ring, rank 0
-    "served_by_copy": served}
-assert lib.oe_zero1_destroy(z4) == 0 and lib.oe_plan_destroy(plan4) == 0
+def copy_plan_case(W, R, pull, push, SH=4096):
+    """Rank R of W with `pull` staged sources and `push` copied shadow targets, asked for explicitly."""
+    g = [buf.alloc(4 * SH * W) for _ in range(W)]
+    s_ = [buf.alloc(2 * SH * W) for _ in range(W)]
+    y = [buf.alloc(512) for _ in range(W)]
+    stage = buf.alloc(pull * 4 * SH)
+    for k in range(W):                                        # rank k's gradient bytes all read k + 1
+        C.memset(g[k], k + 1, 4 * SH * W)
+        C.memset(s_[k], 0, 2 * SH * W)
+    C.memset(s_[R] + 2 * SH * R, 0x5a, 2 * SH)                # "this rank's updated shadow values" (no kernel runs here)
+    d = _lib.oe_zero1_desc()
+    d.rank, d.world, d.first_elem, d.numel = R, W, SH * R, SH
+    for k in range(W):
+        d.grad_bases[k], d.sync_blocks[k], d.shadow_deltas[k] = g[k], y[k], s_[k] - s_[R]
+    d.staging, d.staging_bytes, d.ce_pull_sources, d.ce_push_targets = stage, pull * 4 * SH, pull, push
+    own = _lib.oe_tensor_desc(buf.alloc(4 * SH), g[R] + 4 * SH * R, buf.alloc(4 * SH), buf.alloc(4 * SH), s_[R] + 2 * SH * R, SH, 1.0, 0.1)
+    arr, _ = descs(own)
+    plan = C.c_void_p()
+    assert lib.oe_plan_create(0, arr, 1, 0, C.byref(plan)) == 0, err()
+    too_many = _lib.oe_zero1_desc.from_buffer_copy(d)
+    too_many.ce_pull_sources = pull + 1
+    rc_too_many = lib.oe_zero1_create(plan, C.byref(too_many), C.byref(C.c_void_p()))
+    odd = _lib.oe_zero1_desc.from_buffer_copy(d)
+    odd.staging = stage + 4
+    rc_odd = lib.oe_zero1_create(plan, C.byref(odd), C.byref(C.c_void_p()))
+    z = C.c_void_p()
+    assert lib.oe_zero1_create(plan, C.byref(d), C.byref(z)) == 0, err()
+    before = fake.fake_cuda_calls(b"cuMemcpyAsync")
+    fake.fake_cuda_reset_launches()
+    assert lib.oe_zero1_adamw_step(z, C.byref(hp), 0) == 0, err()
+    seq = launches()
+    staged = [C.string_at(stage + j * 4 * SH, 4 * SH) for j in range(pull)]
+    served = {k: C.string_at(s_[k] + 2 * SH * R, 2 * SH) == b"\x5a" * (2 * SH) for k in range(W)}
+    result = {"too_many": rc_too_many, "odd_staging": rc_odd, "copies": fake.fake_cuda_calls(b"cuMemcpyAsync") - before,
+              "sequence": [x[0] for x in seq], "info": [lib.oe_zero1_info(z, 0), lib.oe_zero1_info(z, 1)],
+              # slot j holds the range of the rank j + 1 places after this one, whole
+              "staged_ranks": [x[0] - 1 for x in staged], "staged_whole": all(x == bytes([x[0]]) * (4 * SH) for x in staged),
+              # the kernel would serve this rank and the next ones; the copies serve the last `push` ranks of the ring
+              "served_by_copy": sorted(k for k, ok in served.items() if ok and k != R)}
+    assert lib.oe_zero1_destroy(z) == 0 and lib.oe_plan_destroy(plan) == 0
+    return result
+
+
+out["zero1_copies"] = {"4": copy_plan_case(4, 1, 2, 1), "8": copy_plan_case(8, 5, 6, 4)}
+
+# the library's own choice by world size, shard size and the staging it was given (contexts made, never stepped)
+def library_choice(W, numel, staging_slots):
+    d = _lib.oe_zero1_desc()
+    d.rank, d.world, d.first_elem, d.numel = 0, W, 0, numel
+    for k in range(W):
+        d.grad_bases[k], d.sync_blocks[k], d.shadow_deltas[k] = 0x10000000 * (k + 1), 0x1000 * (k + 1), 0x40000000 * k
+    d.staging, d.staging_bytes = (0x7000000000, staging_slots * 4 * numel) if staging_slots else (0, 0)
+    plan = C.c_void_p()
+    arr, _ = descs(desc(4096))
+    assert lib.oe_plan_create(0, arr, 1, 0, C.byref(plan)) == 0, err()
+    z = C.c_void_p()
+    assert lib.oe_zero1_create(plan, C.byref(d), C.byref(z)) == 0, err()
+    got = [lib.oe_zero1_info(z, 0), lib.oe_zero1_info(z, 1)]
+    assert lib.oe_zero1_destroy(z) == 0 and lib.oe_plan_destroy(plan) == 0
+    return got
+
+
+BIG, SMALL = 1 << 26, 1 << 20     # 256 MiB and 4 MiB of gradients per shard
+out["zero1_library_choice"] = {
+    "8 ranks": library_choice(8, BIG, 7), "8 ranks, staging for 3": library_choice(8, BIG, 3),
+    "8 ranks, no staging": library_choice(8, BIG, 0), "8 ranks, small shard": library_choice(8, SMALL, 7),
+    "4 ranks": library_choice(4, BIG, 3), "2 ranks": library_choice(2, BIG, 1), "1 rank": library_choice(1, BIG, 0)}
 
 # ---- 7. shutdown refuses while plans live; everything the library allocated is returned -------------------
 rc_shutdown_live = lib.oe_shutdown()

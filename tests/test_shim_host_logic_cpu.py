@@ -73,15 +73,24 @@ def test_sharded_step_is_five_launches_in_order(cases):
 
 
 def test_sharded_step_with_copy_engine_assistance(cases):
-    """Rank 1 of 4 with two staged sources and one copied shadow target: the copies run in ring order from the
-    next rank on, the kernels keep their places in the sequence, and a request the staging cannot hold is refused."""
-    z = cases["zero1_copies"]
-    assert z["too_many"] == -1 and z["odd_staging"] == -1
-    assert z["copies"] == 3
-    assert z["sequence"] == ["oe_rank_exchange", "oe_peer_reduce_sumsq_n4", "oe_rank_exchange", "oe_adamw_fused_peers",
-                             "oe_rank_exchange"]
-    assert z["staged_ranks"] == [3, 4] and z["staged_whole"]           # ranks 2 and 3 fill their words with 3 and 4
-    assert z["served_by_copy"] == {"0": True, "1": True, "2": False, "3": False}
+    """Rank 1 of 4 (two staged sources, one copied shadow target) and rank 5 of 8 (six and four): the copies run in
+    ring order from the next rank on, the kernels keep their places in the sequence, and a request the staging
+    cannot hold is refused."""
+    for world, rank, pull, push in ((4, 1, 2, 1), (8, 5, 6, 4)):
+        z = cases["zero1_copies"][str(world)]
+        assert z["too_many"] == -1 and z["odd_staging"] == -1
+        assert z["copies"] == pull + push and z["info"] == [pull, push]
+        assert z["sequence"] == ["oe_rank_exchange", f"oe_peer_reduce_sumsq_n{world}", "oe_rank_exchange", "oe_adamw_fused_peers",
+                                 "oe_rank_exchange"]
+        assert z["staged_ranks"] == [(rank + 1 + j) % world for j in range(pull)] and z["staged_whole"]
+        assert z["served_by_copy"] == sorted((rank + 1 + j) % world for j in range(world - 1 - push, world - 1))
+
+
+def test_the_librarys_own_copy_plan(cases):
+    """[staged sources, copied shadow targets] as oe_zero1_create resolves them when the caller leaves the choice."""
+    assert cases["zero1_library_choice"] == {
+        "8 ranks": [6, 4], "8 ranks, staging for 3": [3, 4], "8 ranks, no staging": [0, 4], "8 ranks, small shard": [0, 4],
+        "4 ranks": [2, 0], "2 ranks": [0, 0], "1 rank": [0, 0]}
 
 
 def test_sharded_update_launch_shape_follows_the_rank_count(cases):
