@@ -48,8 +48,10 @@ def run(args) -> int:
                      ps.max_norm, local, comm=comm, chunk_elems=args.chunk, multicast=args.multicast,
                      push_order=args.push_order, exchange_timeout_ms=30000,
                      ce_pull_sources=getattr(args, "ce_pull_sources", None) if comm == "abi" else None,
-                     ce_push_targets=getattr(args, "ce_push_targets", None) if comm == "abi" else None)
+                     ce_push_targets=getattr(args, "ce_push_targets", None) if comm == "abi" else None,
+                     staging_writers=bool(getattr(args, "staging_writers", False)) and comm == "abi")
     ce_pull, ce_push = opt.ctx.copy_engine_use() if opt.ctx is not None else (0, 0)
+    staged_by = "owners" if (opt.ctx is not None and opt.ctx.staging_written_by_owners()) else "reader"
     tuning = apply_tuning(opt, args)
     n_params = ps.numel
     gen = torch.Generator(device=f"cuda:{local}").manual_seed(ps.grad_seed * 1000 + rank)
@@ -214,7 +216,7 @@ def run(args) -> int:
             "config": {"workload": key, "title": ps.title, "params": n_params, "tensors": len(ps.params),
                        "optimizer": "adamw", "max_norm": ps.max_norm, "bf16_shadow": True, "sharding": f"zero1 x{world}",
                        "comm": comm, "multicast_shadow_stores": bool(args.multicast), "push_order": args.push_order,
-                       "tuning": tuning, "copy_engine": {"staged_pull_sources": ce_pull, "shadow_copy_targets": ce_push},
+                       "tuning": tuning, "copy_engine": {"staged_pull_sources": ce_pull, "shadow_copy_targets": ce_push, "staged_by": staged_by},
                        "shard_elems": shard, "grad_reduce": "mean, ascending rank order",
                        "l2": "inputs larger than L2: %.1f GB per rank" % ((6.0 * opt.layout.total + 12.0 * shard) / 1e9),
                        "grad_norm": norm_value},

@@ -40,7 +40,7 @@ type SGDHParams struct {
 	StepDev, LRDev                   uint64
 }
 
-// Zero1Desc mirrors oe_zero1_desc (256 bytes): the ranks of a sharded step as seen from one GPU.
+// Zero1Desc mirrors oe_zero1_desc (320 bytes): the ranks of a sharded step as seen from one GPU.
 type Zero1Desc struct {
 	Rank, World                  uint32
 	FirstElem, Numel             uint64
@@ -51,6 +51,7 @@ type Zero1Desc struct {
 	TimeoutMS, Flags             uint32
 	Staging, StagingBytes        uint64 // caller-owned scratch for the copy-engine-assisted reduction, or 0
 	CEPullSources, CEPushTargets uint32 // 0 = the library's choice, 0xffffffff = none
+	StagingBases                 [8]uint64 // rank k's staging as mapped on this GPU, or all 0
 }
 
 // Flag bits of AdamWHParams.Flags / SGDHParams.Flags / GradNorm.

@@ -33,7 +33,7 @@ class oe_zero1_desc(C.Structure):
                 ("grad_bases", C.c_uint64 * 8), ("shadow_deltas", C.c_int64 * 8), ("shadow_mc_delta", C.c_int64),
                 ("sync_blocks", C.c_uint64 * 8), ("timeout_ms", C.c_uint32), ("flags", C.c_uint32),
                 ("staging", C.c_uint64), ("staging_bytes", C.c_uint64), ("ce_pull_sources", C.c_uint32),
-                ("ce_push_targets", C.c_uint32)]
+                ("ce_push_targets", C.c_uint32), ("staging_bases", C.c_uint64 * 8)]
 
 
 OE_ZERO1_SYNC_BYTES = 512

@@ -1282,6 +1282,8 @@ struct oe_zero1 {
     float mean_scale = 1.0f;
     // copy-engine assistance, resolved from the descriptor when the context is made
     uint32_t ce_pull = 0;      // peers whose range a copy stages before the pull kernel
+    bool ce_pull_writes = false;  // the staged ranges are written by their owners into this rank's staging
+    uint32_t staged_count = 0;    // reduce phases begun in that form: the epoch of the staging exchange
     uint64_t ce_slot = 0;      // bytes of one staged range
     uint32_t ce_push = 0;      // ranks served by a copy after the update kernel
     bool ce_push_auto = false; // the library chose: small shards stay on the kernel's stores
@@ -1296,7 +1298,8 @@ int launch_exchange(const oe_driver* d, oe_zero1* z, uint32_t phase, bool with_n
     a.rank = z->desc.rank;
     a.world = z->desc.world;
     a.phase = phase;
-    a.epoch = z->epoch;
+    // the staging exchange counts the reduce phases (one per step, more when a caller times the phase on its own)
+    a.epoch = phase == OE_SYNC_STAGED ? z->staged_count : z->epoch;
     for (uint32_t k = 0; k < OE_MAX_PEERS; k++) a.block[k] = z->desc.sync_blocks[k < z->desc.world ? k : z->desc.rank];
     a.norm_rec = with_norm ? (uint64_t)z->plan->d_norm : 0;
     uint64_t ms = z->desc.timeout_ms ? z->desc.timeout_ms : 10000u;
@@ -1337,7 +1340,7 @@ int zero1_reduce(const oe_driver* d, oe_zero1* z, uint64_t stream) {
     uint64_t out = D.grad_bases[D.rank] + 4ull * D.first_elem;
     uint64_t bases[OE_MAX_PEERS];
     for (uint32_t k = 0; k < OE_MAX_PEERS; k++) bases[k] = D.grad_bases[k];
-    if (z->ce_pull && D.numel) {
+    if (z->ce_pull && D.numel && !z->ce_pull_writes) {
         // Window j: every rank copies from the rank j+1 places after it, so each GPU serves one reader at a
         // time. The pull kernel then finds those ranges in local memory, under the source rank's slot of the sum.
         CtxGuard guard(d, plan->dc->ctx);
@@ -1347,6 +1350,25 @@ int zero1_reduce(const oe_driver* d, oe_zero1* z, uint64_t stream) {
             OE_CU(d->cuMemcpyAsync_((CUdeviceptr)dst, (CUdeviceptr)(D.grad_bases[src] + 4ull * D.first_elem), 4ull * D.numel, s),
                   "cuMemcpyAsync(stage gradients)");
             bases[src] = dst - 4ull * D.first_elem;
+        }
+    } else if (z->ce_pull && D.numel) {
+        // The same windows with the copies going the other way: in window j this rank writes the range that
+        // belongs to the rank j+1 places after it into slot j of that rank's staging, so each GPU serves one
+        // writer at a time; slot j of this rank's staging is filled by the rank j+1 places BEFORE it. An
+        // exchange tells every rank that its staging is complete.
+        {
+            CtxGuard guard(d, plan->dc->ctx);
+            for (uint32_t j = 0; j < z->ce_pull; j++) {
+                const uint32_t to = (D.rank + 1 + j) % D.world;
+                const uint64_t dst = D.staging_bases[to] + (uint64_t)j * z->ce_slot;
+                const uint64_t src = D.grad_bases[D.rank] + 4ull * D.numel * to;
+                OE_CU(d->cuMemcpyAsync_((CUdeviceptr)dst, (CUdeviceptr)src, 4ull * D.numel, s), "cuMemcpyAsync(stage gradients at the owner)");
+                const uint32_t from = (D.rank + D.world - 1 - j) % D.world;
+                bases[from] = D.staging + (uint64_t)j * z->ce_slot - 4ull * D.first_elem;
+            }
+            z->staged_count += 1;
+            int rc = launch_exchange(d, z, OE_SYNC_STAGED, false, s);
+            if (rc) return rc;
         }
     }
     return oe_peer_reduce_grads(plan, bases, D.world, D.first_elem, D.numel, out, &z->mean_scale, OE_PARTIAL_ONLY, stream);
@@ -1461,10 +1483,25 @@ extern "C" int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero
         if (desc->ce_push_targets > others) return fail(OE_ERR_INVALID, "oe_zero1_create: ce_push_targets exceeds the number of peers");
         push = desc->ce_push_targets;
     }
+    // staging_bases: all peers' entries set = the owners write the staged ranges; all zero = this rank reads them
+    uint32_t shared = 0;
+    for (uint32_t k = 0; k < desc->world; k++)
+        if (k != desc->rank && desc->staging_bases[k] != 0) shared++;
+    bool writes = false;
+    if (shared != 0 && pull != 0) {
+        if (shared != others) return fail(OE_ERR_INVALID, "oe_zero1_create: staging_bases must name every peer's staging or none");
+        for (uint32_t k = 0; k < desc->world; k++)
+            if (k != desc->rank && (desc->staging_bases[k] & 15u))
+                return fail(OE_ERR_INVALID, "oe_zero1_create: staging of rank " + std::to_string(k) + " is not 16-byte aligned");
+        if (desc->first_elem != (uint64_t)desc->rank * desc->numel)
+            return fail(OE_ERR_INVALID, "oe_zero1_create: staging written by the owners needs equal shards in rank order (first_elem = rank * numel)");
+        writes = true;
+    }
     oe_zero1* z = new (std::nothrow) oe_zero1();
     if (!z) return fail(OE_ERR_INVALID, "out of host memory");
     z->plan = plan;
     z->desc = *desc;
+    z->ce_pull_writes = writes;
     z->mean_scale = (float)(1.0 / (double)desc->world);
     z->ce_slot = (4ull * desc->numel + 255ull) & ~255ull;
     z->ce_pull = pull;
@@ -1496,6 +1533,7 @@ extern "C" int64_t oe_zero1_info(const oe_zero1* z, int what) {
         case 0: return z->ce_pull;
         case 1: return (z->desc.shadow_mc_delta != 0) ? 0 : z->ce_push;
         case 2: return z->epoch;
+        case 3: return z->ce_pull_writes ? 1 : 0;
         default: return -1;
     }
 }
@@ -1523,7 +1561,7 @@ extern "C" int oe_zero1_sgd_update(oe_zero1* z, const oe_sgd_hparams* hp, uint64
 
 extern "C" int oe_zero1_exchange(oe_zero1* z, uint32_t phase, uint64_t stream) {
     if (!z) return fail(OE_ERR_INVALID, "oe_zero1_exchange: NULL argument");
-    if (phase >= OE_SYNC_PHASES) return fail(OE_ERR_INVALID, "oe_zero1_exchange: unknown phase");
+    if (phase > OE_SYNC_PUSHED) return fail(OE_ERR_INVALID, "oe_zero1_exchange: unknown phase");  // the staging exchange belongs to the reduce phase
     int rc = 0;
     const oe_driver* d = driver_or_fail(&rc);
     if (!d) return rc;

@@ -101,6 +101,7 @@ typedef struct oe_peer_grads {
 #define OE_SYNC_GRADS_READY 0  /* this rank's gradients are complete: the others may pull them      */
 #define OE_SYNC_REDUCED     1  /* this rank's pull is over and its partial sum is published          */
 #define OE_SYNC_PUSHED      2  /* this rank's shadow stores are performed on every GPU               */
+#define OE_SYNC_STAGED      3  /* this rank's gradient copies into the others' staging are complete  */
 typedef struct oe_sync_block {
     uint32_t arrive[OE_SYNC_PHASES][OE_MAX_PEERS]; /* 128 B */
     double partial[2][OE_MAX_PEERS];               /* 128 B, indexed by epoch parity */

@@ -278,7 +278,7 @@ class Zero1Context:
     def __init__(self, plan: Plan, rank: int, world: int, first_elem: int, numel: int, grad_bases: Sequence[int],
                  shadow_deltas: Sequence[int], sync_blocks: Sequence[int], mc_delta: int = 0, timeout_ms: int = 0,
                  flags: int = 0, staging: int = 0, staging_bytes: int = 0, ce_pull_sources: int = 0,
-                 ce_push_targets: int = 0):
+                 ce_push_targets: int = 0, staging_bases: Optional[Sequence[int]] = None):
         d = _lib.oe_zero1_desc()
         d.rank, d.world, d.first_elem, d.numel = rank, world, first_elem, numel
         for k in range(world):
@@ -286,6 +286,8 @@ class Zero1Context:
         d.shadow_mc_delta, d.timeout_ms, d.flags = mc_delta, timeout_ms, flags
         d.staging, d.staging_bytes = staging, staging_bytes
         d.ce_pull_sources, d.ce_push_targets = ce_pull_sources, ce_push_targets
+        for k, base in enumerate(staging_bases or []):
+            d.staging_bases[k] = base
         self._plan = plan  # the context borrows the plan
         self._h = C.c_void_p()
         check(lib().oe_zero1_create(plan._h, C.byref(d), C.byref(self._h)))
@@ -304,6 +306,9 @@ class Zero1Context:
     def copy_engine_use(self) -> Tuple[int, int]:
         """(peers staged by a copy in the reduce phase, ranks served by a shadow copy in the update phase)."""
         return int(lib().oe_zero1_info(self._h, 0)), int(lib().oe_zero1_info(self._h, 1))
+
+    def staging_written_by_owners(self) -> bool:
+        return int(lib().oe_zero1_info(self._h, 3)) == 1
 
     def reduce(self, stream=None) -> None:
         """The reduce phase alone: staged copies (if the context uses them) and the pull kernel."""

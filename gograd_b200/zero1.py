@@ -248,13 +248,15 @@ class Zero1AdamW(Zero1Schedule):
     `ce_pull_sources` / `ce_push_targets` (abi path): how many peers' gradient ranges a copy stages
     before the pull kernel, and how many ranks get their shadow values from a copy after the update
     kernel; None leaves the choice to the library (by world size and shard size), 0 switches it off.
-    The staging buffer (4 bytes x shard length per staged peer) is allocated here."""
+    The staging buffer (4 bytes x shard length per staged peer) is allocated here. `staging_writers`
+    maps every rank's staging on every GPU, so that the staged ranges are written by their owners
+    instead of read by the rank that reduces them."""
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
                  beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
                  chunk_elems: int = 0, multicast: bool = False, exchange_timeout_ms: int = 0,
                  push_order: str = "ascending", ce_pull_sources: Optional[int] = None,
-                 ce_push_targets: Optional[int] = None):
+                 ce_push_targets: Optional[int] = None, staging_writers: bool = False):
         import torch
         import torch.distributed as dist
 
@@ -302,16 +304,13 @@ class Zero1AdamW(Zero1Schedule):
         self._token = torch.zeros(1, dtype=torch.float32, device=dev)
         self._imported: List[int] = []
         self._staging = None
+        self.staging_bases: Optional[List[int]] = None
         self.grad_bases: Optional[List[int]] = None
         self.shadow_deltas: Optional[List[int]] = None
         self.mc_delta = 0
         self.ctx = None
         self._closed = False
         self._lost = False   # a roll call found a rank missing: nothing collective may follow
-        if comm in ("peer", "abi"):
-            # the exchange area of the abi path: zeroed, exported like the other buffers
-            self._sync = torch.zeros(engine.OE_ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device=dev)
-            self._map_peers()
         if comm == "abi":
             # staging for the copy-assisted reduction: what an explicit request needs, else what the library
             # would use (all peers but one from four ranks on, shards of 64 MiB and more)
@@ -319,17 +318,23 @@ class Zero1AdamW(Zero1Schedule):
                 staged = self.world - 2 if self.world >= 4 and 4 * L.shard_len >= (64 << 20) else 0
             else:
                 staged = int(ce_pull_sources)
-            slot = -(-4 * L.shard_len // 256) * 256
-            self._staging = torch.empty(max(staged * slot, 16), dtype=torch.uint8, device=dev) if staged else None
-
+            self._staging_slot = -(-4 * L.shard_len // 256) * 256
+            if staged:
+                self._staging = torch.empty(staged * self._staging_slot, dtype=torch.uint8, device=dev)
+        if comm in ("peer", "abi"):
+            # the exchange area of the abi path: zeroed, exported like the other buffers
+            self._sync = torch.zeros(engine.OE_ZERO1_SYNC_BYTES // 4, dtype=torch.int32, device=dev)
+            self._map_peers(share_staging=staging_writers)
+        if comm == "abi":
             def knob(value):
                 return 0 if value is None else (engine.OE_ZERO1_CE_NONE if int(value) == 0 else int(value))
 
+            staged_bytes = self._staging.numel() if self._staging is not None else 0
             self.ctx = engine.Zero1Context(self.plan, self.rank, self.world, self.lo, L.shard_len, self.grad_bases,
                                            self.shadow_deltas, self.sync_bases, self.mc_delta, exchange_timeout_ms,
-                                           staging=self._staging.data_ptr() if staged else 0,
-                                           staging_bytes=staged * slot, ce_pull_sources=knob(ce_pull_sources),
-                                           ce_push_targets=knob(ce_push_targets))
+                                           staging=self._staging.data_ptr() if staged_bytes else 0,
+                                           staging_bytes=staged_bytes, ce_pull_sources=knob(ce_pull_sources),
+                                           ce_push_targets=knob(ce_push_targets), staging_bases=self.staging_bases)
 
     def _allocate_state(self, dev) -> None:
         torch = self.torch
@@ -347,16 +352,19 @@ class Zero1AdamW(Zero1Schedule):
         return descs
 
     # ---- peer mapping (CUDA IPC through the C ABI) -------------------------------------
-    def _map_peers(self) -> None:
+    def _map_peers(self, share_staging: bool = False) -> None:
         eng, dist = self.engine, self.dist
         mine = {"grad": eng.ipc_export(self.grad_flat.data_ptr(), self.device),
                 "sync": eng.ipc_export(self._sync.data_ptr(), self.device)}
         if self._symm is None:
             mine["shadow"] = eng.ipc_export(self.shadow_flat.data_ptr(), self.device)
+        own = {"grad": self.grad_flat.data_ptr(), "sync": self._sync.data_ptr(), "shadow": self.shadow_flat.data_ptr()}
+        if share_staging and self._staging is not None:
+            mine["staging"] = eng.ipc_export(self._staging.data_ptr(), self.device)
+            own["staging"] = self._staging.data_ptr()
         everyone = [None] * self.world
         dist.all_gather_object(everyone, mine, group=self.pg)
         opened = {}
-        own = {"grad": self.grad_flat.data_ptr(), "sync": self._sync.data_ptr(), "shadow": self.shadow_flat.data_ptr()}
         seen = {key: [] for key in own}
         for r, info in enumerate(everyone):
             for key in own:
@@ -371,6 +379,7 @@ class Zero1AdamW(Zero1Schedule):
                         self._imported.append(opened[handle])
                     seen[key].append(opened[handle] + offset)
         self.grad_bases, self.sync_bases = seen["grad"], seen["sync"]
+        self.staging_bases = seen.get("staging")
         self.shadow_deltas = [a - own["shadow"] for a in seen["shadow"]]
         if self._symm is not None:
             self.mc_delta = int(self._symm.multicast_ptr) - own["shadow"]

@@ -371,6 +371,8 @@ typedef struct oe_zero1_desc {
                                       pull kernel runs: 0 = the library's choice, OE_ZERO1_CE_NONE = none */
     uint32_t ce_push_targets;      /* ranks that receive their shadow copy from a copy after the update
                                       kernel: 0 = the library's choice, OE_ZERO1_CE_NONE = none          */
+    uint64_t staging_bases[8];     /* rank k's staging as mapped on this GPU (own entry = staging), or all 0:
+                                      with them the staged ranges are WRITTEN by their owners (see below)  */
 } oe_zero1_desc;
 #define OE_ZERO1_CE_NONE 0xffffffffu
 /* Copy-engine assistance. With all GPUs of a box reading (or writing) each other at once, SM-issued loads
@@ -380,7 +382,12 @@ typedef struct oe_zero1_desc {
  * stream, in whole-shard pieces:
  *   reduce: the ranges of the first ce_pull_sources ranks after this one are copied into `staging` (4*numel
  *           bytes each), then the pull kernel reads those locally and the remaining peers over NVLink — same
- *           ascending-rank-order sum, bit for bit;
+ *           ascending-rank-order sum, bit for bit. With staging_bases set (every rank's staging mapped on
+ *           every GPU, all of one size) the copies go the other way: each rank writes its own gradient ranges
+ *           into the staging of the ce_pull_sources ranks after it — a copy that writes to a peer runs at
+ *           770 GB/s where one that reads from it runs at 740 — and one more exchange (phase 3) tells every
+ *           rank that its staging is complete. That form needs equal shards in rank order
+ *           (first_elem = rank * numel on every rank) and the same ce_pull_sources on every rank;
  *   update: the kernel stores the shadow to this rank and the next world-1-ce_push_targets ranks, then copies
  *           deliver this rank's shard to the remaining ranks.
  * The library's choice (measured on 8-GPU B200 boxes): eight ranks: all but one peer through staging, four
@@ -414,7 +421,8 @@ OE_API int oe_zero1_sgd_update(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t s
 
 /* what: 0 peers staged by a copy in the reduce phase, 1 ranks served by a shadow copy in the update phase (as
  * resolved when the context was made; the library's own choice still leaves shadow ranges under 64 MiB to the
- * kernel), 2 steps begun so far. -1 for anything else. */
+ * kernel), 2 steps begun so far, 3 whether the staged ranges are written by their owners (1) or read by this rank
+ * (0). -1 for anything else. */
 OE_API int64_t oe_zero1_info(const oe_zero1* z, int what);
 
 /* Waits for `stream` and reads the status word: 0 and *status_out = 0 when every exchange so far

@@ -177,14 +177,18 @@ assert lib.oe_plan_destroy(plan3) == 0
 out["peer_shapes"] = shapes
 
 # ---- 6c. copy-engine assistance of the sharded step: which copies are issued, from where to where ---------
-def copy_plan_case(W, R, pull, push, SH=4096):
-    """Rank R of W with `pull` staged sources and `push` copied shadow targets, asked for explicitly."""
+def copy_plan_case(W, R, pull, push, SH=4096, writers=False):
+    """Rank R of W with `pull` staged sources and `push` copied shadow targets, asked for explicitly; with
+    `writers` every rank's staging is known and the staged ranges are written by their owners."""
     g = [buf.alloc(4 * SH * W) for _ in range(W)]
     s_ = [buf.alloc(2 * SH * W) for _ in range(W)]
     y = [buf.alloc(512) for _ in range(W)]
-    stage = buf.alloc(pull * 4 * SH)
-    for k in range(W):                                        # rank k's gradient bytes all read k + 1
-        C.memset(g[k], k + 1, 4 * SH * W)
+    stages = [buf.alloc(pull * 4 * SH) for _ in range(W)]
+    stage = stages[R]
+    for k in range(W):                                        # rank k's gradient bytes read 16 k + t inside shard t
+        for t in range(W):
+            C.memset(g[k] + 4 * SH * t, 16 * k + t, 4 * SH)
+        C.memset(stages[k], 0xff, pull * 4 * SH)
         C.memset(s_[k], 0, 2 * SH * W)
     C.memset(s_[R] + 2 * SH * R, 0x5a, 2 * SH)                # "this rank's updated shadow values" (no kernel runs here)
     d = _lib.oe_zero1_desc()
@@ -192,6 +196,9 @@ def copy_plan_case(W, R, pull, push, SH=4096):
     for k in range(W):
         d.grad_bases[k], d.sync_blocks[k], d.shadow_deltas[k] = g[k], y[k], s_[k] - s_[R]
     d.staging, d.staging_bytes, d.ce_pull_sources, d.ce_push_targets = stage, pull * 4 * SH, pull, push
+    if writers:
+        for k in range(W):
+            d.staging_bases[k] = stages[k]
     own = _lib.oe_tensor_desc(buf.alloc(4 * SH), g[R] + 4 * SH * R, buf.alloc(4 * SH), buf.alloc(4 * SH), s_[R] + 2 * SH * R, SH, 1.0, 0.1)
     arr, _ = descs(own)
     plan = C.c_void_p()
@@ -208,19 +215,34 @@ def copy_plan_case(W, R, pull, push, SH=4096):
     fake.fake_cuda_reset_launches()
     assert lib.oe_zero1_adamw_step(z, C.byref(hp), 0) == 0, err()
     seq = launches()
-    staged = [C.string_at(stage + j * 4 * SH, 4 * SH) for j in range(pull)]
+    if writers:   # slot j of the rank j + 1 places after this one holds this rank's gradient bytes; its own staging is untouched
+        staged = [C.string_at(stages[(R + 1 + j) % W] + j * 4 * SH, 4 * SH) for j in range(pull)]
+        untouched = C.string_at(stage, pull * 4 * SH) == b"\xff" * (pull * 4 * SH)
+    else:
+        staged = [C.string_at(stage + j * 4 * SH, 4 * SH) for j in range(pull)]
     served = {k: C.string_at(s_[k] + 2 * SH * R, 2 * SH) == b"\x5a" * (2 * SH) for k in range(W)}
     result = {"too_many": rc_too_many, "odd_staging": rc_odd, "copies": fake.fake_cuda_calls(b"cuMemcpyAsync") - before,
-              "sequence": [x[0] for x in seq], "info": [lib.oe_zero1_info(z, 0), lib.oe_zero1_info(z, 1)],
-              # slot j holds the range of the rank j + 1 places after this one, whole
-              "staged_ranks": [x[0] - 1 for x in staged], "staged_whole": all(x == bytes([x[0]]) * (4 * SH) for x in staged),
+              "sequence": [x[0] for x in seq], "info": [lib.oe_zero1_info(z, 0), lib.oe_zero1_info(z, 1), lib.oe_zero1_info(z, 3)],
+              # (rank the bytes come from, shard they were taken from) per slot, and that each slot holds one whole range
+              "staged_from": [[x[0] // 16, x[0] % 16] for x in staged], "staged_whole": all(x == bytes([x[0]]) * (4 * SH) for x in staged),
               # the kernel would serve this rank and the next ones; the copies serve the last `push` ranks of the ring
               "served_by_copy": sorted(k for k, ok in served.items() if ok and k != R)}
-    assert lib.oe_zero1_destroy(z) == 0 and lib.oe_plan_destroy(plan) == 0
+    if writers:
+        result["own_staging_untouched"] = untouched
+    assert lib.oe_zero1_destroy(z) == 0
+    if writers:   # the owners' form needs every peer's staging and equal shards in rank order
+        partial = _lib.oe_zero1_desc.from_buffer_copy(d)
+        partial.staging_bases[(R + 1) % W] = 0
+        shifted = _lib.oe_zero1_desc.from_buffer_copy(d)
+        shifted.first_elem += 4
+        result["refused"] = [lib.oe_zero1_create(plan, C.byref(partial), C.byref(C.c_void_p())),
+                             lib.oe_zero1_create(plan, C.byref(shifted), C.byref(C.c_void_p()))]
+    assert lib.oe_plan_destroy(plan) == 0
     return result
 
 
-out["zero1_copies"] = {"4": copy_plan_case(4, 1, 2, 1), "8": copy_plan_case(8, 5, 6, 4)}
+out["zero1_copies"] = {"4": copy_plan_case(4, 1, 2, 1), "8": copy_plan_case(8, 5, 6, 4),
+                       "8 writers": copy_plan_case(8, 5, 6, 4, writers=True)}
 
 # the library's own choice by world size, shard size and the staging it was given (contexts made, never stepped)
 def library_choice(W, numel, staging_slots):

@@ -31,7 +31,7 @@ def test_struct_layouts_match_the_header():
     assert C.sizeof(_lib.oe_adamw_hparams) == 48
     assert C.sizeof(_lib.oe_sgd_hparams) == 40
     assert _lib.oe_adamw_hparams.step_dev.offset == 32
-    assert C.sizeof(_lib.oe_zero1_desc) == 256 and _lib.oe_zero1_desc.sync_blocks.offset == 160
+    assert C.sizeof(_lib.oe_zero1_desc) == 320 and _lib.oe_zero1_desc.sync_blocks.offset == 160
     assert _lib.oe_zero1_desc.shadow_mc_delta.offset == 152 and _lib.oe_zero1_desc.timeout_ms.offset == 224
 
 
@@ -76,7 +76,7 @@ def test_headers_are_plain_c(tmp_path):
     src.write_text('#include "optengine.h"\n#include "gograd_host.h"\n'
                    "int main(void) { return sizeof(oe_tensor_desc) == 56 && sizeof(oe_adamw_hparams) == 48 &&\n"
                    "                        sizeof(oe_sgd_hparams) == 40 && sizeof(gg_sgd_options) == 24 &&\n"
-                   "                        sizeof(oe_zero1_desc) == 256 && sizeof(gg_sgd_config) == 28 ? 0 : 1; }\n")
+                   "                        sizeof(oe_zero1_desc) == 320 && sizeof(gg_sgd_config) == 28 ? 0 : 1; }\n")
     exe = tmp_path / "abi"
     subprocess.run([cc, "-std=c11", "-Wall", "-Wextra", "-Werror", "-pedantic", "-I", os.path.join(ROOT, "include"),
                     str(src), "-o", str(exe)], check=True)

@@ -139,8 +139,9 @@ def _comm_options(spec, world):
     the ring: the library would not choose that for shards this small, so it is asked for)."""
     parts = spec.split("+")
     options = dict(comm=parts[0], multicast="mc" in parts[1:], push_order="rotated" if "rot" in parts[1:] else "ascending")
-    if "ce" in parts[1:]:
-        options.update(ce_pull_sources=1 if world == 2 else world - 2, ce_push_targets=1 if world <= 4 else world - 4)
+    if "ce" in parts[1:] or "cew" in parts[1:]:   # "cew": the staged ranges are written by their owners
+        options.update(ce_pull_sources=1 if world == 2 else world - 2, ce_push_targets=1 if world <= 4 else world - 4,
+                       staging_writers="cew" in parts[1:])
     return options
 
 
@@ -198,7 +199,7 @@ def _run_real_ranks(world, comm):
     return ref, L, flat, results, oracle
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "peer+rot", "abi+mc", "abi+ce"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "peer+rot", "abi+mc", "abi+ce", "abi+cew"])
 def test_two_real_ranks(comm):
     """Two ranks: every path is bit-identical to the oracle (a two-term sum has one order). "abi" runs
     the whole step through oe_zero1_adamw_step with the library's own exchanges between the ranks;
@@ -214,7 +215,7 @@ def test_two_real_ranks(comm):
             assert np.array_equal(shadow[o:o + n], want), f"rank {rank} shadow[{i}] ({comm})"
 
 
-@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+mc", "abi+ce"])
+@pytest.mark.parametrize("comm", ["peer", "nccl", "abi", "abi+mc", "abi+ce", "abi+cew"])
 def test_all_real_ranks_of_the_box(comm):
     """Every GPU of the box as a rank (4 or 8): the peer path adds in ascending rank order and stays
     bit-identical to the oracle; NCCL's order is its own, so that path is held to the stated

@@ -79,11 +79,25 @@ def test_sharded_step_with_copy_engine_assistance(cases):
     for world, rank, pull, push in ((4, 1, 2, 1), (8, 5, 6, 4)):
         z = cases["zero1_copies"][str(world)]
         assert z["too_many"] == -1 and z["odd_staging"] == -1
-        assert z["copies"] == pull + push and z["info"] == [pull, push]
+        assert z["copies"] == pull + push and z["info"] == [pull, push, 0]
         assert z["sequence"] == ["oe_rank_exchange", f"oe_peer_reduce_sumsq_n{world}", "oe_rank_exchange", "oe_adamw_fused_peers",
                                  "oe_rank_exchange"]
-        assert z["staged_ranks"] == [(rank + 1 + j) % world for j in range(pull)] and z["staged_whole"]
+        # slot j: this rank's shard as the rank j + 1 places after it holds it
+        assert z["staged_from"] == [[(rank + 1 + j) % world, rank] for j in range(pull)] and z["staged_whole"]
         assert z["served_by_copy"] == sorted((rank + 1 + j) % world for j in range(world - 1 - push, world - 1))
+
+
+def test_sharded_step_with_staging_written_by_the_owners(cases):
+    """Rank 5 of 8 knows every rank's staging: it writes its own gradient ranges into slot j of the rank j + 1 places
+    after it (never into its own), one more exchange follows the copies, and the form is refused when a peer's
+    staging is missing or the shards are not in rank order."""
+    z = cases["zero1_copies"]["8 writers"]
+    assert z["copies"] == 6 + 4 and z["info"] == [6, 4, 1]
+    assert z["sequence"] == ["oe_rank_exchange", "oe_rank_exchange", "oe_peer_reduce_sumsq_n8", "oe_rank_exchange",
+                             "oe_adamw_fused_peers", "oe_rank_exchange"]
+    # slot j of the rank j + 1 places after rank 5 holds rank 5's gradients for THAT rank's shard
+    assert z["staged_from"] == [[5, (5 + 1 + j) % 8] for j in range(6)] and z["staged_whole"] and z["own_staging_untouched"]
+    assert z["refused"] == [-1, -1]
 
 
 def test_the_librarys_own_copy_plan(cases):
