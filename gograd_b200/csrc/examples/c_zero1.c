@@ -7,15 +7,18 @@
  * ONE call per rank and step: oe_zero1_adamw_step. The calls only enqueue work; rank 0's first
  * exchange kernel waits (bounded) on its GPU until rank 1's step has been enqueued on the next GPU a
  * few microseconds later. With a single GPU the world has one rank and the exchanges meet themselves.
+ * Run as "c_zero1 copies" it asks for the copy-assisted form of the step and issues each rank's call
+ * from a thread of its own (see the comment at the call).
  *
  * The result is checked on the host against the same arithmetic written out in C: the mean of the
  * ranks' gradients added in ascending rank order, the global norm from a float64 sum, the clip
  * coefficient of the host rule, AdamW in the operation order of autograd/nn.go:519-528, and the bf16
  * shadow as round-to-nearest-even of the master — bit for bit, on every rank.
  *
- *   cc -std=c11 -ffp-contract=off c_zero1.c -I../../../include -L../.. -loptengine -Wl,-rpath,../.. -lm -o c_zero1 && ./c_zero1
+ *   cc -std=c11 -ffp-contract=off c_zero1.c -I../../../include -L../.. -loptengine -Wl,-rpath,../.. -lm -lpthread -o c_zero1 && ./c_zero1
  */
 #include <math.h>
+#include <pthread.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -48,6 +51,19 @@ static uint16_t bf16_rne(float x) {
     uint32_t bits;
     memcpy(&bits, &x, 4);
     return (uint16_t)((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16);
+}
+
+/* One rank's step call, for the mode that gives every rank a host thread of its own. */
+typedef struct rank_call {
+    oe_zero1* z;
+    const oe_adamw_hparams* hp;
+    int rc;
+} rank_call;
+
+static void* rank_step(void* arg) {
+    rank_call* c = (rank_call*)arg;
+    c->rc = oe_zero1_adamw_step(c->z, c->hp, 0);
+    return NULL;
 }
 
 int main(int argc, char** argv) {
@@ -150,7 +166,28 @@ int main(int argc, char** argv) {
         hp.bc2 = (float)(1.0 - pow((double)beta2, (double)step));
         hp.max_norm = max_norm;
         hp.flags = OE_WRITE_SHADOW;
-        for (int r = 0; r < world; r++) CHECK(oe_zero1_adamw_step(z[r], &hp, 0)); /* enqueue only */
+        if (!copies) {
+            for (int r = 0; r < world; r++) CHECK(oe_zero1_adamw_step(z[r], &hp, 0)); /* enqueue only */
+        } else {
+            /* A copy between two devices of ONE process may keep the host in the call until the work queued
+             * before it has run, and a step begins with a wait for the other ranks: so each rank's call comes
+             * from a thread of its own here, as gograd pins one OS thread per device. (Ranks in processes of
+             * their own, the usual case, need nothing of the kind.) */
+            pthread_t th[MAX_RANKS];
+            rank_call call[MAX_RANKS];
+            for (int r = 0; r < world; r++) {
+                call[r].z = z[r];
+                call[r].hp = &hp;
+                call[r].rc = -1;
+                if (pthread_create(&th[r], NULL, rank_step, &call[r]) != 0) return 1;
+            }
+            for (int r = 0; r < world; r++) pthread_join(th[r], NULL);
+            for (int r = 0; r < world; r++)
+                if (call[r].rc != 0) {
+                    fprintf(stderr, "rank %d: oe_zero1_adamw_step failed (%d): %s\n", r, call[r].rc, oe_last_error());
+                    return 1;
+                }
+        }
         for (int r = 0; r < world; r++) {
             uint32_t status = 0;
             CHECK(oe_zero1_status(z[r], &status, 0));

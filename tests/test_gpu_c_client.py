@@ -55,8 +55,8 @@ def test_c_zero1_runs(tmp_path):
     exe = tmp_path / "c_zero1"
     subprocess.run([cc, "-std=c11", "-O1", "-ffp-contract=off", "-Wall", "-Wextra",
                     os.path.join(lib_dir, "csrc", "examples", "c_zero1.c"), "-I", os.path.join(ROOT, "include"), "-L", lib_dir,
-                    "-loptengine", f"-Wl,-rpath,{lib_dir}", "-lm", "-o", str(exe)], check=True)
+                    "-loptengine", f"-Wl,-rpath,{lib_dir}", "-lm", "-lpthread", "-o", str(exe)], check=True)
     for mode in ([], ["copies"]):   # "copies": staged gradient copies and a shadow copy, asked for explicitly
         out = subprocess.run([str(exe)] + mode, capture_output=True, text=True, timeout=300)
-        assert out.returncode == 0, out.stderr
+        assert out.returncode == 0, f"mode {mode}: {out.stderr}"
         assert "c_zero1 ok" in out.stdout
