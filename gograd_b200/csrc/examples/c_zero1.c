@@ -57,12 +57,13 @@ static uint16_t bf16_rne(float x) {
 typedef struct rank_call {
     oe_zero1* z;
     const oe_adamw_hparams* hp;
+    uint64_t stream;
     int rc;
 } rank_call;
 
 static void* rank_step(void* arg) {
     rank_call* c = (rank_call*)arg;
-    c->rc = oe_zero1_adamw_step(c->z, c->hp, 0);
+    c->rc = oe_zero1_adamw_step(c->z, c->hp, c->stream);
     return NULL;
 }
 
@@ -80,7 +81,7 @@ int main(int argc, char** argv) {
     const uint32_t total = SHARD * (uint32_t)world;
     const float lr = 3e-4f, beta1 = 0.9f, beta2 = 0.95f, eps = 1e-8f, decay = 0.1f, max_norm = 0.01f;
     uint64_t grad[MAX_RANKS], shadow[MAX_RANKS], master[MAX_RANKS], m[MAX_RANKS], v[MAX_RANKS], sync[MAX_RANKS];
-    uint64_t staging[MAX_RANKS];
+    uint64_t staging[MAX_RANKS], stream[MAX_RANKS];
     const uint32_t staged = (copies && world > 1) ? (uint32_t)(world > 2 ? world - 2 : 1) : 0;
     oe_plan* plan[MAX_RANKS];
     oe_zero1* z[MAX_RANKS];
@@ -103,7 +104,11 @@ int main(int argc, char** argv) {
         CHECK(oe_mem_alloc(r, 4ull * SHARD, &v[r]));
         CHECK(oe_mem_alloc(r, OE_ZERO1_SYNC_BYTES, &sync[r]));
         staging[r] = 0;
-        if (staged) CHECK(oe_mem_alloc(r, 4ull * SHARD * staged, &staging[r]));
+        stream[r] = 0; /* the device's default stream, unless the step uses copies (below) */
+        if (staged) {
+            CHECK(oe_mem_alloc(r, 4ull * SHARD * staged, &staging[r]));
+            CHECK(oe_stream_create(r, &stream[r]));
+        }
         CHECK(oe_memset_u32(r, shadow[r], 0, total / 2, 0));
         CHECK(oe_memset_u32(r, m[r], 0, SHARD, 0));
         CHECK(oe_memset_u32(r, v[r], 0, SHARD, 0));
@@ -169,15 +174,17 @@ int main(int argc, char** argv) {
         if (!copies) {
             for (int r = 0; r < world; r++) CHECK(oe_zero1_adamw_step(z[r], &hp, 0)); /* enqueue only */
         } else {
-            /* A copy between two devices of ONE process may keep the host in the call until the work queued
-             * before it has run, and a step begins with a wait for the other ranks: so each rank's call comes
-             * from a thread of its own here, as gograd pins one OS thread per device. (Ranks in processes of
-             * their own, the usual case, need nothing of the kind.) */
+            /* A copy between two devices of ONE process is work for both devices: it may keep the host in the
+             * call until the work queued before it has run, and on a device's default stream it is ordered after
+             * that device's own step, which waits for the other rank. So here each rank's call comes from a thread
+             * of its own, as gograd pins one OS thread per device, on a stream created for it. (Ranks in
+             * processes of their own, the usual case, need nothing of the kind.) */
             pthread_t th[MAX_RANKS];
             rank_call call[MAX_RANKS];
             for (int r = 0; r < world; r++) {
                 call[r].z = z[r];
                 call[r].hp = &hp;
+                call[r].stream = stream[r];
                 call[r].rc = -1;
                 if (pthread_create(&th[r], NULL, rank_step, &call[r]) != 0) return 1;
             }
@@ -190,7 +197,7 @@ int main(int argc, char** argv) {
         }
         for (int r = 0; r < world; r++) {
             uint32_t status = 0;
-            CHECK(oe_zero1_status(z[r], &status, 0));
+            CHECK(oe_zero1_status(z[r], &status, stream[r]));
         }
         /* the same step on the host */
         double sumsq = 0.0;
@@ -255,6 +262,7 @@ int main(int argc, char** argv) {
         CHECK(oe_mem_free(r, v[r]));
         CHECK(oe_mem_free(r, sync[r]));
         if (staging[r]) CHECK(oe_mem_free(r, staging[r]));
+        if (stream[r]) CHECK(oe_stream_destroy(r, stream[r]));
     }
     CHECK(oe_shutdown());
     printf("c_zero1 ok: %d rank(s), %d sharded AdamW steps driven from C, master weights and every rank's bf16 shadow equal the host loop bit for bit\n",

@@ -407,9 +407,11 @@ OE_API int oe_zero1_destroy(oe_zero1* z);
  * sums, added in rank order into the global norm -> fused update with the clip folded in, shadow stored
  * to every rank -> exchange "stores performed". hp as for oe_adamw_step / oe_sgd_step.
  * One host thread may enqueue the steps of several ranks (devices) one after the other as long as the context
- * uses no copies; with copies, issue each rank's call from a thread (or process) of its own: a copy between
- * two devices of one process may keep the host in the call until the work queued before it has run, and that
- * work begins with a wait for the other ranks. */
+ * uses no copies. With copies and several ranks in ONE process, issue each rank's call from a thread of its own
+ * and on a stream created for it (oe_stream_create), not the device's default stream: a copy between two devices
+ * of one process is work for both, it may keep the host in the call until the work queued before it has run, and
+ * on a default stream it is ordered after that device's own step, which waits for the other ranks (measured: the
+ * exchanges then run into their limit). Ranks in processes of their own need neither. */
 OE_API int oe_zero1_adamw_step(oe_zero1* z, const oe_adamw_hparams* hp, uint64_t stream);
 OE_API int oe_zero1_sgd_step(oe_zero1* z, const oe_sgd_hparams* hp, uint64_t stream);
 
