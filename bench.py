@@ -601,8 +601,8 @@ def main():
                     help="N > 1, --comm abi: peers whose gradient range a copy stages before the pull kernel (default: the library's choice; 0 = none)")
     ap.add_argument("--ce-push-targets", type=int, default=None,
                     help="N > 1, --comm abi: ranks served by a shadow copy after the update kernel (default: the library's choice; 0 = none)")
-    ap.add_argument("--staging-writers", action="store_true",
-                    help="N > 1, --comm abi: the staged gradient ranges are written by their owners instead of read by the reducing rank")
+    ap.add_argument("--staging-readers", action="store_true",
+                    help="N > 1, --comm abi: the staged gradient ranges are read by the reducing rank instead of written by their owners")
     ap.add_argument("--sweep", action="store_true",
                     help="N > 1: time the two peer kernels over every launch-shape knob instead of the step")
     ap.add_argument("--no-parity-check", action="store_true", help="N > 1: skip the oracle check of one step before the warm-up")

@@ -49,7 +49,7 @@ def run(args) -> int:
                      push_order=args.push_order, exchange_timeout_ms=30000,
                      ce_pull_sources=getattr(args, "ce_pull_sources", None) if comm == "abi" else None,
                      ce_push_targets=getattr(args, "ce_push_targets", None) if comm == "abi" else None,
-                     staging_writers=bool(getattr(args, "staging_writers", False)) and comm == "abi")
+                     staging_writers=not getattr(args, "staging_readers", False))
     ce_pull, ce_push = opt.ctx.copy_engine_use() if opt.ctx is not None else (0, 0)
     staged_by = "owners" if (opt.ctx is not None and opt.ctx.staging_written_by_owners()) else "reader"
     tuning = apply_tuning(opt, args)

@@ -249,14 +249,14 @@ class Zero1AdamW(Zero1Schedule):
     before the pull kernel, and how many ranks get their shadow values from a copy after the update
     kernel; None leaves the choice to the library (by world size and shard size), 0 switches it off.
     The staging buffer (4 bytes x shard length per staged peer) is allocated here. `staging_writers`
-    maps every rank's staging on every GPU, so that the staged ranges are written by their owners
-    instead of read by the rank that reduces them."""
+    (default) maps every rank's staging on every GPU, so that the staged ranges are written by their
+    owners (770 GB/s per GPU on B200 boxes) instead of read by the rank that reduces them (740)."""
 
     def __init__(self, numels: Sequence[int], group_of: Sequence[Tuple[float, float]], lr: float, beta1: float,
                  beta2: float, eps: float, max_norm: float, device: int, comm: str = "peer", process_group=None,
                  chunk_elems: int = 0, multicast: bool = False, exchange_timeout_ms: int = 0,
                  push_order: str = "ascending", ce_pull_sources: Optional[int] = None,
-                 ce_push_targets: Optional[int] = None, staging_writers: bool = False):
+                 ce_push_targets: Optional[int] = None, staging_writers: bool = True):
         import torch
         import torch.distributed as dist
 
