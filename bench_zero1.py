@@ -158,7 +158,7 @@ def run(args) -> int:
         # the link rates this box gave the two access patterns a moment ago, with nothing else riding on them
         read_peak = link["reads_GBs"] if link else None
         store_peak = link["stores_GBs"] if link else None
-        copy_peak = link["ring_copy_GBs"] if link else None
+        copy_peak = max(link["ring_copy_GBs"], link.get("ring_copy_write_GBs", 0.0)) if link else None
         # With copies carrying part of a phase, the phase is rated against the better of the two rates the
         # fabric gave a moment ago: SM-issued accesses to every peer at once, or one copy between neighbours.
         reduce_peak = max(read_peak, copy_peak) if (read_peak and ce_pull) else read_peak
@@ -178,7 +178,7 @@ def run(args) -> int:
             "achieved": pull_remote / (k1 * 1e-3) / 1e9 if k1 else None, "peak": reduce_peak or NVLINK_PEER_GBS, "unit": "GB/s",
             "frac": (pull_remote / (k1 * 1e-3) / 1e9 / (reduce_peak or NVLINK_PEER_GBS)) if k1 else None,
             "peak_kind": ("measured in this run: the better of every rank reading its shard of every peer's gradient buffer at "
-                          "the same time (oe_link_probe_reads) and every rank copying from its neighbour at the same time") if (reduce_peak and ce_pull) else
+                          "the same time (oe_link_probe_reads) and every rank copying from, or to, its neighbour at the same time") if (reduce_peak and ce_pull) else
                          ("measured in this run: every rank reading its shard of every peer's gradient buffer at the same time, "
                           "nothing stored (oe_link_probe_reads)") if read_peak else
                          "builder constant: 770 GB/s, a one-at-a-time copy-engine peer copy measured on this pool "
@@ -288,11 +288,17 @@ def measure_link_peaks(opt, torch, dist, iters: int = 3):
     source = opt.grad_bases[(opt.rank + 1) % world] + 4 * opt.lo
     c = timed(lambda: engine_copy(opt, scratch.data_ptr(), source, 4 * shard))
     del scratch
-    return {"reads_GBs": 4.0 * shard * (world - 1) / r / 1e6, "reads_ms": r,
-            "stores_GBs": 2.0 * shard * (world - 1) / w / 1e6, "stores_ms": w,
-            "ring_copy_GBs": 4.0 * shard / c / 1e6, "ring_copy_ms": c,
-            "how": "oe_link_probe_reads / oe_link_probe_stores / one oe_memcpy_d2d from the next rank, on every rank at once, "
-                   "median of %d, max over ranks" % iters}
+    out = {"reads_GBs": 4.0 * shard * (world - 1) / r / 1e6, "reads_ms": r,
+           "stores_GBs": 2.0 * shard * (world - 1) / w / 1e6, "stores_ms": w,
+           "ring_copy_GBs": 4.0 * shard / c / 1e6, "ring_copy_ms": c,
+           "how": "oe_link_probe_reads / oe_link_probe_stores / one oe_memcpy_d2d from the next rank (and, where the ranks' "
+                  "staging is shared, one into the next rank's staging), on every rank at once, median of %d, max over ranks" % iters}
+    if opt.staging_bases:
+        # the same copy the other way: this rank's gradient range for the next rank, written into that rank's staging
+        nxt = (opt.rank + 1) % world
+        cw = timed(lambda: engine_copy(opt, opt.staging_bases[nxt], opt.grad_flat.data_ptr() + 4 * shard * nxt, 4 * shard))
+        out["ring_copy_write_GBs"], out["ring_copy_write_ms"] = 4.0 * shard / cw / 1e6, cw
+    return out
 
 
 def engine_copy(opt, dst: int, src: int, nbytes: int) -> None:
