@@ -338,8 +338,8 @@ OE_API int oe_link_probe_stores(oe_plan* plan, uint64_t shadow_shard, const int6
 
 /* ---- sharded step driven through this interface alone -------------------------------------------- */
 /* For a host with no collective library (the reference has none: one OS thread per device,
- * autograd/cuda_context.go:29-54). The three points at which the ranks of a step must meet are small
- * kernels of the library: every rank announces its arrival with plain stores into an exchange area in
+ * autograd/cuda_context.go:29-54). The points at which the ranks of a step must meet (three, or four when
+ * staged gradient ranges are written by their owners, below) are small kernels of the library: every rank announces its arrival with plain stores into an exchange area in
  * each rank's memory, then waits for the others' announcements in its own area. The wait is bounded:
  * after timeout_ms (or an equivalent number of polls) the kernel records the missing rank in the area's
  * status word and returns; every later launch of the sharded step (pull-reduce, update, exchanges) sees
@@ -364,7 +364,7 @@ typedef struct oe_zero1_desc {
     uint64_t sync_blocks[8];       /* rank k's exchange area as mapped on this GPU                     */
     uint32_t timeout_ms;           /* limit of every wait, 0 = 10000                                   */
     uint32_t flags;                /* OE_ZERO1_NO_ENTRY_EXCHANGE                                       */
-    /* Copy-engine assistance (see below); all four may be 0.                                          */
+    /* Copy-engine assistance (see below); all of it may be 0.                                         */
     uint64_t staging;              /* caller-owned device scratch, 16-byte aligned, or 0               */
     uint64_t staging_bytes;
     uint32_t ce_pull_sources;      /* peers whose gradient range a copy brings into staging before the
@@ -377,8 +377,8 @@ typedef struct oe_zero1_desc {
 #define OE_ZERO1_CE_NONE 0xffffffffu
 /* Copy-engine assistance. With all GPUs of a box reading (or writing) each other at once, SM-issued loads
  * reach about 665 GB/s and stores about 620 GB/s per GPU; copies issued in RING order — in window j every rank
- * talks to the rank j places after it, so every GPU serves one reader and one writer at a time — reach
- * 740 / 770 GB/s. So from four ranks on the step lets copies carry part of the traffic, all on the caller's
+ * talks to the rank j+1 places after it, so every GPU serves one reader and one writer at a time — reach
+ * 740 GB/s when they read from the peer and 770 GB/s when they write to it. So from four ranks on the step lets copies carry part of the traffic, all on the caller's
  * stream, in whole-shard pieces:
  *   reduce: the ranges of the first ce_pull_sources ranks after this one are copied into `staging` (4*numel
  *           bytes each), then the pull kernel reads those locally and the remaining peers over NVLink — same
