@@ -83,7 +83,7 @@ var oeSymbols = []string{
 	"oe_plan_norm_address", "oe_plan_set_grad_scale", "oe_grad_norm", "oe_norm_finalize", "oe_clip_grad_norm",
 	"oe_read_norm", "oe_adamw_step", "oe_sgd_step", "oe_zero_grads", "oe_cast_bf16",
 	"oe_peer_reduce_grads", "oe_adamw_step_peers", "oe_sgd_step_peers",
-	"oe_zero1_create", "oe_zero1_destroy", "oe_zero1_adamw_step", "oe_zero1_sgd_step", "oe_zero1_status",
+	"oe_zero1_create", "oe_zero1_destroy", "oe_zero1_adamw_step", "oe_zero1_sgd_step", "oe_zero1_status", "oe_zero1_info",
 	"oe_ipc_export", "oe_ipc_import", "oe_ipc_close",
 	"oe_mem_alloc", "oe_mem_free", "oe_memcpy_h2d", "oe_memcpy_d2h", "oe_memset_u32", "oe_stream_sync",
 	"oe_launch_count",
@@ -253,8 +253,11 @@ func CastBF16(device int, src, dst uintptr, count int, stream uintptr) error {
 	return oeCall("oe_cast_bf16", uintptr(device), src, dst, uintptr(count), stream)
 }
 
-// Zero1 is an oe_zero1: a sharded step whose three exchanges between the ranks are kernels of
-// the library, for a host that has no collective library (gograd has none).
+// Zero1 is an oe_zero1: a sharded step whose exchanges between the ranks are kernels of the
+// library, for a host that has no collective library (gograd has none). With Staging set in the
+// descriptor the step lets whole-shard copies carry part of the traffic from four ranks on; a host
+// that keeps all ranks in one process then calls each rank's step from that rank's pinned OS
+// thread on a stream created for it (autograd/cuda_context.go:29-54 pins the thread already).
 type Zero1 struct{ handle uintptr }
 
 func NewZero1(plan *Plan, desc *Zero1Desc) (*Zero1, error) {
@@ -271,6 +274,13 @@ func (z *Zero1) AdamWStep(hp *AdamWHParams, stream uintptr) error {
 
 func (z *Zero1) SGDStep(hp *SGDHParams, stream uintptr) error {
 	return oeCall("oe_zero1_sgd_step", z.handle, uintptr(unsafe.Pointer(hp)), stream)
+}
+
+// CopyPlan reports how many peers' gradient ranges copies stage before the pull kernel and how
+// many ranks receive their shadow values from a copy, as the library resolved them.
+func (z *Zero1) CopyPlan() (stagedSources, shadowCopies int) {
+	lib := oeLib
+	return int(int64(oeCallRaw(lib.fn["oe_zero1_info"], z.handle, 0))), int(int64(oeCallRaw(lib.fn["oe_zero1_info"], z.handle, 1)))
 }
 
 // Status waits for stream; a rank that missed an exchange is reported as an *Error whose message
