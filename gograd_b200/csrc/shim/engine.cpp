@@ -1478,7 +1478,8 @@ extern "C" int oe_zero1_create(oe_plan* plan, const oe_zero1_desc* desc, oe_zero
         pull = desc->ce_pull_sources;
     }
     if (desc->ce_push_targets == 0) {
-        if (desc->world >= 8) push = others - 3;
+        // a caller that gives no staging has not asked for copies at all: all-zero fields mean the kernels alone
+        if (desc->world >= 8 && desc->staging != 0) push = others - 3;
     } else if (desc->ce_push_targets != OE_ZERO1_CE_NONE) {
         if (desc->ce_push_targets > others) return fail(OE_ERR_INVALID, "oe_zero1_create: ce_push_targets exceeds the number of peers");
         push = desc->ce_push_targets;

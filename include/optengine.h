@@ -390,9 +390,10 @@ typedef struct oe_zero1_desc {
  *           (first_elem = rank * numel on every rank) and the same ce_pull_sources on every rank;
  *   update: the kernel stores the shadow to this rank and the next world-1-ce_push_targets ranks, then copies
  *           deliver this rank's shard to the remaining ranks.
- * The library's choice (measured on 8-GPU B200 boxes): eight ranks: all but one peer through staging, four
- * shadow copies; four to seven ranks: all but one peer through staging, no shadow copies; fewer: none. Without
- * (enough) staging the reduce stays on the SM path. */
+ * The library's choice (measured on 8-GPU B200 boxes), made only for a caller that provides staging: eight
+ * ranks: all but one peer through staging, four shadow copies; four to seven ranks: all but one peer through
+ * staging, no shadow copies; fewer: none. With staging for fewer ranges than that, as many as fit are staged.
+ * A descriptor whose copy fields are all zero runs on the kernels alone. */
 
 typedef struct oe_zero1 oe_zero1;
 

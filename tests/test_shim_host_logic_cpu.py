@@ -103,7 +103,7 @@ def test_sharded_step_with_staging_written_by_the_owners(cases):
 def test_the_librarys_own_copy_plan(cases):
     """[staged sources, copied shadow targets] as oe_zero1_create resolves them when the caller leaves the choice."""
     assert cases["zero1_library_choice"] == {
-        "8 ranks": [6, 4], "8 ranks, staging for 3": [3, 4], "8 ranks, no staging": [0, 4], "8 ranks, small shard": [0, 4],
+        "8 ranks": [6, 4], "8 ranks, staging for 3": [3, 4], "8 ranks, no staging": [0, 0], "8 ranks, small shard": [0, 4],
         "4 ranks": [2, 0], "2 ranks": [0, 0], "1 rank": [0, 0]}
 
 
